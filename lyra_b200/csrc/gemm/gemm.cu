@@ -1,0 +1,468 @@
+// Persistent warp-specialised bf16 GEMM for sm_100a: TMA (local memory) -> 128B-swizzled shared
+// memory -> tcgen05.mma with fp32 accumulators in TMEM -> tcgen05.ld epilogue.
+//
+//   D[M,N] = alpha * A[M,K] x B[N,K]^T + beta * Cin        (dense)
+//   grouped-M : rows of A/D are sorted by group, each 128-row tile belongs to one group and uses
+//               that group's B (ragged grouped GEMM of a mixture-of-experts layer; the reference's
+//               `GEMM` / `GEMM_DLHS`, lyra/kernels/gemm.py:512-1120)
+//   grouped-K : per group g, D[g] = A[:, rows_g]^T-style contraction over the group's rows
+//               (expert weight gradients; the reference's `TGEMM`, lyra/kernels/gemm.py:1175-1445)
+//   batched   : independent problems of the same shape (Newton-Schulz over stacked expert matrices)
+//
+// Either operand may be K-major (contraction dim contiguous) or MN-major (its own dim contiguous), so
+// forward, data-gradient and weight-gradient products of an [in,out]-layout weight run without transposes.
+// Epilogues: plain store (bf16 or fp32, optional bias, optional alpha/beta with a second input), and the
+// fused clamped SwiGLU of the reference (lyra/kernels/common.py:98-114) where each 256-wide accumulator
+// tile holds 128 gate columns and their 128 linear columns.
+//
+// Roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 = epilogue.
+// Two 256-column accumulators (all 512 TMEM columns) let the epilogue of tile i overlap tile i+1.
+#include "../common/sm100.cuh"
+#include "../common/tmap.h"
+
+namespace lyra {
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int GEMM_THREADS = 192;
+
+enum GroupMode : int { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2, GROUP_BATCH = 3 };
+enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU = 1 };
+
+struct GemmParams {
+  int M, N, K;              // per-problem extents (N = accumulator columns; SwiGLU output has N/2)
+  int m_tiles, n_tiles, total_tiles;
+  void* C;                  // output
+  const void* Cin;          // optional second input of the epilogue (same dtype / ld as C)
+  long long ldc;
+  long long c_group_stride; // elements between per-group outputs (grouped-K / batched)
+  int out_fp32;
+  float alpha, beta;
+  const float* bias;        // [groups, N] or [N] or null
+  long long bias_group_stride;
+  int group_mode;
+  const int* tile_group;    // grouped-M: group of each 128-row tile, -1 = unused tile
+  const int* group_offsets; // grouped-K: [G+1] row offsets, multiples of 64
+  int num_groups;
+  int n_split;              // SwiGLU: column where the linear half starts in B (= hidden size)
+  float swiglu_beta, swiglu_limit;
+  int* status;
+};
+
+struct TileInfo {
+  int m0, n0, ga, gb, gc, krow0, num_kb;
+  bool valid;
+};
+
+template <int BN, int EPI>
+__device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
+  TileInfo t;
+  constexpr int NSTEP = (EPI == EPI_SWIGLU) ? BN / 2 : BN;
+  t.valid = true;
+  t.ga = t.gb = t.gc = 0;
+  t.krow0 = 0;
+  t.num_kb = (p.K + BK - 1) / BK;
+  int local = tile;
+  if (p.group_mode == GROUP_K || p.group_mode == GROUP_BATCH) {
+    const int per = p.m_tiles * p.n_tiles;
+    const int g = tile / per;
+    local = tile - g * per;
+    t.gc = g;
+    if (p.group_mode == GROUP_K) {
+      const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
+      t.krow0 = b;
+      t.num_kb = (e - b + BK - 1) / BK;
+    } else {
+      t.ga = t.gb = g;
+    }
+  }
+  const int m_blk = local / p.n_tiles;
+  const int n_blk = local - m_blk * p.n_tiles;
+  t.m0 = m_blk * BM;
+  t.n0 = n_blk * NSTEP;
+  if (p.group_mode == GROUP_M) {
+    const int g = p.tile_group[m_blk];
+    t.valid = g >= 0;
+    t.gb = g < 0 ? 0 : g;
+  }
+  return t;
+}
+
+__device__ __forceinline__ float swiglu_act(float g, float l, float beta, float limit) {
+  g = fminf(g, limit);
+  l = fminf(fmaxf(l, -limit), limit);
+  return (l + 1.0f) * g * (1.0f / (1.0f + __expf(-beta * g)));
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+  constexpr int A_BYTES = BM * BK * 2;
+  constexpr int B_BYTES = BN * BK * 2;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int STAGES = (BN == 256) ? 4 : 6;
+  constexpr uint32_t TMEM_COLS = 2 * BN;  // 512 or 256: a power of two
+  constexpr uint32_t IDESC = make_idesc(BM, BN, 1, 1, A_MN ? 1 : 0, B_MN ? 1 : 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tfull_bar[a]), 1);
+      mbar_init(smem_u32(&tempty_bar[a]), 4);
+    }
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_holder;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_a);
+      tma_prefetch_desc(&tma_b);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const TileInfo t = decode_tile<BN, EPI>(p, tile);
+        if (!t.valid) continue;
+        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abortp)) {
+            atomicExch(p.status, STATUS_TIMEOUT_EMPTY);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const int k0 = t.krow0 + kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * (BK * 128), &tma_a, bar, t.m0 + j * 64, k0, t.ga);
+          } else {
+            tma_load_3d(sa, &tma_a, bar, k0, t.m0, t.ga);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) {
+              int col = t.n0 + j * 64;
+              if (EPI == EPI_SWIGLU && j >= BN / 128) col = p.n_split + t.n0 + (j - BN / 128) * 64;
+              tma_load_3d(sb + j * (BK * 128), &tma_b, bar, col, k0, t.gb);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 128; ++j) {
+              int row = t.n0 + j * 128;
+              if (EPI == EPI_SWIGLU && j >= 1) row = p.n_split + t.n0;
+              tma_load_3d(sb + j * (128 * 128), &tma_b, bar, k0, row, t.gb);
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
+        const TileInfo t = decode_tile<BN, EPI>(p, tile);
+        if (!t.valid) continue;
+        if (t.num_kb == 0) continue;  // empty group: epilogue writes zeros without an accumulator
+        const int acc = tile_it & 1;
+        const uint32_t aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abortp)) {
+          atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + acc * BN;
+        for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(smem_u32(&full_bar[s]), ph, abortp)) {
+            atomicExch(p.status, STATUS_TIMEOUT_FULL);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint32_t sb = sa + A_BYTES;
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + k * 2048, BK * 128, 1024) : make_smem_desc(sa + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + k * 2048, BK * 128, 1024) : make_smem_desc(sb + k * 32, 16, 1024);
+            tc_mma_ss(tmem_d, da, db, IDESC, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(smem_u32(&empty_bar[s]));  // frees the stage when these MMAs retire
+        }
+        if (ok) tc_commit(smem_u32(&tfull_bar[acc]));
+        ++tile_it;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (4 warps, one TMEM lane quarter each)
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    uint32_t tile_it = 0;
+    for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x) {
+      const TileInfo t = decode_tile<BN, EPI>(p, tile);
+      if (!t.valid) continue;
+      const bool have_acc = t.num_kb > 0;
+      const int acc = tile_it & 1;
+      if (have_acc) {
+        const uint32_t aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abortp)) {
+          if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+          abort_flag = 1;
+          break;
+        }
+        tc_fence_after();
+      }
+      const uint32_t taddr = tmem_base + acc * BN + (uint32_t(quarter * 32) << 16);
+      const int row = t.m0 + row_in_tile;
+      const bool row_ok = row < p.M;
+      const long long c_off = (long long)t.gc * p.c_group_stride + (long long)row * p.ldc;
+      const float* bias = p.bias ? p.bias + (long long)(p.group_mode == GROUP_M ? t.gb : t.gc) * p.bias_group_stride : nullptr;
+
+      if (EPI == EPI_STORE) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          const int col = t.n0 + c * 32;
+          if (row_ok && col < p.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+            if (bias) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (col + i < p.N) v[i] += bias[col + i];
+            }
+            if (p.out_fp32) {
+              float* dst = reinterpret_cast<float*>(p.C) + c_off + col;
+              const float* src = p.Cin ? reinterpret_cast<const float*>(p.Cin) + c_off + col : nullptr;
+#pragma unroll
+              for (int q = 0; q < 8; ++q) {
+                if (col + q * 4 < p.N) {
+                  float4 o = make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+                  if (src) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(src + q * 4);
+                    o.x += p.beta * s4.x; o.y += p.beta * s4.y; o.z += p.beta * s4.z; o.w += p.beta * s4.w;
+                  }
+                  *reinterpret_cast<float4*>(dst + q * 4) = o;
+                }
+              }
+            } else {
+              __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+              const __nv_bfloat16* src = p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + c_off + col : nullptr;
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                if (col + q * 8 < p.N) {
+                  if (src) {
+                    const uint4 s4 = *reinterpret_cast<const uint4*>(src + q * 8);
+                    const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&s4);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                      const float2 f = __bfloat1622float2(sp[i]);
+                      v[q * 8 + 2 * i] += p.beta * f.x;
+                      v[q * 8 + 2 * i + 1] += p.beta * f.y;
+                    }
+                  }
+                  uint4 o;
+                  o.x = pack_bf16(v[q * 8 + 0], v[q * 8 + 1]);
+                  o.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+                  o.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+                  o.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+                  *reinterpret_cast<uint4*>(dst + q * 8) = o;
+                }
+              }
+            }
+          }
+        }
+      } else {
+        // SwiGLU: accumulator columns [0,BN/2) = gate, [BN/2,BN) = linear, output columns n0 .. n0+BN/2
+        const int n_out = p.n_split;
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          uint32_t g[32], l[32];
+          tmem_ld32(taddr + c * 32, g);
+          tmem_ld32(taddr + BN / 2 + c * 32, l);
+          tmem_ld_wait();
+          const int col = t.n0 + c * 32;
+          if (row_ok && col < n_out) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float gv = __uint_as_float(g[i]), lv = __uint_as_float(l[i]);
+              if (bias && col + i < n_out) {
+                gv += bias[col + i];
+                lv += bias[n_out + col + i];
+              }
+              v[i] = swiglu_act(gv, lv, p.swiglu_beta, p.swiglu_limit);
+            }
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col + q * 8 < n_out) {
+                uint4 o;
+                o.x = pack_bf16(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(dst + q * 8) = o;
+              }
+            }
+          }
+        }
+      }
+      if (have_acc) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+        ++tile_it;
+      }
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  __syncthreads();
+  if (abort_flag) {
+    // let any TMA copy still in flight land before the shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int BN>
+constexpr int gemm_smem_bytes() {
+  return ((BN == 256) ? 4 : 6) * (BM * BK * 2 + BN * BK * 2) + 1024;
+}
+
+template <int BN, bool A_MN, bool B_MN, int EPI>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+  auto kern = gemm_kernel<BN, A_MN, B_MN, EPI>;
+  static bool configured = false;
+  constexpr int smem = gemm_smem_bytes<BN>();
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    configured = true;
+  }
+  int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+  if (grid <= 0) return 0;
+  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+}  // namespace lyra
+
+using namespace lyra;
+
+// Operand description: a row-major 2-D (or stacked 3-D) bf16 array.
+//   K-major  operand: rows = M (or N), cols = K        -> mn_major = 0
+//   MN-major operand: rows = K,        cols = M (or N)  -> mn_major = 1
+// `ld` = elements between rows, `group_stride` = elements between stacked matrices (0 if not stacked).
+extern "C" int lyra_gemm_bf16(
+    const void* A, long long lda, long long a_group_stride, int a_mn,
+    const void* B, long long ldb, long long b_group_stride, int b_mn,
+    void* C, const void* Cin, long long ldc, long long c_group_stride, int out_fp32,
+    int M, int N, int K, float alpha, float beta,
+    const float* bias, long long bias_group_stride,
+    int group_mode, int num_groups, const int* tile_group, const int* group_offsets, int total_rows,
+    int epilogue, int n_split, float swiglu_beta, float swiglu_limit,
+    int* status, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8))) return -10;
+  const int G = num_groups > 0 ? num_groups : 1;
+  constexpr int BN = 256;
+
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.Cin = Cin; p.ldc = ldc; p.c_group_stride = c_group_stride; p.out_fp32 = out_fp32;
+  p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = bias_group_stride;
+  p.group_mode = group_mode; p.tile_group = tile_group; p.group_offsets = group_offsets; p.num_groups = G;
+  p.n_split = n_split; p.swiglu_beta = swiglu_beta; p.swiglu_limit = swiglu_limit; p.status = status;
+  p.m_tiles = (M + BM - 1) / BM;
+  if (epilogue == EPI_SWIGLU) p.n_tiles = (n_split + BN / 2 - 1) / (BN / 2);
+  else p.n_tiles = (N + BN - 1) / BN;
+  p.total_tiles = p.m_tiles * p.n_tiles * ((group_mode == GROUP_K || group_mode == GROUP_BATCH) ? G : 1);
+
+  // Tensor maps (3-D: inner, rows, group). Row counts seen by TMA:
+  //  A K-major : dims {K, rows_a, Ga};  A MN-major: dims {M, krows, Ga}
+  const bool a_grouped = group_mode == GROUP_BATCH;
+  const bool b_grouped = group_mode == GROUP_BATCH || group_mode == GROUP_M;
+  const uint64_t krows = (group_mode == GROUP_K) ? (uint64_t)total_rows : (uint64_t)K;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    if (a_mn) { dims[0] = M; dims[1] = krows; box[0] = 64; box[1] = BK; }
+    else      { dims[0] = K; dims[1] = M;     box[0] = 64; box[1] = BM; }
+    dims[2] = a_grouped ? G : 1; box[2] = 1;
+    strides[0] = (uint64_t)lda * 2;
+    strides[1] = a_grouped ? (uint64_t)a_group_stride * 2 : dims[1] * strides[0];
+    if (make_tmap(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
+  }
+  {
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    if (b_mn) { dims[0] = N; dims[1] = krows; box[0] = 64; box[1] = BK; }
+    else      { dims[0] = K; dims[1] = N;     box[0] = 64; box[1] = 128; }
+    dims[2] = b_grouped ? G : 1; box[2] = 1;
+    strides[0] = (uint64_t)ldb * 2;
+    strides[1] = b_grouped ? (uint64_t)b_group_stride * 2 : dims[1] * strides[0];
+    if (make_tmap(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  const int code = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
+  if (epilogue == EPI_SWIGLU) {
+    switch (code) {
+      case 0: return launch_gemm<BN, false, false, EPI_SWIGLU>(ta, tb, p, s);
+      case 1: return launch_gemm<BN, false, true, EPI_SWIGLU>(ta, tb, p, s);
+      default: return -13;
+    }
+  }
+  switch (code) {
+    case 0: return launch_gemm<BN, false, false, EPI_STORE>(ta, tb, p, s);
+    case 1: return launch_gemm<BN, false, true, EPI_STORE>(ta, tb, p, s);
+    case 2: return launch_gemm<BN, true, false, EPI_STORE>(ta, tb, p, s);
+    default: return launch_gemm<BN, true, true, EPI_STORE>(ta, tb, p, s);
+  }
+}
