@@ -38,7 +38,7 @@ def interleaved_moe(layers: int, every: int = 4, first: int = 4) -> tuple[MLPKin
     return tuple("moe" if (i >= first and (i - first) % every == 0) else "dense" for i in range(1, layers + 1))
 
 
-def moe_outer_dense(layers: int, start_dense: int = 2, end_dense: int = 0) -> tuple[MLPKind, ...]:
+def moe_outer_dense(layers: int, start_dense: int = 0, end_dense: int = 0) -> tuple[MLPKind, ...]:
     return tuple("dense" if (i < start_dense or i >= layers - end_dense) else "moe" for i in range(layers))
 
 
