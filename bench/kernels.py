@@ -91,6 +91,29 @@ def bench_gemm():
 
 BENCHES = {"gemm": bench_gemm}
 
+
+
+def bench_attention():
+    from lyra_b200.ops import attention as A
+
+    for (B, Nq, Nkv, T, D, name) in [(4, 16, 4, 4096, 128, "small"), (2, 32, 8, 4096, 128, "medium")]:
+        q = torch.randn(B, T, Nq, D, device="cuda").bfloat16().transpose(1, 2)
+        k = torch.randn(B, T, Nkv, D, device="cuda").bfloat16().transpose(1, 2)
+        v = torch.randn(B, T, Nkv, D, device="cuda").bfloat16().transpose(1, 2)
+        do = torch.randn(B, T, Nq, D, device="cuda").bfloat16().transpose(1, 2)
+        sinks = torch.zeros(Nq, device="cuda")
+        for window in (0, 128):
+            mean_pos = (T + 1) / 2 if not window else (window * (window + 1) / 2 + (T - window) * window) / T
+            fl = 4.0 * B * Nq * T * mean_pos * D
+            out, lse = A.flash_fwd(q, k, v, sinks, D ** -0.5, window)
+            report(f"flash fwd {name} B{B} T{T} {Nq}q/{Nkv}kv hd{D} window{window}", time_ms(lambda: A.flash_fwd(q, k, v, sinks, D ** -0.5, window)), fl)
+            report(f"flash bwd {name} B{B} T{T} {Nq}q/{Nkv}kv hd{D} window{window}",
+                   time_ms(lambda: A.flash_bwd(q, k, v, out, do, lse, sinks, D ** -0.5, window)), 2.5 * fl)
+
+
+BENCHES["attention"] = bench_attention
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
     for name, fn in BENCHES.items():
