@@ -27,7 +27,7 @@ constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
 
 enum GroupMode : int { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2, GROUP_BATCH = 3 };
-enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU = 1 };
+enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_CE_FWD = 2, EPI_CE_DZ = 3 };
 
 struct GemmParams {
   int M, N, K;              // per-problem extents (N = accumulator columns; SwiGLU output has N/2)
@@ -46,6 +46,14 @@ struct GemmParams {
   int num_groups;
   int n_split;              // SwiGLU: column where the linear half starts in B (= hidden size)
   float swiglu_beta, swiglu_limit;
+  int raster_n_major;       // 1: consecutive tiles walk M first (the B operand is streamed once; used by the vocabulary GEMMs)
+  // fused linear cross-entropy epilogues (B = the [V, C] head, N = real vocabulary size)
+  const int* ce_y;          // [M] target ids
+  float* ce_part_m;         // [n_tiles, M] per-tile row maxima          (EPI_CE_FWD)
+  float* ce_part_l;         // [n_tiles, M] per-tile sum exp(z - max)    (EPI_CE_FWD)
+  float* ce_tgt;            // [M] target logit                          (EPI_CE_FWD)
+  const float* ce_lse;      // [M] log-sum-exp                           (EPI_CE_DZ)
+  const float* ce_gscale;   // device scalar multiplying dZ              (EPI_CE_DZ)
   int* status;
 };
 
@@ -76,8 +84,14 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
       t.ga = t.gb = g;
     }
   }
-  const int m_blk = local / p.n_tiles;
-  const int n_blk = local - m_blk * p.n_tiles;
+  int m_blk, n_blk;
+  if (p.raster_n_major) {
+    n_blk = local / p.m_tiles;
+    m_blk = local - n_blk * p.m_tiles;
+  } else {
+    m_blk = local / p.n_tiles;
+    n_blk = local - m_blk * p.n_tiles;
+  }
   t.m0 = m_blk * BM;
   t.n0 = n_blk * NSTEP;
   if (p.group_mode == GROUP_M) {
@@ -312,6 +326,73 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             }
           }
         }
+      } else if (EPI == EPI_CE_FWD) {
+        // one pass over the tile: online (max, sum exp) per row and the target logit if it lies in this tile
+        const int y = row_ok ? p.ce_y[row] : -1;
+        float mx = -INFINITY, l = 0.f, tz = 0.f;
+        bool has_t = false;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = t.n0 + c * 32;
+          if (col < p.N) {
+            float cm = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const float z = (col + i < p.N) ? __uint_as_float(r[i]) : -INFINITY;
+              r[i] = __float_as_uint(z);
+              cm = fmaxf(cm, z);
+              if (col + i == y) { tz = z; has_t = true; }
+            }
+            if (cm > mx) {
+              l *= __expf(mx - cm);
+              mx = cm;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) l += __expf(__uint_as_float(r[i]) - mx);
+          }
+        }
+        if (row_ok) {
+          const long long pi = (long long)(t.n0 / BN) * p.M + row;
+          p.ce_part_m[pi] = mx;
+          p.ce_part_l[pi] = l;
+          if (has_t) p.ce_tgt[row] = tz;
+        }
+      } else if (EPI == EPI_CE_DZ) {
+        // dZ = (softmax - onehot) * g as bf16, softmax recomputed from the stored log-sum-exp
+        const int y = row_ok ? p.ce_y[row] : -1;
+        const float lse = row_ok ? p.ce_lse[row] : 0.f;
+        const float g = *p.ce_gscale;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          const int col = t.n0 + c * 32;
+          if (row_ok && col < p.N) {
+            float v[32];
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float pr = __expf(__uint_as_float(r[i]) - lse);
+              if (col + i == y) pr -= 1.0f;
+              v[i] = pr * g;
+            }
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col + q * 8 < p.N) {
+                uint4 o;
+                o.x = pack_bf16(v[q * 8 + 0], v[q * 8 + 1]);
+                o.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+                o.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+                o.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+                *reinterpret_cast<uint4*>(dst + q * 8) = o;
+              }
+            }
+          }
+        }
       } else {
         // SwiGLU: accumulator columns [0,BN/2) = gate, [BN/2,BN) = linear, output columns n0 .. n0+BN/2
         const int n_out = p.n_split;
@@ -419,6 +500,7 @@ extern "C" int lyra_gemm_bf16(
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = bias_group_stride;
   p.group_mode = group_mode; p.tile_group = tile_group; p.group_offsets = group_offsets; p.num_groups = G;
   p.n_split = n_split; p.swiglu_beta = swiglu_beta; p.swiglu_limit = swiglu_limit; p.status = status;
+  p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.m_tiles = (M + BM - 1) / BM;
   if (epilogue == EPI_SWIGLU) p.n_tiles = (n_split + BN / 2 - 1) / (BN / 2);
   else p.n_tiles = (N + BN - 1) / BN;
@@ -465,4 +547,79 @@ extern "C" int lyra_gemm_bf16(
     case 2: return launch_gemm<BN, true, false, EPI_STORE>(ta, tb, p, s);
     default: return launch_gemm<BN, true, true, EPI_STORE>(ta, tb, p, s);
   }
+}
+
+
+// Fused output head + cross entropy, forward: x [M, K] bf16, w [V, K] bf16 (first `vocab` rows used).
+// Writes per-tile partial (max, sum-exp) [ceil(vocab/256), M] and the target logit [M]; `lyra_ce_merge` finishes.
+// mode 0 = forward partials; mode 1 = dZ[M, vocab] (ld = ldz) = (softmax - onehot) * (*gscale).
+extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long long ldw, const int* y, int M, int vocab, int K, int mode,
+                            float* part_m, float* part_l, float* tgt, const float* lse, const float* gscale, void* dz, long long ldz,
+                            int* status, void* stream) {
+  if (M <= 0) return 0;
+  constexpr int BN = 256;
+  GemmParams p;
+  p.M = M; p.N = vocab; p.K = K;
+  p.C = dz; p.Cin = nullptr; p.ldc = ldz; p.c_group_stride = 0; p.out_fp32 = 0;
+  p.alpha = 1.f; p.beta = 0.f; p.bias = nullptr; p.bias_group_stride = 0;
+  p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
+  p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
+  p.raster_n_major = 1;
+  p.ce_y = y; p.ce_part_m = part_m; p.ce_part_l = part_l; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_gscale = gscale;
+  p.m_tiles = (M + BM - 1) / BM;
+  p.n_tiles = (vocab + BN - 1) / BN;
+  p.total_tiles = p.m_tiles * p.n_tiles;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, 1}, strides[2] = {(uint64_t)ldx * 2, (uint64_t)M * ldx * 2};
+    uint32_t box[3] = {64, BM, 1};
+    if (make_tmap(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)vocab, 1}, strides[2] = {(uint64_t)ldw * 2, (uint64_t)vocab * ldw * 2};
+    uint32_t box[3] = {64, 128, 1};
+    if (make_tmap(&tb, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  return mode == 0 ? launch_gemm<BN, false, false, EPI_CE_FWD>(ta, tb, p, s) : launch_gemm<BN, false, false, EPI_CE_DZ>(ta, tb, p, s);
+}
+
+namespace lyra {
+// One warp per row: merges the per-tile partials into lse and the row loss (lse - target logit).
+__global__ void ce_merge_kernel(const float* __restrict__ part_m, const float* __restrict__ part_l, const float* __restrict__ tgt,
+                                float* __restrict__ lse, float* __restrict__ row_loss, int M, int n_tiles) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= M) return;
+  float m = -INFINITY, l = 0.f;
+  for (int t = lane; t < n_tiles; t += 32) {
+    const float pm = part_m[(long long)t * M + row], pl = part_l[(long long)t * M + row];
+    if (pm > m) {
+      l = l * __expf(m - pm) + pl;
+      m = pm;
+    } else if (pm > -INFINITY) {
+      l += pl * __expf(pm - m);
+    }
+  }
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) {
+    const float om = __shfl_xor_sync(0xffffffffu, m, s), ol = __shfl_xor_sync(0xffffffffu, l, s);
+    const float nm = fmaxf(m, om);
+    l = (m > -INFINITY ? l * __expf(m - nm) : 0.f) + (om > -INFINITY ? ol * __expf(om - nm) : 0.f);
+    m = nm;
+  }
+  if (lane == 0) {
+    const float v = m + __logf(l);
+    lse[row] = v;
+    row_loss[row] = v - tgt[row];
+  }
+}
+}  // namespace lyra
+
+extern "C" int lyra_ce_merge(const float* part_m, const float* part_l, const float* tgt, float* lse, float* row_loss, int M, int n_tiles,
+                             void* stream) {
+  if (M <= 0) return 0;
+  lyra::ce_merge_kernel<<<(M + 7) / 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(part_m, part_l, tgt, lse, row_loss, M, n_tiles);
+  LYRA_CHECK_LAUNCH();
+  return 0;
 }

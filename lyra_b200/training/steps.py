@@ -94,9 +94,13 @@ class Stepper:
             grads = self.rt.reduce_grads(grads)
         with scope("optimizer"):
             trainable = {p: t for p, t in self.params.items() if p in grads}
-            metrics = optimizer_step({p: t.data for p, t in trainable.items()}, grads, self.state.optimizer, step, self.tcfg, rt=self.rt)
+            metrics = optimizer_step({p: t.detach() for p, t in trainable.items()}, grads, self.state.optimizer, step, self.tcfg, rt=self.rt)
         for t in self.params.values():
             t.grad = None
+        if self.device.type == "cuda":
+            from lyra_b200.ops import cuda_ops
+
+            cuda_ops.invalidate_shadows()
         if self.rt is not None:
             self.rt.after_optimizer(self.params)
         return {"loss": totals[0], "ce_loss": totals[1], "aux_loss": totals[2], **metrics}
