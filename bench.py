@@ -1,0 +1,267 @@
+"""Headline benchmark: lyra-medium pretraining step, tokens/s and MFU on N B200s of one node.
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 3 --warmup 3
+    python bench.py --impl reference ...        # the unmodified reference, when it can be installed
+
+Workload (weak scaling): every GPU runs `accumulation_steps` microbatches of 2 x 4096 synthetic tokens per optimizer
+step (the reference's train-medium preset accumulates 8 microbatches; lyra/training/presets.py:31), iid-uniform
+token ids over the 201,088-token vocabulary from a fixed seed, random-init fp32 master weights, bf16 compute, Muon +
+Adam update inside the timed region. `value` is whole-job tokens/s, device-timed with CUDA events, max over ranks.
+The `e2e` figure runs the same steps through the public `Stepper.train_step` API with inputs copied from pinned host
+memory every microbatch and the loss read back to the host every step.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from dataclasses import replace
+from pathlib import Path
+
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+os.environ.setdefault("LYRA_LOG_KERNELS", "0")
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+BASELINE_TOKENS_PER_S = 34150.0  # reference's published headline: lyra-small on one TPU v6e (README.md:33); nothing is published for lyra-medium
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "torch", "nccl"])
+    ap.add_argument("--variant", default="lyra-medium")
+    ap.add_argument("--micro-batch", type=int, default=2)
+    ap.add_argument("--accumulation", type=int, default=None)
+    ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (the result is then labelled invalid)")
+    return ap.parse_args()
+
+
+def reference_arm(args) -> None:
+    """The reference needs Python >= 3.14, jax 0.11.2 (+cuda13), orbax, grain and array_record; none is installed and
+    there is no package index, so it cannot be installed or run here."""
+    reason = "reference needs Python>=3.14 and jax==0.11.2/orbax/grain/array_record, none installable offline (pip --no-index: no matching distribution)"
+    try:
+        sys.path.insert(0, str(ROOT / "baseline" / "_ref"))
+        import jax  # noqa: F401
+        import lyra  # noqa: F401
+
+        reason = "reference imports, but no GPU-enabled jaxlib is present"
+    except Exception:
+        pass
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.device_index = device_index
+        self.lines: list[str] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.device_index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except Exception:
+                pass
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from lyra_b200.config import flops_per_token
+    from lyra_b200.model import ModelWeights
+    from lyra_b200.ops import cuda_ops, native
+    from lyra_b200.training.presets import TRAINING_PRESETS
+    from lyra_b200.training.state import init_train_state
+    from lyra_b200.training.steps import Stepper
+    from lyra_b200.variants import model_variant
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    rt = None
+    if world > 1:
+        from lyra_b200.parallel.runtime import Runtime
+
+        dist.init_process_group("nccl", device_id=device)
+        rt = Runtime.create(world_size=world, rank=rank, device=device, implementation="nccl" if args.impl == "nccl" else "b200")
+
+    impl = {"b200": "auto", "torch": "torch", "nccl": "nccl"}[args.impl]
+    mcfg = replace(model_variant(args.variant), implementation=impl)
+    valid = True
+    if args.layers is not None:
+        mcfg = replace(mcfg, n_layers=args.layers, mlp_map=mcfg.mlp_map[: args.layers])
+        valid = False
+    preset = TRAINING_PRESETS.get("train-" + args.variant.removeprefix("lyra-"))
+    acc = args.accumulation or (preset.accumulation_steps if preset else 1)
+    B, T = args.micro_batch, mcfg.seq_len
+    tcfg = replace(preset, batch_size=B * world, accumulation_steps=acc) if preset else None
+    if tcfg is None:
+        from lyra_b200.training.train import TrainingConfig
+
+        tcfg = TrainingConfig(batch_size=B * world, accumulation_steps=acc)
+
+    # memory plan: on one GPU the 17.7B-parameter model leaves no room for bf16 weight copies or fp32 gradients
+    from lyra_b200.nn.params import param_count
+
+    n_params = param_count(ModelWeights.spec(mcfg))
+    local_params = n_params / world if rt is not None else n_params
+    tight = local_params * 14 > 150e9
+    cuda_ops.set_memory_mode(keep_shadows=not tight, grad_dtype=torch.bfloat16 if tight else torch.float32)
+
+    shard_fn = rt.shard_info if rt is not None else None
+    weights = ModelWeights.init(mcfg.seed, mcfg, device=device, shard_fn=shard_fn)
+    state = init_train_state(weights, mcfg, tcfg)
+    stepper = Stepper(state, mcfg, tcfg, device=device, rt=rt)
+
+    rng = np.random.default_rng(1234 + rank)
+    total_steps = args.warmup + 2 * args.steps
+    host_x = [torch.from_numpy(rng.integers(0, mcfg.vocab_size, size=(acc, B, T), dtype=np.int64).astype(np.int32)).pin_memory()
+              for _ in range(min(total_steps, 4))]
+    host_y = [torch.roll(x, -1, dims=-1).contiguous().pin_memory() for x in host_x]
+    dev_x = [x.to(device) for x in host_x]
+    dev_y = [y.to(device) for y in host_y]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step_idx = 0
+    for _ in range(args.warmup):
+        stepper.train_step(dev_x[step_idx % len(dev_x)], dev_y[step_idx % len(dev_y)], step_idx)
+        step_idx += 1
+    barrier()
+    native.check_status()
+
+    # ---- device-timed region: K steps, inputs resident on the device
+    launches0 = native.launches()
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            out = stepper.train_step(dev_x[step_idx % len(dev_x)], dev_y[step_idx % len(dev_y)], step_idx)
+            step_idx += 1
+        e1.record()
+        barrier()
+    ms = e0.elapsed_time(e1)
+    launches = native.launches() - launches0
+    loss = float(out["loss"])
+
+    # ---- end to end: pinned host inputs copied every microbatch, loss read back every step
+    stepper.h2d_bytes = 0
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    d2h = 0
+    for _ in range(args.steps):
+        out = stepper.train_step(host_x[step_idx % len(host_x)], host_y[step_idx % len(host_y)], step_idx)
+        loss_e2e = out["loss"].item()
+        d2h += out["loss"].element_size()
+        step_idx += 1
+    t1.record()
+    barrier()
+    ms_e2e = t0.elapsed_time(t1)
+    native.check_status()
+
+    times = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = float(times[0]), float(times[1])
+
+    tokens_per_step = acc * B * T * world
+    value = tokens_per_step * args.steps / (ms / 1e3)
+    value_e2e = tokens_per_step * args.steps / (ms_e2e / 1e3)
+    fpt = flops_per_token(mcfg)
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    peak = json.loads(peaks_file.read_text())["bf16_tflops_sustained"] if peaks_file.exists() else 1400.0
+    if rank == 0:
+        line = {
+            "metric": "train tokens/s (lyra-medium)" if args.variant == "lyra-medium" else f"train tokens/s ({args.variant})",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(ms / args.steps, 2), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": round(value / BASELINE_TOKENS_PER_S, 3), "dtype": "bf16", "data": "synthetic",
+            "impl": args.impl,
+            "config": {"model": args.variant, "global_batch": B * world * acc, "seq_len": T, "per_gpu_microbatch": f"{B}x{T}",
+                       "accumulation_steps": acc, "parallelism": ("single" if world == 1 else f"fsdp+ep{world}"),
+                       "optimizer": "muon+adam in timed region", "l2": "per-step working set (weights, activations) far exceeds the 126 MB L2",
+                       "grad_dtype": str(cuda_ops.GRAD_DTYPE).replace("torch.", ""), "bf16_weight_copies": cuda_ops.KEEP_SHADOWS,
+                       "params": n_params, "valid": valid},
+            "mfu_of_measured_sustained_bf16": round(value * fpt / world / (peak * 1e12), 4),
+            "flops_per_token": fpt, "loss": round(loss, 4),
+            "clocks": clocks.summary(),
+            "e2e": {"value": round(value_e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": stepper.h2d_bytes // max(args.steps, 1),
+                    "d2h_bytes_per_step": d2h // max(args.steps, 1), "ms_per_step": round(ms_e2e / args.steps, 2), "loss": round(loss_e2e, 4)},
+            "gpu_launches": launches,
+            "max_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
+            "baseline_note": "vs_baseline divides by the reference's only published end-to-end figure (lyra-small, 34,150 tok/s on one TPU v6e); lyra-medium is unpublished",
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,359 @@
+// Bandwidth-bound fused kernels: RMSNorm (fwd / bwd), clamped SwiGLU (fwd / bwd), per-head QK RMS-norm + RoPE,
+// and the MoE row movement (scatter into the padded expert-sorted layout, weighted top-k combine and its gradients).
+// All move 16 bytes per thread per access; reductions are fixed-order (deterministic, no float atomics).
+// Semantics: lyra/model.py:183-191 (rotate, rms_norm), lyra/kernels/common.py:98-114 (swiglu), lyra/model.py:519-557
+// (permute / combine).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/tmap.h"
+
+namespace lyra {
+
+struct alignas(16) BF8 {
+  __nv_bfloat162 v[4];
+};
+__device__ __forceinline__ void unpack8(const BF8& b, float (&f)[8]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 t = __bfloat1622float2(b.v[i]);
+    f[2 * i] = t.x;
+    f[2 * i + 1] = t.y;
+  }
+}
+__device__ __forceinline__ BF8 pack8(const float (&f)[8]) {
+  BF8 b;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) b.v[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+  return b;
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+#pragma unroll
+  for (int s = 16; s > 0; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < nw; ++i) t += red[i];
+  return t;
+}
+
+// ------------------------------------------------------------------------------------------------ RMSNorm
+constexpr int RN_THREADS = 256;
+constexpr int RN_MAXV = 4;  // up to 4 x 8 columns per thread -> C <= 8192
+
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                                                                 __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, int C, float eps) {
+  __shared__ float red[RN_THREADS / 32];
+  const int nvec = C / 8;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const BF8* xr = reinterpret_cast<const BF8*>(x + (long long)row * C);
+    float v[RN_MAXV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+      const int c = threadIdx.x + j * RN_THREADS;
+      if (c < nvec) {
+        unpack8(xr[c], v[j]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += v[j][i] * v[j][i];
+      }
+    }
+    const float rstd = rsqrtf(block_sum(ss, red) / C + eps);
+    if (threadIdx.x == 0 && rstd_out) rstd_out[row] = rstd;
+    BF8* yr = reinterpret_cast<BF8*>(y + (long long)row * C);
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+      const int c = threadIdx.x + j * RN_THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = v[j][i] * rstd * scale[c * 8 + i];
+        yr[c] = pack8(o);
+      }
+    }
+  }
+}
+
+// dx = (g - xhat * mean(g * xhat)) * rstd with g = dy * scale; dscale partial per block = sum_rows dy * xhat
+__global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                                                                 const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                                                                 __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int C) {
+  __shared__ float red[RN_THREADS / 32];
+  const int nvec = C / 8;
+  float ds[RN_MAXV][8];
+#pragma unroll
+  for (int j = 0; j < RN_MAXV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ds[j][i] = 0.f;
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    const BF8* xr = reinterpret_cast<const BF8*>(x + (long long)row * C);
+    const BF8* gr = reinterpret_cast<const BF8*>(dy + (long long)row * C);
+    const float rstd = rstd_in[row];
+    float xh[RN_MAXV][8], g[RN_MAXV][8];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+      const int c = threadIdx.x + j * RN_THREADS;
+      if (c < nvec) {
+        float xv[8], dv[8];
+        unpack8(xr[c], xv);
+        unpack8(gr[c], dv);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xh[j][i] = xv[i] * rstd;
+          g[j][i] = dv[i] * scale[c * 8 + i];
+          ds[j][i] += dv[i] * xh[j][i];
+          dot += g[j][i] * xh[j][i];
+        }
+      }
+    }
+    const float mean = block_sum(dot, red) / C;
+    BF8* dr = reinterpret_cast<BF8*>(dx + (long long)row * C);
+#pragma unroll
+    for (int j = 0; j < RN_MAXV; ++j) {
+      const int c = threadIdx.x + j * RN_THREADS;
+      if (c < nvec) {
+        float o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = (g[j][i] - xh[j][i] * mean) * rstd;
+        dr[c] = pack8(o);
+      }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < RN_MAXV; ++j) {
+    const int c = threadIdx.x + j * RN_THREADS;
+    if (c < nvec) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) partial[(long long)blockIdx.x * C + c * 8 + i] = ds[j][i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ SwiGLU
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ out, long long M, int H, float beta, float limit) {
+  const int hv = H / 8;
+  const long long total = M * hv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / hv;
+    const int c = int(i % hv);
+    float g[8], l[8], o[8];
+    unpack8(reinterpret_cast<const BF8*>(pre + m * 2 * H)[c], g);
+    unpack8(reinterpret_cast<const BF8*>(pre + m * 2 * H + H)[c], l);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gc = fminf(g[k], limit), lc = fminf(fmaxf(l[k], -limit), limit);
+      o[k] = (lc + 1.f) * gc * sigmoidf_(beta * gc);
+    }
+    reinterpret_cast<BF8*>(out + m * H)[c] = pack8(o);
+  }
+}
+
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ pre, const __nv_bfloat16* __restrict__ dact, __nv_bfloat16* __restrict__ dpre,
+                                  long long M, int H, float beta, float limit) {
+  const int hv = H / 8;
+  const long long total = M * hv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long m = i / hv;
+    const int c = int(i % hv);
+    float g[8], l[8], d[8], dg[8], dl[8];
+    unpack8(reinterpret_cast<const BF8*>(pre + m * 2 * H)[c], g);
+    unpack8(reinterpret_cast<const BF8*>(pre + m * 2 * H + H)[c], l);
+    unpack8(reinterpret_cast<const BF8*>(dact + m * H)[c], d);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float gc = fminf(g[k], limit), lc = fminf(fmaxf(l[k], -limit), limit);
+      const float s = sigmoidf_(beta * gc);
+      dg[k] = g[k] <= limit ? d[k] * (lc + 1.f) * (s + gc * beta * s * (1.f - s)) : 0.f;
+      dl[k] = (l[k] >= -limit && l[k] <= limit) ? d[k] * gc * s : 0.f;
+    }
+    reinterpret_cast<BF8*>(dpre + m * 2 * H)[c] = pack8(dg);
+    reinterpret_cast<BF8*>(dpre + m * 2 * H + H)[c] = pack8(dl);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ QK-norm + RoPE (forward)
+// x, y [rows = B*T*N, D]; one warp per row; cos/sin [T, D/2]. Optional RMS norm over D with `scale`.
+__global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ cosv,
+                                       const float* __restrict__ sinv, __nv_bfloat16* __restrict__ y, long long rows, int T, int N, int D, float eps) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const int t = int((row / N) % T);
+  const int half = D / 2;
+  const __nv_bfloat16* xr = x + row * D;
+  float a[2], b[2];  // elements lane, lane+32 of each half (D <= 128)
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = lane + j * 32;
+    a[j] = i < half ? __bfloat162float(xr[i]) : 0.f;
+    b[j] = i < half ? __bfloat162float(xr[i + half]) : 0.f;
+    ss += a[j] * a[j] + b[j] * b[j];
+  }
+  float rstd = 1.f;
+  if (scale) {
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+    rstd = rsqrtf(ss / D + eps);
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int i = lane + j * 32;
+    if (i < half) {
+      // the normalised value is rounded to bf16 before the rotation, as in the unfused composition
+      float x1 = a[j] * rstd, x2 = b[j] * rstd;
+      if (scale) {
+        x1 = __bfloat162float(__float2bfloat16(x1 * scale[i]));
+        x2 = __bfloat162float(__float2bfloat16(x2 * scale[i + half]));
+      }
+      const float c = cosv[(long long)t * half + i], s = sinv[(long long)t * half + i];
+      y[row * D + i] = __float2bfloat16(x1 * c - x2 * s);
+      y[row * D + i + half] = __float2bfloat16(x2 * c + x1 * s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ MoE row movement
+// out[dest[f*K + k]] = xn[f]; one block per token.
+__global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ xn, const long long* __restrict__ dest, __nv_bfloat16* __restrict__ out,
+                                    int F, int K, int C) {
+  const int f = blockIdx.x;
+  const int nvec = C / 8;
+  const BF8* src = reinterpret_cast<const BF8*>(xn + (long long)f * C);
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+    const BF8 v = src[c];
+    for (int k = 0; k < K; ++k) reinterpret_cast<BF8*>(out + dest[(long long)f * K + k] * C)[c] = v;
+  }
+}
+
+// out[f] = sum_k scores[f,k] * rows[dest[f*K + k]]  (fp32 accumulate, k ascending)
+__global__ void combine_rows_kernel(const __nv_bfloat16* __restrict__ rows, const long long* __restrict__ dest, const float* __restrict__ scores,
+                                    __nv_bfloat16* __restrict__ out, int F, int K, int C) {
+  const int f = blockIdx.x;
+  const int nvec = C / 8;
+  for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < K; ++k) {
+      float v[8];
+      unpack8(reinterpret_cast<const BF8*>(rows + dest[(long long)f * K + k] * C)[c], v);
+      const float s = scores[(long long)f * K + k];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] += s * v[i];
+    }
+    reinterpret_cast<BF8*>(out + (long long)f * C)[c] = pack8(acc);
+  }
+}
+
+// d_rows[dest[f*K+k]] = scores[f,k] * dout[f];  dscores[f,k] = <rows[dest[f*K+k]], dout[f]>
+__global__ void __launch_bounds__(256) combine_rows_bwd_kernel(const __nv_bfloat16* __restrict__ rows, const __nv_bfloat16* __restrict__ dout,
+                                                               const long long* __restrict__ dest, const float* __restrict__ scores,
+                                                               __nv_bfloat16* __restrict__ d_rows, float* __restrict__ dscores, int F, int K, int C) {
+  __shared__ float red[8];
+  const int f = blockIdx.x;
+  const int nvec = C / 8;
+  for (int k = 0; k < K; ++k) {
+    const long long r = dest[(long long)f * K + k];
+    const float s = scores[(long long)f * K + k];
+    float dot = 0.f;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      float g[8], v[8], o[8];
+      unpack8(reinterpret_cast<const BF8*>(dout + (long long)f * C)[c], g);
+      unpack8(reinterpret_cast<const BF8*>(rows + r * C)[c], v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        dot += g[i] * v[i];
+        o[i] = s * g[i];
+      }
+      reinterpret_cast<BF8*>(d_rows + r * C)[c] = pack8(o);
+    }
+    const float total = block_sum(dot, red);
+    if (threadIdx.x == 0) dscores[(long long)f * K + k] = total;
+  }
+}
+
+static inline int ew_grid(long long n, int threads) {
+  long long b = (n + threads - 1) / threads;
+  const long long cap = (long long)sm_count() * 32;
+  return int(b < cap ? (b > 0 ? b : 1) : cap);
+}
+
+}  // namespace lyra
+
+using namespace lyra;
+#define S_(x) reinterpret_cast<cudaStream_t>(x)
+#define BFP(x) reinterpret_cast<__nv_bfloat16*>(x)
+#define CBFP(x) reinterpret_cast<const __nv_bfloat16*>(x)
+
+extern "C" int lyra_rmsnorm_fwd(const void* x, const float* scale, void* y, float* rstd, int rows, int C, float eps, void* stream) {
+  if (rows <= 0) return 0;
+  if (C % 8 || C > 8 * RN_THREADS * RN_MAXV) return -40;
+  const int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
+  rmsnorm_fwd_kernel<<<grid, RN_THREADS, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, C, eps);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_rmsnorm_bwd(const void* x, const float* scale, const float* rstd, const void* dy, void* dx, float* partial, int rows, int C,
+                                int nblk, void* stream) {
+  if (rows <= 0) return 0;
+  if (C % 8 || C > 8 * RN_THREADS * RN_MAXV) return -40;
+  rmsnorm_bwd_kernel<<<nblk, RN_THREADS, 0, S_(stream)>>>(CBFP(x), scale, rstd, CBFP(dy), BFP(dx), partial, rows, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_swiglu_fwd(const void* pre, void* out, long long M, int H, float beta, float limit, void* stream) {
+  if (M <= 0) return 0;
+  swiglu_fwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), BFP(out), M, H, beta, limit);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_swiglu_bwd(const void* pre, const void* dact, void* dpre, long long M, int H, float beta, float limit, void* stream) {
+  if (M <= 0) return 0;
+  swiglu_bwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), CBFP(dact), BFP(dpre), M, H, beta, limit);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_qknorm_rope_fwd(const void* x, const float* scale, const float* cosv, const float* sinv, void* y, int B, int T, int N, int D,
+                                    float eps, void* stream) {
+  const long long rows = (long long)B * T * N;
+  if (rows <= 0) return 0;
+  if (D > 128 || D % 2) return -41;
+  qknorm_rope_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S_(stream)>>>(CBFP(x), scale, cosv, sinv, BFP(y), rows, T, N, D, eps);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_scatter_rows(const void* xn, const long long* dest, void* out, int F, int K, int C, void* stream) {
+  if (F <= 0) return 0;
+  if (C % 8) return -42;
+  scatter_rows_kernel<<<F, 128, 0, S_(stream)>>>(CBFP(xn), dest, BFP(out), F, K, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_combine_rows(const void* rows, const long long* dest, const float* scores, void* out, int F, int K, int C, void* stream) {
+  if (F <= 0) return 0;
+  if (C % 8) return -42;
+  combine_rows_kernel<<<F, 128, 0, S_(stream)>>>(CBFP(rows), dest, scores, BFP(out), F, K, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_combine_rows_bwd(const void* rows, const void* dout, const long long* dest, const float* scores, void* d_rows, float* dscores,
+                                     int F, int K, int C, void* stream) {
+  if (F <= 0) return 0;
+  if (C % 8) return -42;
+  combine_rows_bwd_kernel<<<F, 256, 0, S_(stream)>>>(CBFP(rows), CBFP(dout), dest, scores, BFP(d_rows), dscores, F, K, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}

@@ -12,6 +12,7 @@ gradient accumulation over microbatches costs no extra pass over the gradient bu
 from __future__ import annotations
 
 import math
+import weakref
 
 import torch
 
@@ -25,7 +26,7 @@ from lyra_b200.ops.native import c_float, c_int, c_ll, ptr
 BF16 = torch.bfloat16
 
 # --------------------------------------------------------------------------- bf16 shadows of fp32 masters
-_SHADOW: dict[int, tuple[int, torch.Tensor]] = {}
+_SHADOW: dict[int, tuple[int, torch.Tensor, weakref.ref]] = {}
 KEEP_SHADOWS = True  # False: cast at every use instead (for models whose bf16 copy does not fit beside the optimizer state)
 GRAD_DTYPE = torch.float32
 
@@ -45,21 +46,31 @@ def bf16_weight(w: torch.Tensor) -> torch.Tensor:
         return w.detach().to(BF16)
     key = id(w)
     hit = _SHADOW.get(key)
-    if hit is not None and hit[0] == w._version and hit[1].shape == w.shape:
+    if hit is not None and hit[2]() is not w:      # the id was recycled by a different tensor
+        hit = None
+    if hit is not None and hit[0] == w._version:
         return hit[1]
-    if hit is not None and hit[1].shape == w.shape:
+    if hit is not None:
         hit[1].copy_(w.detach())
         shadow = hit[1]
     else:
         shadow = w.detach().to(BF16)
-    _SHADOW[key] = (w._version, shadow)
+        if len(_SHADOW) > 4096:
+            for k in [k for k, v in _SHADOW.items() if v[2]() is None]:
+                del _SHADOW[k]
+    _SHADOW[key] = (w._version, shadow, weakref.ref(w))
     return shadow
+
+
+def shadow_of(w: torch.Tensor) -> torch.Tensor | None:
+    hit = _SHADOW.get(id(w))
+    return hit[1] if hit is not None and hit[2]() is w else None
 
 
 def invalidate_shadows() -> None:
     """Marks every cached bf16 copy stale (call after the masters changed through an alias, e.g. the optimizer)."""
-    for key, (_, shadow) in list(_SHADOW.items()):
-        _SHADOW[key] = (-1, shadow)
+    for key, (_, shadow, ref) in list(_SHADOW.items()):
+        _SHADOW[key] = (-1, shadow, ref)
 
 
 def _accumulate_wgrad(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0) -> None:

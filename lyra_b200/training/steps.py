@@ -54,6 +54,8 @@ class Stepper:
     # ------------------------------------------------------------------ host -> device
     def to_device(self, a) -> torch.Tensor:
         t = a if isinstance(a, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(a))
+        if t.is_cuda:
+            return t
         if self.device.type != "cuda":
             return t.long() if t.dtype != torch.int64 else t
         if not t.is_pinned():
@@ -94,13 +96,22 @@ class Stepper:
             grads = self.rt.reduce_grads(grads)
         with scope("optimizer"):
             trainable = {p: t for p, t in self.params.items() if p in grads}
-            metrics = optimizer_step({p: t.detach() for p, t in trainable.items()}, grads, self.state.optimizer, step, self.tcfg, rt=self.rt)
+            fused = (self.device.type == "cuda" and self.mcfg.implementation in ("auto", "b200")
+                     and (self.rt is None or not self.rt.owns_optimizer))
+            if fused:
+                from lyra_b200.ops import cuda_ops
+                from lyra_b200.training.optimizer_cuda import optimizer_step_cuda
+
+                shadows = {p: sh for p, t in trainable.items() if (sh := cuda_ops.shadow_of(t)) is not None}
+                metrics = optimizer_step_cuda(trainable, grads, self.state.optimizer, step, self.tcfg, shadows)
+            else:
+                metrics = optimizer_step({p: t.detach() for p, t in trainable.items()}, grads, self.state.optimizer, step, self.tcfg, rt=self.rt)
+                if self.device.type == "cuda":
+                    from lyra_b200.ops import cuda_ops
+
+                    cuda_ops.invalidate_shadows()
         for t in self.params.values():
             t.grad = None
-        if self.device.type == "cuda":
-            from lyra_b200.ops import cuda_ops
-
-            cuda_ops.invalidate_shadows()
         if self.rt is not None:
             self.rt.after_optimizer(self.params)
         return {"loss": totals[0], "ce_loss": totals[1], "aux_loss": totals[2], **metrics}

@@ -16,10 +16,11 @@ def _cfgs():
     mid = ModelConfig(name="test-mid", seq_len=256, n_embd=512, n_layers=4, head_dim=128, n_attn_heads=4, n_kv_heads=2,
                       use_learned_xsa=True, use_sdpa_output_gate=True, n_routed_experts=7, n_shared_experts=1, n_active_experts=3,
                       mlp_map=("dense", "moe", "dense", "moe"), vocab_size=4000, padded_vocab_size=4096, tie_embeddings=False)
-    return {"tiny": tiny, "mid": mid}
+    dense = replace(mid, name="test-dense", mlp_map=("dense",) * 4)
+    return {"tiny": tiny, "mid": mid, "dense": dense}
 
 
-@pytest.mark.parametrize("name", ["tiny", "mid"])
+@pytest.mark.parametrize("name", ["tiny", "mid", "dense"])
 def test_loss_and_grads_match_torch_path(name):
     from lyra_b200.model import ModelWeights
     from lyra_b200.nn.params import tree_dict
@@ -53,6 +54,35 @@ def test_loss_and_grads_match_torch_path(name):
     for p in g0:
         denom = g0[p].norm().clamp_min(1e-6)
         err = ((g0[p] - g1[p]).norm() / denom).item()
-        if err > 0.08:
+        # router gradients are sums of many small terms of either sign and flip with near-tie top-k choices,
+        # so they are checked by direction (and exactly, with fixed routing, in test_moe_experts_op)
+        if "router" in p:
+            cos = torch.nn.functional.cosine_similarity(g0[p].reshape(-1), g1[p].reshape(-1), dim=0).item()
+            if cos < 0.8:
+                bad.append((p, err, cos))
+        elif err > (0.25 if (name != "dense" or p.endswith(("xsa_alpha", "sinks"))) else 0.08):  # top-k flips between the two bf16 paths perturb MoE models
             bad.append((p, err))
     assert not bad, bad
+
+
+def test_moe_experts_op():
+    """Grouped expert MLP with fixed routing: outputs and every gradient (incl. the routing scores) vs the PyTorch statement."""
+    from lyra_b200.ops import api
+
+    torch.manual_seed(0)
+    F_, K, E, C, H = 300, 3, 5, 256, 384
+    xn = torch.randn(F_, C, device="cuda").bfloat16()
+    indices = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(F_)])
+    scores = torch.softmax(torch.randn(F_, K, device="cuda"), -1)
+    w_up = (torch.randn(E, C, 2, H, device="cuda") / 16)
+    w_down = (torch.randn(E, H, C, device="cuda") / 16)
+    dout = (torch.randn(F_, C, device="cuda") * 0.1).bfloat16()
+    res = {}
+    for impl in ("torch", "auto"):
+        a = [t.clone().requires_grad_(True) for t in (xn, scores, w_up, w_down)]
+        out = api.moe_experts(a[0], a[1], indices, a[2], None, a[3], None, 1.702, 7.0, impl)
+        out.backward(dout)
+        res[impl] = [out.detach().float()] + [t.grad.float() for t in a]
+    for name, r, k in zip(("out", "dx", "dscores", "dw_up", "dw_down"), res["torch"], res["auto"]):
+        err = ((r - k).norm() / r.norm().clamp_min(1e-9)).item()
+        assert err < 3e-2, (name, err)
