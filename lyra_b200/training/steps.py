@@ -46,6 +46,10 @@ class Stepper:
         for p in self.params.values():
             if p.is_floating_point():
                 p.requires_grad_(True)
+                try:  # gradients may be kept in bf16 when fp32 ones do not fit (torch >= 2.9 checks the dtype)
+                    p.grad_dtype = None
+                except Exception:
+                    pass
         self.world = rt.data_size if rt is not None else 1
         self.copy_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0

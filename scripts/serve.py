@@ -1,0 +1,56 @@
+"""Chat with a checkpoint (own Orbax-layout checkpoints or GPT-OSS ``original/`` checkpoints)."""
+
+from __future__ import annotations
+
+import sys
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Literal
+
+import tyro
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+
+@dataclass(frozen=True)
+class Args:
+    variant: str = "lyra-small"
+    """Model variant."""
+    weights: str | None = None
+    """Checkpoint path; defaults to chkpt/<variant>."""
+    format: Literal["orbax", "gpt-oss"] = "orbax"
+    """Checkpoint format."""
+    device: Literal["auto", "cpu", "gpu"] = "auto"
+    """Device."""
+    max_new_tokens: int = 256
+    """Tokens to generate per turn."""
+    max_cache_length: int | None = None
+    """Prompt plus generation length; defaults to the model's context length."""
+    temperature: float | None = None
+    """Sampling temperature; defaults to the variant's."""
+    top_k: int | None = None
+    """Top-k sampling; defaults to the variant's."""
+    fp8: bool = False
+    """Store MLP weights and the KV cache in block-scaled FP8."""
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = tyro.cli(Args, args=argv)
+    import torch
+
+    from lyra_b200.generate import InferenceConfig, apply_inference_overrides, load_model, serve_model
+    from lyra_b200.gpt_oss import load_gpt_oss_model
+    from lyra_b200.variants import model_variant
+
+    device = "cuda" if (args.device == "gpu" or (args.device == "auto" and torch.cuda.is_available())) else "cpu"
+    icfg = InferenceConfig(weights=args.weights or str(ROOT / "chkpt" / args.variant), max_new_tokens=args.max_new_tokens,
+                           max_cache_length=args.max_cache_length, temperature=args.temperature, top_k=args.top_k, fp8=args.fp8)
+    mcfg = apply_inference_overrides(model_variant(args.variant), icfg)
+    model = load_gpt_oss_model(icfg.weights, mcfg, device=device) if args.format == "gpt-oss" else load_model(mcfg, icfg, device=device)
+    serve_model(model, mcfg, icfg, harmony=args.format == "gpt-oss", device=device)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
