@@ -1,0 +1,19 @@
+"""Shared small configurations for CPU tests."""
+
+from dataclasses import replace
+
+import numpy as np
+
+from lyra_b200.variants import model_variant
+
+
+def small_config(**kw):
+    """The ``dev`` variant with a small vocabulary so CPU steps take milliseconds."""
+    base = replace(model_variant("dev"), seq_len=32, vocab_size=500, padded_vocab_size=512, n_layers=4,
+                   mlp_map=("dense", "moe", "dense", "moe"), implementation="torch")
+    return replace(base, **kw)
+
+
+def token_file(path, n=6000, vocab=500, seed=0):
+    np.save(path, np.random.default_rng(seed).integers(0, vocab, size=n).astype("<i4"))
+    return path

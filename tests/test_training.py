@@ -1,0 +1,158 @@
+"""Train loop, checkpoints, resume, schedule, optimizer (CPU)."""
+
+import json
+from dataclasses import replace
+
+import numpy as np
+import pytest
+import torch
+
+from lyra_b200.data import DataLoaderConfig
+from lyra_b200.model import ModelWeights
+from lyra_b200.nn.checkpoints import checkpoint_run_config, checkpoint_steps, resolve_checkpoint
+from lyra_b200.nn.params import tree_dict
+from lyra_b200.training.optimizer import OptimizerState, newtonschulz, optimizer_step, wsd_lr
+from lyra_b200.training.presets import TRAINING_PRESETS
+from lyra_b200.training.state import init_train_state, load_train_state, save_checkpoint
+from lyra_b200.training.train import TrainHooks, TrainingConfig, train
+from tests.helpers import small_config, token_file
+
+
+def _tcfg(tmp_path, **kw):
+    base = dict(steps=6, batch_size=2, accumulation_steps=1, data_path=token_file(tmp_path / "tok.npy"), eval_data_path=tmp_path / "tok.npy",
+                eval_every=3, eval_batches=1, checkpoint_every=3, checkpoint_path=tmp_path / "run", log_every=1, numerics_every=3,
+                data_loader=DataLoaderConfig(worker_count=1))
+    base.update(kw)
+    return TrainingConfig(**base)
+
+
+def _scales(config):
+    return [wsd_lr(s, config)[2] for s in range(config.steps)]
+
+
+def test_default_schedule_warms_up_then_cosine_decays():
+    config = replace(TRAINING_PRESETS["train-dev"], steps=48)
+    s = _scales(config)
+    assert (config.warmup_steps, config.stable_steps, config.decay_steps) == (2, 0, 46)
+    assert np.allclose(s[:3], [0.5, 1.0, 1.0]) and s[3] < 1.0 and abs(s[-1]) < 1e-6
+    assert all(b <= a for a, b in zip(s[1:], s[2:]))
+    assert replace(config, steps=954).warmup_steps == 29
+
+
+def test_linear_wsd_schedule_from_cli():
+    from scripts.train import Args, training_config
+
+    config = training_config(Args(run="train-dev", steps=20, warmup_fraction=0.1, stable_fraction=0.8, decay_type="linear"))
+    assert (config.warmup_steps, config.stable_steps, config.decay_steps) == (2, 16, 2)
+    assert np.allclose(_scales(config), [0.5] + [1.0] * 18 + [0.0])
+    one = replace(TRAINING_PRESETS["train-dev"], steps=1)
+    assert np.isclose(wsd_lr(0, one)[2], 1.0) and np.isclose(wsd_lr(0, one)[0], one.adam_max_lr)
+
+
+def test_cli_paths_expand_home_and_presets_save_where_serve_looks():
+    from pathlib import Path
+
+    from scripts.train import ROOT, Args, training_config
+
+    config = training_config(Args(data="~/data", eval_data="~/val", out="~/checkpoints", resume="~/previous"))
+    assert [str(p) for p in (config.data_path, config.eval_data_path, config.checkpoint_path, config.resume_from)] == [
+        str(Path.home() / n) for n in ("data", "val", "checkpoints", "previous")]
+    for variant in ("lyra-small", "lyra-medium", "lyra-large", "lyra-max"):
+        assert training_config(Args(variant=variant)).checkpoint_path == ROOT / "chkpt" / variant
+
+
+def test_newton_schulz_orthogonalises():
+    torch.manual_seed(0)
+    for shape in ((24, 64), (64, 24)):
+        o = newtonschulz(torch.randn(*shape)).float()
+        s = torch.linalg.svdvals(o)
+        assert s.max() < 1.6 and s.min() > 0.3
+
+
+def test_non_finite_gradient_skips_the_step():
+    c = small_config()
+    tcfg = TrainingConfig(steps=4, batch_size=2, accumulation_steps=1)
+    w = ModelWeights.init(0, c)
+    params = tree_dict(w)
+    state = OptimizerState.init(w, ModelWeights.spec(c), tcfg)
+    grads = {p: torch.randn_like(t) * 0.01 for p, t in params.items()}
+    optimizer_step(params, grads, state, 0, tcfg)
+    before = {p: t.clone() for p, t in params.items()}
+    mom = {p: t.clone() for p, t in state.muon_moment.items()}
+    grads["tok/emb"][0, 0] = float("inf")
+    m = optimizer_step(params, grads, state, 1, tcfg)
+    assert not bool(m["grad_is_finite"]) and int(state.adam_count) == 1
+    assert all(torch.equal(before[p], params[p]) for p in params)
+    assert all(torch.equal(mom[p], state.muon_moment[p]) for p in mom)
+
+
+def test_checkpoint_round_trip_and_variant_mismatch(tmp_path):
+    c = small_config()
+    tcfg = TrainingConfig(steps=4, batch_size=2, accumulation_steps=1)
+    state = init_train_state(ModelWeights.init(0, c), c, tcfg)
+    for t in state.optimizer.muon_moment.values():
+        t.copy_(torch.randn(t.shape).to(t.dtype))
+    state.optimizer.adam_count += 3
+    save_checkpoint(tmp_path, 7, state, b'{"position": 5}', {"resume_signature": {}}, keep=2)
+    restored = load_train_state(tmp_path, c, tcfg)
+    assert restored.step == 7 and restored.loader_state == b'{"position": 5}'
+    a, b = tree_dict(state.params), tree_dict(restored.state.params)
+    assert a.keys() == b.keys() and all(torch.equal(a[k], b[k]) and a[k].dtype == b[k].dtype for k in a)
+    for name in ("muon_moment", "adam_mu", "adam_nu"):
+        x, y = getattr(state.optimizer, name), getattr(restored.state.optimizer, name)
+        assert x.keys() == y.keys() and all(torch.equal(x[k], y[k]) for k in x)
+    assert int(restored.state.optimizer.adam_count) == 3
+    with pytest.raises(ValueError, match="does not match the model config"):
+        load_train_state(tmp_path, replace(c, use_sdpa_output_gate=True), tcfg)
+
+
+def test_resolve_checkpoint_ignores_incomplete_directories(tmp_path):
+    (tmp_path / "step_00000002").mkdir()
+    (tmp_path / "step_00000002" / "_CHECKPOINT_METADATA").write_text("{}")
+    (tmp_path / "step_00000005").mkdir()                                        # no metadata: unfinished
+    (tmp_path / "step_00000009.orbax-checkpoint-tmp-0").mkdir()
+    (tmp_path / "step_00000009.orbax-checkpoint-tmp-0" / "_CHECKPOINT_METADATA").write_text("{}")
+    assert [p.name for p in checkpoint_steps(tmp_path)] == ["step_00000002"]
+    assert resolve_checkpoint(tmp_path).name == "step_00000002"
+    with pytest.raises(FileNotFoundError):
+        resolve_checkpoint(tmp_path / "nothing")
+
+
+def test_train_refuses_a_directory_with_checkpoints_and_rejects_changed_settings(tmp_path):
+    c = small_config()
+    tcfg = _tcfg(tmp_path, steps=3, eval_data_path=None, numerics_every=None)
+    train(ModelWeights.init(0, c), c, tcfg, device="cpu")
+    with pytest.raises(FileExistsError):
+        train(ModelWeights.init(0, c), c, tcfg, device="cpu")
+    with pytest.raises(ValueError, match="training settings differ"):
+        train(None, c, replace(tcfg, resume_from=tmp_path / "run", muon_max_lr=1.0), device="cpu")
+    with pytest.raises(ValueError, match="model settings differ"):
+        train(None, replace(c, swiglu_limit=3.0), replace(tcfg, resume_from=tmp_path / "run"), device="cpu")
+
+
+def test_interrupted_run_resumes_bit_exactly(tmp_path):
+    c = small_config()
+    full = train(ModelWeights.init(0, c), c, _tcfg(tmp_path), device="cpu")
+
+    class Boom(TrainHooks):
+        def before_step(self, step, *a):
+            if step == 4:
+                raise RuntimeError("interrupted")
+
+    tcfg = _tcfg(tmp_path, checkpoint_path=tmp_path / "run2")
+    with pytest.raises(RuntimeError, match="interrupted"):
+        train(ModelWeights.init(0, c), c, tcfg, device="cpu", hooks=Boom())
+    resumed = train(None, c, replace(tcfg, resume_from=tmp_path / "run2"), device="cpu")
+    a, b = tree_dict(full.params), tree_dict(resumed.params)
+    assert all(torch.equal(a[k], b[k]) for k in a)
+    for name in ("muon_moment", "adam_mu", "adam_nu"):
+        x, y = getattr(full.optimizer, name), getattr(resumed.optimizer, name)
+        assert all(torch.equal(x[k], y[k]) for k in x)
+    rows = [json.loads(l) for l in (tmp_path / "run2" / "metrics.jsonl").read_text().splitlines()]
+    assert [r["step"] for r in rows if r["kind"] == "train"] == [1, 2, 3, 4, 5, 6]
+    assert [r["step"] for r in rows if r["kind"] == "eval"] == [0, 3, 6]
+    meta = checkpoint_run_config(resolve_checkpoint(tmp_path / "run2"))
+    assert set(meta["run_artifacts"]) >= {"metrics.jsonl", "numerics.jsonl"}
+    assert (tmp_path / "run2" / "metrics.png").exists() and (tmp_path / "run2" / "config.json").exists()
+    numerics = [json.loads(l) for l in (tmp_path / "run2" / "numerics.jsonl").read_text().splitlines()]
+    assert any("load_max_ratio" in s for s in numerics[0]["records"].values())
