@@ -139,19 +139,18 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    rt = None
-    if world > 1:
-        from lyra_b200.parallel.runtime import Runtime
-
-        dist.init_process_group("nccl", device_id=device)
-        rt = Runtime.create(world_size=world, rank=rank, device=device, implementation="nccl" if args.impl == "nccl" else "b200")
-
     impl = {"b200": "auto", "torch": "torch", "nccl": "nccl"}[args.impl]
     mcfg = replace(model_variant(args.variant), implementation=impl)
     valid = True
     if args.layers is not None:
         mcfg = replace(mcfg, n_layers=args.layers, mlp_map=mcfg.mlp_map[: args.layers])
         valid = False
+    rt = None
+    if world > 1:
+        from lyra_b200.parallel.runtime import Runtime
+
+        dist.init_process_group("nccl", device_id=device)
+        rt = Runtime.create(world_size=world, rank=rank, device=device, implementation="nccl" if args.impl in ("nccl", "torch") else "b200", mcfg=mcfg)
     preset = TRAINING_PRESETS.get("train-" + args.variant.removeprefix("lyra-"))
     acc = args.accumulation or (preset.accumulation_steps if preset else 1)
     B, T = args.micro_batch, mcfg.seq_len

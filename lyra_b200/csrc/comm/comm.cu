@@ -1,0 +1,310 @@
+// NVLink / NVSwitch data movement between the GPUs of one node through peer-mapped (symmetric) memory.
+// Every kernel takes raw peer pointers and uses plain 16-byte loads / stores plus system-scope release / acquire
+// flags: no collective library call, no multicast, and nothing that can wait forever - every wait spins for a
+// bounded time, then records STATUS_TIMEOUT_PEER in a status word and returns.
+//
+//   p2p_copy      : pull a buffer from one peer (parameter broadcast from its owner = the all-gather leg of ZeRO-3)
+//   reduce_pull   : out = sum over ranks of peer[r][...] in rank order (gradient reduce to the owning rank; deterministic)
+//   signal / wait : epoch flags (a stream-ordered barrier across ranks)
+//   ep_*          : expert-parallel token exchange - counts push, layout, row dispatch into the owner's expert-sorted
+//                   receive buffer, and the return of expert outputs to the source rank's combine buffer
+//                   (roles of lyra/kernels/ep_moe.py:9-37,94-127 in the reference)
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../common/tmap.h"
+
+namespace lyra {
+
+constexpr int MAX_RANKS = 16;
+constexpr long long PEER_WAIT_NS = 2000000000LL;  // 2 s
+constexpr int STATUS_PEER_TIMEOUT = 4;
+constexpr int STATUS_EP_OVERFLOW = 6;
+
+struct PeerPtrs {
+  void* p[MAX_RANKS];
+};
+
+__device__ __forceinline__ void st_release_sys(int* addr, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* addr) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ long long now_ns() {
+  long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+// Spins until *flag >= value or the time limit passes. Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(const int* flag, int value) {
+  const long long start = now_ns();
+  while (ld_acquire_sys(flag) < value) {
+    if (now_ns() - start > PEER_WAIT_NS) return false;
+    __nanosleep(200);
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------ copies / reductions
+__global__ void p2p_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long n16) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+}
+
+// fp32 or bf16 inputs on every rank, fp32 (or bf16) output; 8 elements per thread per step.
+template <bool IN_BF16, bool OUT_BF16>
+__global__ void reduce_pull_kernel(void* __restrict__ out, PeerPtrs peers, int world, long long n) {
+  const long long n8 = n / 8;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      if (IN_BF16) {
+        const uint4 v = reinterpret_cast<const uint4*>(peers.p[r])[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(h[k]);
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      } else {
+        const float4 a = reinterpret_cast<const float4*>(peers.p[r])[2 * i], b = reinterpret_cast<const float4*>(peers.p[r])[2 * i + 1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+    }
+    if (OUT_BF16) {
+      uint4 o;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      reinterpret_cast<uint4*>(out)[i] = o;
+    } else {
+      reinterpret_cast<float4*>(out)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ flags
+// Thread r writes `value` into slot [my_rank] of rank r's flag array (after all earlier writes of this stream).
+__global__ void signal_kernel(PeerPtrs flag_arrays, int world, int my_rank, int value) {
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flag_arrays.p[r]) + my_rank, value);
+  }
+}
+// Thread r waits until slot [r] of the local flag array reaches `value`.
+__global__ void wait_kernel(const int* __restrict__ flags, int world, int value, int* status) {
+  const int r = threadIdx.x;
+  if (r < world && !wait_flag(flags + r, value)) atomicExch(status, STATUS_PEER_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------------ expert-parallel exchange
+// Writes this rank's per-expert counts into row [my_rank] of every rank's counts matrix, then raises its flag there.
+__global__ void ep_counts_push_kernel(const int* __restrict__ my_counts, PeerPtrs counts_mats, PeerPtrs flag_arrays, int world, int my_rank,
+                                      int n_experts, int epoch) {
+  const int r = blockIdx.x;  // destination rank
+  int* dst = reinterpret_cast<int*>(counts_mats.p[r]) + (long long)my_rank * n_experts;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) dst[e] = my_counts[e];
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) st_release_sys(reinterpret_cast<int*>(flag_arrays.p[r]) + my_rank, epoch);
+}
+
+// One block. From counts[world][E] (all ranks' routed counts):
+//   send_base[e]   : row in the owner's receive buffer where this rank's rows of expert e start
+//   recv_offsets   : [E_local + 1] padded (x128) row offsets of this rank's local experts
+//   tile_group     : [cap_rows / 128] local expert of each 128-row tile, -1 beyond the used rows
+// Receive layout is expert-major, then source-rank-major (lyra/kernels/ep_moe.py:9-37), each expert padded to 128 rows.
+__global__ void ep_layout_kernel(const int* __restrict__ counts, int world, int my_rank, int n_experts, int e_local, int cap_rows,
+                                 int* __restrict__ send_base, int* __restrict__ recv_offsets, int* __restrict__ tile_group,
+                                 int* __restrict__ recv_total, int* status) {
+  extern __shared__ int sh[];  // per-expert totals [E], padded bases [E]
+  int* total = sh;
+  int* base = sh + n_experts;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int t = 0;
+    for (int s = 0; s < world; ++s) t += counts[s * n_experts + e];
+    total[e] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int d = 0; d < world; ++d) {
+      int off = 0;
+      for (int j = 0; j < e_local; ++j) {
+        const int e = d * e_local + j;
+        base[e] = off;
+        if (d == my_rank) recv_offsets[j] = off;
+        off += (total[e] + 127) / 128 * 128;
+      }
+      if (off > cap_rows) atomicExch(status, STATUS_EP_OVERFLOW);
+      if (d == my_rank) {
+        recv_offsets[e_local] = off;
+        *recv_total = off;
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int before = 0;
+    for (int s = 0; s < my_rank; ++s) before += counts[s * n_experts + e];
+    send_base[e] = base[e] + before;
+  }
+  const int used = recv_offsets[e_local] < cap_rows ? recv_offsets[e_local] : cap_rows;
+  for (int t = threadIdx.x; t < cap_rows / 128; t += blockDim.x) {
+    const int row = t * 128;
+    int g = -1;
+    if (row < used) {
+      for (int j = 0; j < e_local; ++j)
+        if (row >= recv_offsets[j] && row < recv_offsets[j + 1]) g = j;
+    }
+    tile_group[t] = g;
+  }
+}
+
+// One block per assignment a = f * K + k: copies the source row into the owner's receive buffer and records (rank, a).
+// `src_div` = K when the source rows are tokens (forward: row a / K), 1 when they are per-assignment rows (backward).
+__global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ expert_of, const int* __restrict__ rank_in_expert,
+                                   const int* __restrict__ send_base, PeerPtrs recv_bufs, PeerPtrs recv_meta, int my_rank, int e_local, int cap_rows,
+                                   int n_assign, int src_div, int C) {
+  const int a = blockIdx.x;
+  if (a >= n_assign) return;
+  const int e = expert_of[a];
+  const int d = e / e_local;
+  const int row = send_base[e] + rank_in_expert[a];
+  if (row >= cap_rows) return;  // overflow was flagged by the layout kernel
+  const uint4* s = reinterpret_cast<const uint4*>(src + (long long)(a / src_div) * C);
+  uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recv_bufs.p[d]) + (long long)row * C);
+  for (int c = threadIdx.x; c < C / 8; c += blockDim.x) o[c] = s[c];
+  if (threadIdx.x == 0 && recv_meta.p[d]) reinterpret_cast<int*>(recv_meta.p[d])[row] = (my_rank << 24) | a;
+}
+
+// One block per received row: sends the row back to slot a of the source rank's return buffer.
+__global__ void ep_return_kernel(const __nv_bfloat16* __restrict__ rows, const int* __restrict__ meta, const int* __restrict__ recv_offsets,
+                                 const int* __restrict__ counts, int world, int my_rank, int n_experts, int e_local, PeerPtrs ret_bufs, int C) {
+  const int row = blockIdx.x;
+  if (row >= recv_offsets[e_local]) return;
+  // is the row a real one (not expert padding)?
+  int j = 0;
+  while (j + 1 < e_local && row >= recv_offsets[j + 1]) ++j;
+  int valid = 0;
+  for (int s = 0; s < world; ++s) valid += counts[s * n_experts + my_rank * e_local + j];
+  if (row - recv_offsets[j] >= valid) return;
+  const int m = meta[row];
+  const int src_rank = m >> 24, a = m & 0xFFFFFF;
+  const uint4* s = reinterpret_cast<const uint4*>(rows + (long long)row * C);
+  uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(ret_bufs.p[src_rank]) + (long long)a * C);
+  for (int c = threadIdx.x; c < C / 8; c += blockDim.x) o[c] = s[c];
+}
+
+// Zeroes the padding rows of the receive buffer (rows of an expert beyond its real count), so they contribute nothing to dW.
+__global__ void ep_zero_pad_kernel(__nv_bfloat16* __restrict__ rows, const int* __restrict__ recv_offsets, const int* __restrict__ counts, int world,
+                                   int my_rank, int n_experts, int e_local, int C) {
+  const int row = blockIdx.x;
+  if (row >= recv_offsets[e_local]) return;
+  int j = 0;
+  while (j + 1 < e_local && row >= recv_offsets[j + 1]) ++j;
+  int valid = 0;
+  for (int s = 0; s < world; ++s) valid += counts[s * n_experts + my_rank * e_local + j];
+  if (row - recv_offsets[j] < valid) return;
+  uint4* o = reinterpret_cast<uint4*>(rows + (long long)row * C);
+  for (int c = threadIdx.x; c < C / 8; c += blockDim.x) o[c] = make_uint4(0, 0, 0, 0);
+}
+
+static PeerPtrs make_ptrs(const long long* ptrs, int world) {
+  PeerPtrs p;
+  for (int i = 0; i < MAX_RANKS; ++i) p.p[i] = i < world ? reinterpret_cast<void*>(ptrs[i]) : nullptr;
+  return p;
+}
+static inline int copy_grid(long long n) {
+  long long b = (n + 255) / 256;
+  const long long cap = (long long)sm_count() * 8;
+  return int(b < cap ? (b > 0 ? b : 1) : cap);
+}
+
+}  // namespace lyra
+
+using namespace lyra;
+#define ST(x) reinterpret_cast<cudaStream_t>(x)
+
+extern "C" int lyra_p2p_copy(void* dst, const void* src, long long nbytes, void* stream) {
+  if (nbytes <= 0) return 0;
+  if (nbytes % 16 || (reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) % 16) return -50;
+  p2p_copy_kernel<<<copy_grid(nbytes / 16), 256, 0, ST(stream)>>>(reinterpret_cast<uint4*>(dst), reinterpret_cast<const uint4*>(src), nbytes / 16);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_reduce_pull(void* out, const long long* peer_ptrs, int world, long long n, int in_bf16, int out_bf16, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 8 || world > MAX_RANKS) return -51;
+  const PeerPtrs p = make_ptrs(peer_ptrs, world);
+  const int grid = copy_grid(n / 8);
+  if (in_bf16 && out_bf16) reduce_pull_kernel<true, true><<<grid, 256, 0, ST(stream)>>>(out, p, world, n);
+  else if (in_bf16) reduce_pull_kernel<true, false><<<grid, 256, 0, ST(stream)>>>(out, p, world, n);
+  else if (out_bf16) reduce_pull_kernel<false, true><<<grid, 256, 0, ST(stream)>>>(out, p, world, n);
+  else reduce_pull_kernel<false, false><<<grid, 256, 0, ST(stream)>>>(out, p, world, n);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_signal(const long long* flag_arrays, int world, int my_rank, int value, void* stream) {
+  signal_kernel<<<1, 32, 0, ST(stream)>>>(make_ptrs(flag_arrays, world), world, my_rank, value);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_wait(const int* flags, int world, int value, int* status, void* stream) {
+  wait_kernel<<<1, 32, 0, ST(stream)>>>(flags, world, value, status);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_counts_push(const int* my_counts, const long long* counts_mats, const long long* flag_arrays, int world, int my_rank,
+                                   int n_experts, int epoch, void* stream) {
+  ep_counts_push_kernel<<<world, 128, 0, ST(stream)>>>(my_counts, make_ptrs(counts_mats, world), make_ptrs(flag_arrays, world), world, my_rank,
+                                                       n_experts, epoch);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_layout(const int* counts, int world, int my_rank, int n_experts, int e_local, int cap_rows, int* send_base,
+                              int* recv_offsets, int* tile_group, int* recv_total, int* status, void* stream) {
+  ep_layout_kernel<<<1, 256, 2 * n_experts * sizeof(int), ST(stream)>>>(counts, world, my_rank, n_experts, e_local, cap_rows, send_base, recv_offsets,
+                                                                         tile_group, recv_total, status);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_dispatch(const void* src, const int* expert_of, const int* rank_in_expert, const int* send_base, const long long* recv_bufs,
+                                const long long* recv_meta, int world, int my_rank, int e_local, int cap_rows, int n_assign, int src_div, int C,
+                                void* stream) {
+  if (n_assign <= 0) return 0;
+  if (C % 8) return -52;
+  PeerPtrs meta = recv_meta ? make_ptrs(recv_meta, world) : make_ptrs(recv_bufs, 0);
+  ep_dispatch_kernel<<<n_assign, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(src), expert_of, rank_in_expert, send_base,
+                                                       make_ptrs(recv_bufs, world), meta, my_rank, e_local, cap_rows, n_assign, src_div, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_return(const void* rows, const int* meta, const int* recv_offsets, const int* counts, int world, int my_rank, int n_experts,
+                              int e_local, const long long* ret_bufs, int cap_rows, int C, void* stream) {
+  ep_return_kernel<<<cap_rows, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(rows), meta, recv_offsets, counts, world, my_rank,
+                                                     n_experts, e_local, make_ptrs(ret_bufs, world), C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_zero_pad(void* rows, const int* recv_offsets, const int* counts, int world, int my_rank, int n_experts, int e_local,
+                                int cap_rows, int C, void* stream) {
+  ep_zero_pad_kernel<<<cap_rows, 128, 0, ST(stream)>>>(reinterpret_cast<__nv_bfloat16*>(rows), recv_offsets, counts, world, my_rank, n_experts,
+                                                       e_local, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}

@@ -21,6 +21,7 @@ from __future__ import annotations
 import ctypes
 import itertools
 import json
+import math
 import os
 import shutil
 import time
@@ -155,16 +156,27 @@ def _chunk_file(base: Path, index: tuple[int, ...]) -> Path:
     return base / "c" / Path(*map(str, index)) if index else base / "c"
 
 
-def save_tree(root: Path, tree: Any, *, shard_of=None, writes_leaf=None, is_primary: bool = True) -> None:
+def save_tree(root: Path, tree: Any, *, shard_of=None, writes_leaf=None, is_primary: bool = True, all_leaves=None) -> None:
     """Writes one pytree checkpointable. ``shard_of(path, tensor) -> (global_shape, ShardInfo)`` describes how the
     local tensor sits in the global array; ``writes_leaf(path)`` says whether this rank writes its chunk (one writer
     per distinct shard). The primary rank also writes the tree and array metadata."""
     leaves = tree_dict(tree)
     files: list[tuple[Path, np.ndarray]] = []
     meta: dict[str, dict] = {}
+    if all_leaves and is_primary:  # leaves owned by other ranks: the primary writes their array metadata
+        for path, (gshape, dtype, parts) in all_leaves.items():
+            if path in leaves and leaves[path].numel() > 0:
+                continue
+            base = root / _leaf_dir(path)
+            base.mkdir(parents=True, exist_ok=True)
+            chunk_shape = tuple(s // p for s, p in zip(gshape, parts))
+            (base / "zarr.json").write_text(json.dumps(_zarr_json(gshape, chunk_shape, dtype)))
+            meta[path] = {"shape": list(gshape), "dtype": _ZARR_DTYPES[dtype], "chunks": list(parts)}
     for path, t in leaves.items():
         if not isinstance(t, torch.Tensor):
             t = torch.as_tensor(t)
+        if all_leaves and t.numel() == 0 and path in all_leaves and math.prod(all_leaves[path][0]) > 0:
+            continue  # placeholder of a leaf owned elsewhere
         gshape, shard = shard_of(path, t) if shard_of else (tuple(t.shape), ShardInfo())
         parts, index = _chunk_grid(gshape, shard)
         chunk_shape = tuple(s // p for s, p in zip(gshape, parts))
@@ -250,7 +262,8 @@ def save_checkpointables(path: Path, checkpointables: dict[str, Any], *, custom_
             continue
         handlers[name] = "pytree"
         save_tree(root, value, shard_of=(rt.shard_of if rt is not None else None),
-                  writes_leaf=(rt.writes_leaf if rt is not None else None), is_primary=primary)
+                  writes_leaf=(rt.writes_leaf if rt is not None else None), is_primary=primary,
+                  all_leaves=(rt.checkpoint_leaves(name, value) if rt is not None else None))
     _barrier(rt)
     if primary:
         (tmp / METADATA_FILE).write_text(json.dumps({
@@ -286,6 +299,8 @@ def load_checkpointables(path: Path, abstract: dict[str, Any], *, device="cpu", 
             if tuple(saved[p]["shape"]) != gshape and not isinstance(leaf, torch.Tensor):
                 raise ValueError(mismatch)
             shard = rt.shard_info(p, leaf) if (rt is not None and isinstance(leaf, ArraySpec)) else ShardInfo()
+            if shard.absent:
+                return torch.empty(0, dtype=getattr(leaf, "dtype", torch.float32), device=device)
             return load_leaf(root, p, shard, getattr(leaf, "dtype", None), device)
 
         out[name] = map_with_path(load, tree)

@@ -161,6 +161,7 @@ class ShardInfo:
     """Which slice of the global array a rank holds: ``{dim: (index, parts)}``."""
 
     slices: tuple[tuple[int, int, int], ...] = ()  # (dim, index, parts)
+    absent: bool = False  # this rank holds no part of the leaf (it is owned elsewhere); a 0-element placeholder stands in
 
     def local_shape(self, shape: tuple[int, ...]) -> tuple[int, ...]:
         out = list(shape)
@@ -183,6 +184,8 @@ def init_leaf(spec: ArraySpec, seed: int, path: str, device, shard: ShardInfo | 
     (``stacked_init``, lyra/model.py:145-151), which lets an expert-parallel rank initialise only its experts."""
     fn = _INITIALIZERS[spec.init]
     shard = shard or ShardInfo()
+    if shard.absent:
+        return torch.empty(0, dtype=spec.dtype, device=device)
     stacked = spec.kind.startswith("moe_mlp") and spec.init not in ("zeros", "ones")
     if stacked:
         expert_slices = [s for s in shard.slices if s[0] == 0]

@@ -89,6 +89,7 @@ STATUS_NAMES = {
     3: "timeout waiting for an accumulator",
     4: "timeout waiting for a peer flag",
     5: "bad argument",
+    6: "expert-parallel receive buffer overflow (raise LYRA_EP_CAPACITY)",
 }
 
 

@@ -1,0 +1,267 @@
+"""Expert-parallel mixture-of-experts layer: dropless token exchange + local grouped expert MLP + weighted combine
+(the job of lyra/kernels/ep_moe.py in the reference, which off-TPU falls back to a dense [E, N, C] all-to-all).
+
+Receive layout on the expert's rank: expert-major, then source-rank-major (lyra/kernels/ep_moe.py:9-37), every expert's
+rows padded to a multiple of 128 so each GEMM tile belongs to one expert.
+
+* ``b200`` path: counts are pushed into every peer's counts matrix, each rank derives the full layout on the device,
+  token rows are stored straight into the owner's receive buffer over NVLink, epoch flags order the phases, and expert
+  outputs are stored straight back into the source rank's combine buffer. No host synchronisation, no collective call.
+* ``nccl`` path (baseline / CPU): the same exchange with ``all_to_all_single`` and host-side split sizes.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+import torch.distributed as dist
+
+from lyra_b200.config import ModelConfig
+from lyra_b200.ops import api as ops
+from lyra_b200.ops import reference as ref
+
+BF16 = torch.bfloat16
+CAPACITY = float(os.environ.get("LYRA_EP_CAPACITY", "2.0"))
+
+
+def ep_moe_forward(rt, xn, scores, indices, w, c: ModelConfig):
+    Kr = c.n_active_routed_experts
+    r_scores, r_idx = scores[:, :Kr].contiguous(), indices[:, :Kr].contiguous()
+    if rt.implementation == "b200" and xn.is_cuda:
+        out = _EPMoEKernel.apply(xn.contiguous(), r_scores.float(), r_idx, w.mlp_up, w.mlp_down, rt, c)
+    else:
+        out = _ep_moe_collectives(rt, xn, r_scores, r_idx, w, c)
+    for j in range(c.n_shared_experts):
+        up, down = rt.shared_expert_weights(w.mlp_up, w.mlp_down, j)
+        impl = c.implementation
+        h = ops.linear_swiglu(xn, up, None, c.swiglu_beta, c.swiglu_limit, impl)
+        o = ops.linear(h, down, None, impl)
+        out = out + o * scores[:, Kr + j, None].to(o.dtype)
+    return out
+
+
+# ============================================================================================ baseline: collectives
+class _AllToAll(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, send_splits, recv_splits, group):
+        ctx.splits, ctx.group = (send_splits, recv_splits), group
+        out = x.new_empty(sum(recv_splits), *x.shape[1:])
+        dist.all_to_all_single(out, x.contiguous(), recv_splits, send_splits, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        send_splits, recv_splits = ctx.splits
+        out = g.new_empty(sum(send_splits), *g.shape[1:])
+        dist.all_to_all_single(out, g.contiguous(), send_splits, recv_splits, group=ctx.group)
+        return out, None, None, None
+
+
+def _ep_moe_collectives(rt, xn, scores, indices, w, c: ModelConfig):
+    F_, K = indices.shape
+    E, El, W = c.n_experts, rt.e_local, rt.world
+    flat = indices.reshape(-1)
+    order = torch.argsort(flat, stable=True)                       # assignments sorted by expert (= by destination rank)
+    counts = torch.bincount(flat, minlength=E)
+    all_counts = [torch.zeros_like(counts) for _ in range(W)]
+    dist.all_gather(all_counts, counts, group=rt.group)
+    all_counts = torch.stack(all_counts)                           # [source, expert]
+    send_splits = counts.view(W, El).sum(1).tolist()
+    recv_counts = all_counts[:, rt.rank * El:(rt.rank + 1) * El]   # [source, local expert]
+    recv_splits = recv_counts.sum(1).tolist()
+    rows = xn[order // K]
+    recv = _AllToAll.apply(rows, send_splits, recv_splits, rt.group)   # source-major, expert-sorted within a source
+    # reorder to expert-major
+    src_id = torch.repeat_interleave(torch.arange(W, device=xn.device), torch.tensor(recv_splits, device=xn.device))
+    exp_id = torch.cat([torch.repeat_interleave(torch.arange(El, device=xn.device), recv_counts[s]) for s in range(W)]) if recv.shape[0] else src_id
+    perm = torch.argsort(exp_id * W + src_id, stable=True)
+    grouped = recv[perm]
+    groups = recv_counts.sum(0)
+    C, H = w.mlp_up.shape[1], w.mlp_up.shape[3]
+    t = ref.grouped_gemm_autograd(grouped, w.mlp_up.reshape(El, C, 2 * H), groups, None if w.mlp_up_bias is None else w.mlp_up_bias.reshape(El, 2 * H))
+    t = ref.swiglu(t.reshape(-1, 2, H), c.swiglu_beta, c.swiglu_limit).to(xn.dtype)
+    t = ref.grouped_gemm_autograd(t, w.mlp_down, groups, w.mlp_down_bias)
+    inv = torch.empty_like(perm)
+    inv[perm] = torch.arange(perm.numel(), device=perm.device)
+    back = _AllToAll.apply(t[inv], recv_splits, send_splits, rt.group)      # rows in `order` order
+    unsort = torch.empty_like(order)
+    unsort[order] = torch.arange(order.numel(), device=order.device)
+    ret = back[unsort].view(F_, K, C)
+    return torch.einsum("fkc,fk->fc", ret.float(), scores.float()).to(xn.dtype)
+
+
+# ============================================================================================ product: peer-memory kernels
+class EPBuffers:
+    """Peer-mapped buffers of the exchange, created on first use (the same order on every rank)."""
+
+    def __init__(self, rt, F_: int, K: int, C: int):
+        from lyra_b200.parallel.comm import SymmetricSlab
+
+        self.rt = rt
+        name = dist.group.WORLD.group_name
+        E, W = rt.mcfg.n_experts, rt.world
+        self.cap = ((int(CAPACITY * F_ * K) + 127) // 128 + rt.e_local) * 128
+        self.A = F_ * K
+        dev = rt.device
+        self.counts = [SymmetricSlab(W * E * 4, dev, name) for _ in range(2)]
+        self.scratch_recv = [SymmetricSlab(self.cap * C * 2, dev, name) for _ in range(2)]   # backward receive (parity)
+        self.scratch_ret = [SymmetricSlab(self.A * C * 2, dev, name) for _ in range(2)]      # backward return (parity)
+        self.layer: dict[int, dict] = {}
+        self.calls = 0
+        self.C, self.name = C, name
+
+    def for_layer(self, idx: int) -> dict:
+        from lyra_b200.parallel.comm import SymmetricSlab
+
+        if idx not in self.layer:
+            dev = self.rt.device
+            self.layer[idx] = {
+                "recv": SymmetricSlab(self.cap * self.C * 2, dev, self.name),
+                "meta": SymmetricSlab(self.cap * 4, dev, self.name),
+                "ret": SymmetricSlab(self.A * self.C * 2, dev, self.name),
+            }
+        return self.layer[idx]
+
+
+def _arr(ptrs):
+    return (ctypes.c_longlong * len(ptrs))(*ptrs)
+
+
+class _Exchange:
+    """One routing decision: layout + the dispatch / return primitives for both directions."""
+
+    def __init__(self, rt, indices: torch.Tensor, C: int):
+        from lyra_b200.ops import native
+
+        self.rt, self.nat, self.lib = rt, native, native.kernels()
+        F_, K = indices.shape
+        key = (F_, K, C)
+        if rt._ep_state.get("key") != key:
+            rt._ep_state = {"key": key, "buf": EPBuffers(rt, F_, K, C)}
+        self.buf: EPBuffers = rt._ep_state["buf"]
+        self.F, self.K, self.C = F_, K, C
+        self.W, self.E, self.El, self.rank = rt.world, rt.mcfg.n_experts, rt.e_local, rt.rank
+        comm = rt._comm
+        self.flags = comm.flag_slab
+        dev = indices.device
+        flat = indices.reshape(-1)
+        self.expert_of = flat.to(torch.int32).contiguous()
+        counts = torch.bincount(flat, minlength=self.E).to(torch.int32)
+        order = torch.argsort(flat, stable=True)
+        starts = torch.cumsum(counts, 0) - counts
+        rie = torch.empty_like(order)
+        rie[order] = torch.arange(flat.numel(), device=dev) - starts[flat[order]].long()
+        self.rank_in_expert = rie.to(torch.int32).contiguous()
+        # counts exchange
+        self.buf.calls += 1
+        par = self.buf.calls & 1
+        self.counts_slab = self.buf.counts[par]
+        stream = native.stream_ptr()
+        rt._ep_epoch = getattr(rt, "_ep_epoch", 0) + 1
+        ep = rt._ep_epoch
+        native.check(self.lib.lyra_ep_counts_push(native.ptr(counts), _arr(self.counts_slab.peer_ptrs), _arr(self.flags.peers_at(64)), self.W,
+                                                  self.rank, self.E, ep, stream), "ep_counts_push")
+        native.check(self.lib.lyra_wait(ctypes.c_void_p(self.flags.buffer.data_ptr() + 64), self.W, ep, native.ptr(native.status_word()), stream), "wait")
+        self.counts_mat = self.counts_slab.view(0, self.W * self.E, torch.int32).clone()   # private copy: the slab is reused by later calls
+        self.send_base = torch.empty(self.E, dtype=torch.int32, device=dev)
+        self.offsets = torch.empty(self.El + 1, dtype=torch.int32, device=dev)
+        self.tile_group = torch.empty(self.buf.cap // 128, dtype=torch.int32, device=dev)
+        self.total = torch.empty(1, dtype=torch.int32, device=dev)
+        native.check(self.lib.lyra_ep_layout(native.ptr(self.counts_mat), self.W, self.rank, self.E, self.El, self.buf.cap, native.ptr(self.send_base),
+                                             native.ptr(self.offsets), native.ptr(self.tile_group), native.ptr(self.total),
+                                             native.ptr(native.status_word()), stream), "ep_layout")
+        native.count_launch(3)
+
+    def _phase(self, flag_offset: int) -> None:
+        """Raises this rank's flag on all peers and waits for everyone's: all stores of the phase have landed."""
+        nat = self.nat
+        self.rt._ep_phase = getattr(self.rt, "_ep_phase", {})
+        v = self.rt._ep_phase.get(flag_offset, 0) + 1
+        self.rt._ep_phase[flag_offset] = v
+        stream = nat.stream_ptr()
+        nat.check(self.lib.lyra_signal(_arr(self.flags.peers_at(flag_offset)), self.W, self.rank, v, stream), "signal")
+        nat.check(self.lib.lyra_wait(ctypes.c_void_p(self.flags.buffer.data_ptr() + flag_offset), self.W, v, nat.ptr(nat.status_word()), stream), "wait")
+        nat.count_launch(2)
+
+    def dispatch(self, src: torch.Tensor, src_div: int, recv_slab, meta_slab) -> torch.Tensor:
+        nat = self.nat
+        nat.check(self.lib.lyra_ep_dispatch(nat.ptr(src), nat.ptr(self.expert_of), nat.ptr(self.rank_in_expert), nat.ptr(self.send_base),
+                                            _arr(recv_slab.peer_ptrs), _arr(meta_slab.peer_ptrs) if meta_slab is not None else None, self.W, self.rank,
+                                            self.El, self.buf.cap, self.F * self.K, src_div, self.C, nat.stream_ptr()), "ep_dispatch")
+        self._phase(128)
+        recv = recv_slab.view(0, self.buf.cap * self.C, BF16).view(self.buf.cap, self.C)
+        nat.check(self.lib.lyra_ep_zero_pad(nat.ptr(recv), nat.ptr(self.offsets), nat.ptr(self.counts_mat), self.W, self.rank, self.E, self.El,
+                                            self.buf.cap, self.C, nat.stream_ptr()), "ep_zero_pad")
+        nat.count_launch(2)
+        return recv
+
+    def collect(self, rows: torch.Tensor, meta_slab, ret_slab) -> torch.Tensor:
+        nat = self.nat
+        meta = meta_slab.view(0, self.buf.cap, torch.int32)
+        nat.check(self.lib.lyra_ep_return(nat.ptr(rows), nat.ptr(meta), nat.ptr(self.offsets), nat.ptr(self.counts_mat), self.W, self.rank, self.E,
+                                          self.El, _arr(ret_slab.peer_ptrs), self.buf.cap, self.C, nat.stream_ptr()), "ep_return")
+        self._phase(192)
+        nat.count_launch()
+        return ret_slab.view(0, self.F * self.K * self.C, BF16).view(self.F * self.K, self.C)
+
+
+class _EPMoEKernel(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, xn, scores, indices, w_up, w_down, rt, c):
+        from lyra_b200.ops import cuda_ops, elementwise as ew, gemm as G
+
+        F_, K = indices.shape
+        El, C, _, H = w_up.shape
+        ex = _Exchange(rt, indices, C)
+        bufs = ex.buf.for_layer(rt._layer)
+        x_recv = ex.dispatch(xn, K, bufs["recv"], bufs["meta"])
+        wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
+        cap = ex.buf.cap
+        act = G.grouped_gemm(x_recv, wu, ex.tile_group, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
+                             out=torch.zeros(cap, H, dtype=BF16, device=xn.device))
+        down = G.grouped_gemm(act, wd, ex.tile_group, out=torch.zeros(cap, C, dtype=BF16, device=xn.device))
+        ret = ex.collect(down, bufs["meta"], bufs["ret"])
+        ident = torch.arange(F_ * K, device=xn.device)
+        out = ew.combine_rows(ret, ident, scores, F_, K)
+        ctx.save_for_backward(scores, w_up, w_down, ident)
+        ctx.ex, ctx.bufs, ctx.cfg, ctx.rt = ex, bufs, (c.swiglu_beta, c.swiglu_limit), rt
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from lyra_b200.ops import cuda_ops, elementwise as ew, gemm as G
+
+        scores, w_up, w_down, ident = ctx.saved_tensors
+        ex, bufs, (beta, limit) = ctx.ex, ctx.bufs, ctx.cfg
+        F_, K = scores.shape
+        El, C, _, H = w_up.shape
+        cap, dev = ex.buf.cap, dout.device
+        par = ex.buf.calls & 1
+        ret = bufs["ret"].view(0, F_ * K * C, BF16).view(F_ * K, C)
+        d_ret, dscores = ew.combine_rows_bwd(ret, dout.contiguous(), ident, scores, F_ * K)
+        d_down = ex.dispatch(d_ret, 1, ex.buf.scratch_recv[par], None)
+        x_recv = bufs["recv"].view(0, cap * C, BF16).view(cap, C)
+        wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
+        pre = G.grouped_gemm(x_recv, wu, ex.tile_group, out=torch.zeros(cap, 2 * H, dtype=BF16, device=dev))
+        act = ew.swiglu_fwd(pre, beta, limit)
+        gd = cuda_ops.GRAD_DTYPE
+        if w_down.requires_grad:
+            if w_down.grad is None:
+                w_down.grad = G.grouped_wgrad(act, d_down, ex.offsets, El).to(gd)
+            else:
+                G.grouped_wgrad(act, d_down, ex.offsets, El, out=w_down.grad, accumulate=True)
+        d_act = G.grouped_gemm(d_down, wd, ex.tile_group, w_kmajor=True, out=torch.zeros(cap, H, dtype=BF16, device=dev))
+        del act
+        d_pre = ew.swiglu_bwd(pre, d_act, beta, limit)
+        del pre, d_act
+        if w_up.requires_grad:
+            if w_up.grad is None:
+                w_up.grad = G.grouped_wgrad(x_recv, d_pre, ex.offsets, El).view(w_up.shape).to(gd)
+            else:
+                G.grouped_wgrad(x_recv, d_pre, ex.offsets, El, out=w_up.grad.view(El, C, 2 * H), accumulate=True)
+        dx_recv = G.grouped_gemm(d_pre, wu, ex.tile_group, w_kmajor=True, out=torch.zeros(cap, C, dtype=BF16, device=dev))
+        dx_a = ex.collect(dx_recv, bufs["meta"], ex.buf.scratch_ret[par])
+        dxn = ew.gather_sum_rows(dx_a, ident, F_, K)
+        return dxn, dscores, None, None, None, None, None

@@ -1,0 +1,269 @@
+"""Sharding runtime for one NVSwitch node: one process per GPU, one flat group of ranks that is at once the
+data-parallel, the parameter-sharding (ZeRO-3 style) and the expert-parallel axis.
+
+What is sharded and how (the reference shards rows of every matrix over an ``fsdp`` axis and all-gathers the whole
+model at the top of a step, lyra/nn/params.py:154-165, lyra/training/steps.py:75-91; here the unit is chosen for Muon):
+
+* dense matrices and embeddings - each leaf is *owned* by one rank (greedy size balancing). The owner keeps the fp32
+  master and the optimizer moments and runs Newton-Schulz on the whole matrix locally; every rank keeps a bf16 compute
+  copy that it pulls from the owner over NVLink after the optimizer step, and accumulates its gradient into a
+  peer-mapped buffer from which the owner pull-reduces (fixed rank order, deterministic) at the end of the step;
+* expert stacks - sharded by expert over the ranks; tokens travel to the experts (dispatch) and results travel back
+  (return + weighted combine). The shared expert is applied to local tokens from a replicated bf16 copy that its
+  owning rank refreshes once per step - not broadcast on every call as in lyra/kernels/ep_moe.py:62-77;
+* small leaves (norm scales, sinks, biases, router, gate) - replicated; their gradients are summed over ranks.
+
+``implementation="b200"`` moves all of this with the kernels of ``csrc/comm`` over peer-mapped memory;
+``implementation="nccl"`` uses torch.distributed collectives with the same data flow (the baseline mode, also the
+mode that runs on CPU with gloo).
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from lyra_b200.config import ModelConfig
+from lyra_b200.nn.params import ArraySpec, ShardInfo, Tag, tree_dict
+
+BF16 = torch.bfloat16
+SMALL_LEAF = int(os.environ.get("LYRA_SMALL_LEAF", 1 << 16))  # leaves below this many elements are replicated
+
+
+def _is_expert(spec: ArraySpec) -> bool:
+    return spec.kind.startswith("moe_mlp")
+
+
+@dataclass
+class Plan:
+    """Static placement of every parameter leaf."""
+
+    owner: dict[str, int] = field(default_factory=dict)        # dense sharded leaves -> owning rank
+    replicated: set = field(default_factory=set)
+    expert: set = field(default_factory=set)
+    specs: dict[str, ArraySpec] = field(default_factory=dict)
+
+    @classmethod
+    def build(cls, mcfg: ModelConfig, world: int) -> "Plan":
+        from lyra_b200.model import ModelWeights
+
+        plan = cls()
+        plan.specs = tree_dict(ModelWeights.spec(mcfg))
+        dense = []
+        for path, spec in plan.specs.items():
+            n = math.prod(spec.shape)
+            if _is_expert(spec) and world > 1 and mcfg.n_experts % world == 0:
+                plan.expert.add(path)
+            elif world > 1 and n >= SMALL_LEAF and spec.tag in (Tag.MATRIX, Tag.EMBEDDING):
+                dense.append((n, path))
+            else:
+                plan.replicated.add(path)
+        load = [0] * world
+        for n, path in sorted(dense, key=lambda x: (-x[0], x[1])):
+            r = min(range(world), key=lambda i: (load[i], i))
+            plan.owner[path] = r
+            load[r] += n
+        return plan
+
+
+class Runtime:
+    def __init__(self, world_size: int, rank: int, device, implementation: str, mcfg: ModelConfig, group=None):
+        self.world, self.rank, self.device = world_size, rank, torch.device(device)
+        self.implementation = implementation if self.device.type == "cuda" else "nccl"
+        self.mcfg = mcfg
+        self.group = group
+        self.plan = Plan.build(mcfg, world_size)
+        self.ep_size = world_size if self.plan.expert else 1
+        self.tp_size = 1
+        self.data_size, self.data_rank = world_size, rank
+        self.owns_optimizer = False
+        self.e_local = mcfg.n_experts // self.ep_size
+        self._path_of: dict[int, str] = {}
+        self._views: dict[str, torch.Tensor] = {}
+        self._masters: dict[str, torch.Tensor] = {}
+        self._comm = None
+        self._ep_state: dict = {}
+        self._layer = 0
+
+    @classmethod
+    def create(cls, *, world_size: int, rank: int, device, implementation: str = "b200", mcfg: ModelConfig | None = None) -> "Runtime":
+        assert mcfg is not None, "Runtime.create needs the model configuration to plan the sharding"
+        return cls(world_size, rank, device, implementation, mcfg)
+
+    # ------------------------------------------------------------------ placement queries (init / checkpoints)
+    def shard_info(self, path: str, spec: Any) -> ShardInfo:
+        base = path.split("#")[0]
+        if base in self.plan.expert:
+            return ShardInfo(((0, self.rank, self.ep_size),))
+        if base in self.plan.owner and self.plan.owner[base] != self.rank:
+            return ShardInfo(absent=True)
+        return ShardInfo()
+
+    def shard_of(self, path: str, t: torch.Tensor):
+        spec = self.plan.specs.get(path)
+        if spec is None:
+            return tuple(t.shape), ShardInfo()
+        info = self.shard_info(path, spec)
+        return tuple(spec.shape), (ShardInfo() if info.absent else info)
+
+    def writes_leaf(self, path: str) -> bool:
+        if path in self.plan.expert:
+            return True
+        if path in self.plan.owner:
+            return self.plan.owner[path] == self.rank
+        return self.rank == 0
+
+    def checkpoint_leaves(self, name: str, tree: Any) -> dict[str, tuple[tuple[int, ...], torch.dtype, tuple[int, ...]]] | None:
+        """Global shape, dtype and chunk grid of every leaf of a parameter-shaped checkpointable, including the leaves
+        this rank does not hold. ``tree`` supplies the dtype (moments differ from parameters)."""
+        present = tree_dict(tree)
+        if not present or not all(p in self.plan.specs for p in present):
+            return None
+        dtype = next(iter(present.values())).dtype
+        tags = {self.plan.specs[p].tag for p in present}
+        out = {}
+        for p, spec in self.plan.specs.items():
+            if spec.tag not in tags and name != "params":
+                continue
+            parts = [1] * len(spec.shape)
+            if p in self.plan.expert:
+                parts[0] = self.ep_size
+            out[p] = (tuple(spec.shape), present[p].dtype if p in present else dtype, tuple(parts))
+        return out
+
+    def barrier(self) -> None:
+        dist.barrier(group=self.group)
+
+    # ------------------------------------------------------------------ registration of the parameter tree
+    def register(self, params: Any) -> None:
+        """Binds the runtime to a parameter tree: allocates the bf16 compute copies and gradient buffers of every
+        sharded dense leaf (and of the shared expert), fills them from the owners and remembers which tensor is which leaf."""
+        from lyra_b200.parallel.comm import Comm
+
+        leaves = tree_dict(params)
+        self._masters = leaves
+        self._path_of = {id(t): p for p, t in leaves.items()}
+        c = self.mcfg
+        entries: list[tuple[str, tuple[int, ...], int]] = []   # (name, shape, owner)
+        for path, owner in self.plan.owner.items():
+            entries.append((path, tuple(self.plan.specs[path].shape), owner))
+        self._shared: dict[str, tuple[str, int]] = {}
+        if self.ep_size > 1 and c.n_shared_experts:
+            for path in sorted(self.plan.expert):
+                if path.endswith(("mlp_up", "mlp_down")):
+                    for j in range(c.n_shared_experts):
+                        e = c.n_routed_experts + j
+                        name = f"{path}#shared{j}"
+                        entries.append((name, tuple(self.plan.specs[path].shape[1:]), e // self.e_local))
+                        self._shared[name] = (path, e)
+        self._entries = entries
+        from lyra_b200.ops import cuda_ops
+
+        grad_dtype = cuda_ops.GRAD_DTYPE if self.device.type == "cuda" else torch.float32
+        self._comm = Comm(self, entries, grad_dtype)
+        for name, shape, owner in entries:
+            w = self._comm.weight_view(name).view(shape)
+            w.requires_grad_(True)
+            try:
+                w.grad_dtype = None
+            except Exception:
+                pass
+            self._views[name] = w
+        self.refresh_weights()
+
+    def _master_of(self, name: str) -> torch.Tensor:
+        if name in self._shared:
+            path, e = self._shared[name]
+            return self._masters[path][e - self.rank * self.e_local]
+        return self._masters[name]
+
+    @torch.no_grad()
+    def refresh_weights(self) -> None:
+        """Owners publish bf16 copies of their masters; every rank pulls the leaves it does not own."""
+        for name, shape, owner in self._entries:
+            if owner == self.rank:
+                self._comm.weight_view(name).view(shape).copy_(self._master_of(name).detach())
+        self._comm.gather_weights()
+
+    # ------------------------------------------------------------------ hooks used by the model / stepper
+    def begin_layer(self, idx: int) -> None:
+        self._layer = idx
+
+    def begin_microbatch(self, index: int, total: int) -> None:
+        if index == 0:
+            self._comm.zero_grads()
+            for w in self._views.values():
+                w.grad = self._comm.grad_view_of(w)
+
+    def materialize(self, p):
+        if p is None or not isinstance(p, torch.Tensor):
+            return p
+        path = self._path_of.get(id(p))
+        if path is not None and path in self._views:
+            return self._views[path]
+        return p
+
+    def shared_expert_weights(self, up_leaf: torch.Tensor, down_leaf: torch.Tensor, j: int = 0):
+        up_path, down_path = self._path_of[id(up_leaf)], self._path_of[id(down_leaf)]
+        return self._views[f"{up_path}#shared{j}"], self._views[f"{down_path}#shared{j}"]
+
+    def tp_all_reduce(self, t):
+        return t
+
+    def sum_scalars(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def sum_over_ranks(self, *ts: torch.Tensor):
+        stacked = torch.stack([t.float() for t in ts])
+        dist.all_reduce(stacked, group=self.group)
+        return tuple(stacked.unbind(0))
+
+    def max_over_ranks(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.clone()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return t
+
+    @torch.no_grad()
+    def reduce_grads(self, grads: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        """Turns per-rank gradients into the gradients of the leaves this rank updates: owned dense leaves are
+        pull-reduced from every rank's buffer, replicated leaves are summed over ranks, expert leaves are local
+        except the shared expert, whose slot receives the sum of every rank's shared-expert gradient."""
+        out: dict[str, torch.Tensor] = {}
+        reduced = self._comm.reduce_grads()                      # name -> reduced gradient (owned entries only)
+        small = {p: g for p, g in grads.items() if p in self.plan.replicated}
+        self._comm.all_reduce_small(small)
+        for p, g in grads.items():
+            if p in self.plan.replicated:
+                out[p] = g
+            elif p in self.plan.expert:
+                out[p] = g
+        for p in self.plan.expert:
+            if p not in out and p in self._masters and p.endswith(("mlp_up", "mlp_down")):
+                # an expert leaf that saw no routed token still needs a (zero) gradient slot for the shared expert
+                out[p] = torch.zeros_like(self._masters[p], dtype=next(iter(grads.values())).dtype if grads else torch.float32)
+        for name, g in reduced.items():
+            if name in self._shared:
+                path, e = self._shared[name]
+                out[path][e - self.rank * self.e_local].copy_(g.view(out[path].shape[1:]))
+            else:
+                out[name] = g.view(self.plan.specs[name].shape)
+        return out
+
+    def after_optimizer(self, params: dict[str, torch.Tensor]) -> None:
+        self.refresh_weights()
+
+    def counts_once(self, path: str) -> bool:
+        """Whether this rank counts ``path`` in global norms (replicated leaves are counted by rank 0 only)."""
+        return path not in self.plan.replicated or self.rank == 0
+
+    # ------------------------------------------------------------------ expert parallel MoE
+    def ep_moe(self, xn, scores, indices, w, c: ModelConfig):
+        from lyra_b200.parallel.ep import ep_moe_forward
+
+        return ep_moe_forward(self, xn, scores, indices, w, c)

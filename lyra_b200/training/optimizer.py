@@ -54,6 +54,8 @@ class OptimizerState:
         p, s = tree_dict(params), tree_dict(spec)
         st = cls()
         for path, leaf in p.items():
+            if leaf.numel() == 0 and math.prod(s[path].shape) > 0:
+                continue  # owned by another rank
             if s[path].tag in MUON_TAGS:
                 st.muon_moment[path] = torch.zeros_like(leaf, dtype=tcfg.muon_moment_dtype)
             else:
@@ -110,16 +112,13 @@ def optimizer_step(params: dict[str, torch.Tensor], grads: dict[str, torch.Tenso
     muon_paths = [p for p in params if p in state.muon_moment]
     adam_paths = [p for p in params if p in state.adam_mu]
 
-    use_cuda = dev.type == "cuda" and rt is not None and getattr(rt, "fused_optimizer", False)
-    if use_cuda:
-        return rt.optimizer_step(params, grads, state, step, tcfg)
-
     # ---- norms and per-matrix RMS (global quantities: summed over ranks for sharded leaves)
     zero = torch.zeros((), dtype=torch.float32, device=dev)
-    muon_sq = sum((_sumsq(grads[p]) for p in muon_paths), zero)
-    adam_sq = sum((_sumsq(grads[p]) for p in adam_paths), zero)
+    once = (lambda p: rt.counts_once(p)) if rt is not None else (lambda p: True)
+    muon_sq = sum((_sumsq(grads[p]) for p in muon_paths if once(p)), zero)
+    adam_sq = sum((_sumsq(grads[p]) for p in adam_paths if once(p)), zero)
     if rt is not None:
-        muon_sq, adam_sq = rt.sum_over_shards(muon_sq, adam_sq)
+        muon_sq, adam_sq = rt.sum_over_ranks(muon_sq, adam_sq)
     grad_norm = (muon_sq + adam_sq).sqrt()
     finite = torch.isfinite(grad_norm)
     enabled = finite.float()
@@ -131,8 +130,6 @@ def optimizer_step(params: dict[str, torch.Tensor], grads: dict[str, torch.Tenso
         m, swapped = as_matrices(p, g.float())
         msq = (m * m).sum(dim=(-2, -1), keepdim=True)
         numel = m.shape[-2] * m.shape[-1]
-        if rt is not None:
-            msq, numel = rt.matrix_sumsq(p, msq, numel)
         r = (msq / numel).sqrt()
         all_rms.append(r.reshape(-1))
         scale = torch.where(torch.isfinite(r), torch.clamp(tcfg.muon_grad_clip / (r + 1e-8), max=1.0), torch.ones_like(r))
@@ -145,6 +142,10 @@ def optimizer_step(params: dict[str, torch.Tensor], grads: dict[str, torch.Tenso
         "grad_is_finite": finite,
         "muon_grad_rms_max": all_rms_t.max(), "muon_grad_clip_frac": (all_rms_t > tcfg.muon_grad_clip).float().mean(),
     }
+    if rt is not None:
+        metrics["muon_grad_rms_max"] = rt.max_over_ranks(metrics["muon_grad_rms_max"])
+        clipped_n, total_n = rt.sum_over_ranks((all_rms_t > tcfg.muon_grad_clip).float().sum(), torch.tensor(float(all_rms_t.numel()), device=dev))
+        metrics["muon_grad_clip_frac"] = clipped_n / total_n.clamp_min(1.0)
 
     # ---- Muon
     lr_m = muon_lr * enabled
@@ -155,12 +156,8 @@ def optimizer_step(params: dict[str, torch.Tensor], grads: dict[str, torch.Tenso
         state.muon_moment[p].copy_(m_new)
         d = (g + tcfg.muon_momentum * m_new.float()) if tcfg.muon_nesterov else m_new.float()
         dm, swapped = as_matrices(p, d)
-        if rt is not None:
-            ns = rt.newton_schulz(p, dm)
-            rows, cols = rt.matrix_shape(p, dm)
-        else:
-            ns = newtonschulz(dm)
-            rows, cols = dm.shape[-2], dm.shape[-1]
+        ns = newtonschulz(dm)  # every matrix is whole on the rank that updates it
+        rows, cols = dm.shape[-2], dm.shape[-1]
         stepv = lr_m * ns.float() * (math.sqrt(max(rows, cols)) * tcfg.muon_update_rms)
         stepv = stepv.transpose(-3, -2) if swapped else stepv
         w = params[p]

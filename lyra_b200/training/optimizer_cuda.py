@@ -65,7 +65,7 @@ def _matrix_geometry(path: str, shape: tuple[int, ...]) -> tuple[int, int, int, 
 
 @torch.no_grad()
 def optimizer_step_cuda(params: dict[str, torch.Tensor], grads: dict[str, torch.Tensor], state: OptimizerState, step: int, tcfg,
-                        shadows: dict[str, torch.Tensor] | None = None) -> dict[str, torch.Tensor]:
+                        shadows: dict[str, torch.Tensor] | None = None, rt=None) -> dict[str, torch.Tensor]:
     lib = native.kernels()
     adam_lr, muon_lr, lr_scale = wsd_lr(step, tcfg)
     dev = state.adam_count.device
@@ -76,8 +76,11 @@ def optimizer_step_cuda(params: dict[str, torch.Tensor], grads: dict[str, torch.
 
     # ---- global norm, finite gate, per-matrix RMS clip factors
     zero = torch.zeros((), dtype=torch.float32, device=dev)
-    muon_sq = sum((_sumsq(grads[p]) for p in muon_paths), zero)
-    adam_sq = sum((_sumsq(grads[p]) for p in adam_paths), zero)
+    once = (lambda p: rt.counts_once(p)) if rt is not None else (lambda p: True)
+    muon_sq = sum((_sumsq(grads[p]) for p in muon_paths if once(p)), zero)
+    adam_sq = sum((_sumsq(grads[p]) for p in adam_paths if once(p)), zero)
+    if rt is not None:
+        muon_sq, adam_sq = rt.sum_over_ranks(muon_sq, adam_sq)
     grad_norm = (muon_sq + adam_sq).sqrt()
     finite = torch.isfinite(grad_norm)
     enabled = finite.float().reshape(1).contiguous()
@@ -96,6 +99,11 @@ def optimizer_step_cuda(params: dict[str, torch.Tensor], grads: dict[str, torch.
         "grad_norm": grad_norm, "muon_grad_norm": muon_sq.sqrt(), "adam_grad_norm": adam_sq.sqrt(), "grad_is_finite": finite,
         "muon_grad_rms_max": all_rms_t.max(), "muon_grad_clip_frac": (all_rms_t > tcfg.muon_grad_clip).float().mean(),
     }
+
+    if rt is not None:
+        metrics["muon_grad_rms_max"] = rt.max_over_ranks(metrics["muon_grad_rms_max"])
+        clipped_n, total_n = rt.sum_over_ranks((all_rms_t > tcfg.muon_grad_clip).float().sum(), torch.tensor(float(all_rms_t.numel()), device=dev))
+        metrics["muon_grad_clip_frac"] = clipped_n / total_n.clamp_min(1.0)
 
     # ---- Muon
     nesterov = tcfg.muon_momentum if tcfg.muon_nesterov else -1.0

@@ -42,7 +42,7 @@ class Stepper:
 
     def __init__(self, state: TrainState, mcfg: ModelConfig, tcfg, *, device, rt=None):
         self.state, self.mcfg, self.tcfg, self.rt, self.device = state, mcfg, tcfg, rt, torch.device(device)
-        self.params = tree_dict(state.params)
+        self.params = {p: t for p, t in tree_dict(state.params).items() if t.numel() > 0}  # placeholders of leaves owned by other ranks are skipped
         for p in self.params.values():
             if p.is_floating_point():
                 p.requires_grad_(True)
@@ -51,6 +51,8 @@ class Stepper:
                 except Exception:
                     pass
         self.world = rt.data_size if rt is not None else 1
+        if rt is not None:
+            rt.register(state.params)
         self.copy_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -107,7 +109,7 @@ class Stepper:
                 from lyra_b200.training.optimizer_cuda import optimizer_step_cuda
 
                 shadows = {p: sh for p, t in trainable.items() if (sh := cuda_ops.shadow_of(t)) is not None}
-                metrics = optimizer_step_cuda(trainable, grads, self.state.optimizer, step, self.tcfg, shadows)
+                metrics = optimizer_step_cuda(trainable, grads, self.state.optimizer, step, self.tcfg, shadows, rt=self.rt)
             else:
                 metrics = optimizer_step({p: t.detach() for p, t in trainable.items()}, grads, self.state.optimizer, step, self.tcfg, rt=self.rt)
                 if self.device.type == "cuda":

@@ -130,7 +130,7 @@ def main(argv: list[str] | None = None) -> int:
 
         dist.init_process_group("nccl" if use_gpu else "gloo")
         rt = Runtime.create(world_size=world, rank=dist.get_rank(), device=device,
-                            implementation="nccl" if (args.implementation in ("torch", "nccl") or not use_gpu) else "b200")
+                            implementation="nccl" if (args.implementation in ("torch", "nccl") or not use_gpu) else "b200", mcfg=mcfg)
     if rt is None or rt.rank == 0:
         print(f"Training {mcfg.name} for {tcfg.steps:,} steps")
     model = None

@@ -1,0 +1,103 @@
+"""Two gloo ranks on CPU: the sharding runtime in its collective ("nccl") mode must reproduce the single-process step:
+leaf ownership, weight gather, gradient reduce, replicated-leaf all-reduce, expert-parallel exchange, shared expert."""
+
+import os
+import sys
+from dataclasses import replace
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+os.environ["LYRA_SMALL_LEAF"] = "2048"  # shard the small test model's matrices too (inherited by the spawned ranks)
+
+
+def _cfg():
+    from tests.helpers import small_config
+
+    return small_config(n_routed_experts=7, n_shared_experts=1, n_active_experts=3, n_embd=64, head_dim=16, n_attn_heads=4, n_kv_heads=2,
+                        vocab_size=2000, padded_vocab_size=2048, compute_dtype=torch.float32, seq_len=16,
+                        load_balance_weight=0.0)  # the balance term is a product of per-rank means, so it is not additive over ranks
+
+
+def _worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lyra_b200.model import ModelWeights
+        from lyra_b200.nn.params import tree_dict
+        from lyra_b200.parallel.runtime import Runtime
+        from lyra_b200.training.state import init_train_state, save_checkpoint, load_train_state
+        from lyra_b200.training.steps import Stepper
+        from lyra_b200.training.train import TrainingConfig
+
+        c = _cfg()
+        tcfg = TrainingConfig(steps=4, batch_size=4, accumulation_steps=2)
+        rt = Runtime.create(world_size=world, rank=rank, device="cpu", implementation="nccl", mcfg=c)
+        w = ModelWeights.init(0, c, shard_fn=rt.shard_info)
+        state = init_train_state(w, c, tcfg)
+        st = Stepper(state, c, tcfg, device="cpu", rt=rt)
+        data = np.load(tmp + "/batch.npy")                      # [A, 4, T] global batch
+        xs = data[:, rank * 2:(rank + 1) * 2]
+        ys = np.roll(xs, -1, axis=-1)
+        out = None
+        for step in range(2):
+            out = st.train_step(xs, ys, step)
+        torch.save({"loss": float(out["loss"]), "grad_norm": float(out["grad_norm"]),
+                    "params": {p: t.detach().clone() for p, t in tree_dict(w).items() if t.numel()},
+                    "owner": dict(rt.plan.owner), "expert": sorted(rt.plan.expert)}, f"{tmp}/rank{rank}.pt")
+        save_checkpoint(Path(tmp) / "ckpt", 2, state, b'{"position": 0}', {"resume_signature": {}}, keep=1, rt=rt)
+        restored = load_train_state(Path(tmp) / "ckpt", c, tcfg, rt=rt)
+        a, b = tree_dict(state.params), tree_dict(restored.state.params)
+        assert all(torch.equal(a[k], b[k]) for k in a)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_step_matches_single_process(tmp_path):
+    from lyra_b200.model import ModelWeights
+    from lyra_b200.nn.checkpoints import load_leaf
+    from lyra_b200.nn.params import ShardInfo, tree_dict
+    from lyra_b200.training.state import init_train_state
+    from lyra_b200.training.steps import Stepper
+    from lyra_b200.training.train import TrainingConfig
+
+    c = _cfg()
+    rng = np.random.default_rng(0)
+    data = rng.integers(0, c.vocab_size, size=(2, 4, c.seq_len)).astype(np.int32)
+    np.save(tmp_path / "batch.npy", data)
+    port = 29600 + os.getpid() % 300
+    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+
+    tcfg = TrainingConfig(steps=4, batch_size=4, accumulation_steps=2)
+    w = ModelWeights.init(0, c)
+    st = Stepper(init_train_state(w, c, tcfg), c, tcfg, device="cpu")
+    for step in range(2):
+        out = st.train_step(data, np.roll(data, -1, axis=-1), step)
+    ref = tree_dict(w)
+    ranks = [torch.load(tmp_path / f"rank{r}.pt", weights_only=False) for r in range(2)]
+    assert abs(ranks[0]["loss"] - float(out["loss"])) < 1e-4 and abs(ranks[0]["grad_norm"] - float(out["grad_norm"])) < 1e-3 * float(out["grad_norm"])
+    owner, experts = ranks[0]["owner"], set(ranks[0]["expert"])
+    assert owner and experts and set(owner.values()) == {0, 1}
+    el = c.n_experts // 2
+    for p, full in ref.items():
+        if p in experts:
+            for r in range(2):
+                assert torch.allclose(ranks[r]["params"][p], full[r * el:(r + 1) * el], atol=1.5e-3), p
+        elif p in owner:
+            assert p in ranks[owner[p]]["params"] and p not in ranks[1 - owner[p]]["params"]
+            assert torch.allclose(ranks[owner[p]]["params"][p], full, atol=1.5e-3), p
+        else:
+            for r in range(2):
+                assert torch.allclose(ranks[r]["params"][p], full, atol=1.5e-3), p
+    # the checkpoint written by two ranks holds global arrays readable without the runtime
+    ck = tmp_path / "ckpt" / "step_00000002" / "params"
+    some_expert = next(iter(sorted(experts)))
+    assert torch.allclose(load_leaf(ck, some_expert, ShardInfo()), ref[some_expert], atol=1.5e-3)
+    some_dense = next(iter(sorted(owner)))
+    assert torch.allclose(load_leaf(ck, some_dense, ShardInfo()), ref[some_dense], atol=1.5e-3)
