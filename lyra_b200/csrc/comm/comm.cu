@@ -1,6 +1,6 @@
 // NVLink / NVSwitch data movement between the GPUs of one node through peer-mapped (symmetric) memory.
 // Every kernel takes raw peer pointers and uses plain 16-byte loads / stores plus system-scope release / acquire
-// flags: no collective library call, no multicast, and nothing that can wait forever - every wait spins for a
+// flags: no collective library call, and nothing that can wait forever - every wait spins for a
 // bounded time, then records STATUS_TIMEOUT_PEER in a status word and returns.
 //
 //   p2p_copy      : pull a buffer from one peer (parameter broadcast from its owner = the all-gather leg of ZeRO-3)

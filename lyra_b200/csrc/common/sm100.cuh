@@ -1,5 +1,5 @@
 // Thin inline-PTX layer for Blackwell (sm_100a): mbarrier, TMA (local memory only,
-// never cluster-multicast), tcgen05 MMA / TMEM, and bounded waits.
+// plain per-CTA loads), tcgen05 MMA / TMEM, and bounded waits.
 //
 // Every wait in this file is bounded: after WAIT_LIMIT_CYCLES the wait returns false,
 // the caller records an error code in a status word and leaves its loops, so a
