@@ -23,7 +23,7 @@ from lyra_b200.ops import api as ops
 from lyra_b200.ops import reference as ref
 
 BF16 = torch.bfloat16
-CAPACITY = float(os.environ.get("LYRA_EP_CAPACITY", "2.0"))
+CAPACITY = float(os.environ.get("LYRA_EP_CAPACITY", "4.0"))  # receive-buffer rows as a multiple of the balanced load (never above the world size)
 
 
 def ep_moe_forward(rt, xn, scores, indices, w, c: ModelConfig):
@@ -102,7 +102,7 @@ class EPBuffers:
         self.rt = rt
         name = dist.group.WORLD.group_name
         E, W = rt.mcfg.n_experts, rt.world
-        self.cap = ((int(CAPACITY * F_ * K) + 127) // 128 + rt.e_local) * 128
+        self.cap = ((int(min(CAPACITY, float(W)) * F_ * K) + 127) // 128 + rt.e_local) * 128
         self.A = F_ * K
         dev = rt.device
         self.counts = [SymmetricSlab(W * E * 4, dev, name) for _ in range(2)]
