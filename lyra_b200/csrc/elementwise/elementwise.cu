@@ -278,6 +278,31 @@ __global__ void __launch_bounds__(256) combine_rows_bwd_kernel(const __nv_bfloat
   }
 }
 
+// Deterministic embedding gradient (sorted segment-sum, lyra/kernels/embs.py:22-29): positions are sorted by token id;
+// the block at the first position of each run of equal ids sums the run's gradient rows in order (fp32) and adds the
+// sum into that id's row of the gradient buffer. One writer per row: no atomics, fixed summation order.
+template <typename G>
+__global__ void embedding_grad_kernel(const long long* __restrict__ sorted_ids, const long long* __restrict__ order,
+                                      const __nv_bfloat16* __restrict__ g, G* __restrict__ grad, int F, int C) {
+  const int i = blockIdx.x;
+  const long long id = sorted_ids[i];
+  if (i > 0 && sorted_ids[i - 1] == id) return;
+  int end = i + 1;
+  while (end < F && sorted_ids[end] == id) ++end;
+  for (int c = threadIdx.x; c < C / 8; c += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = i; j < end; ++j) {
+      float v[8];
+      unpack8(reinterpret_cast<const BF8*>(g + order[j] * C)[c], v);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) acc[k] += v[k];
+    }
+    G* dst = grad + id * C + c * 8;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) dst[k] = G(float(dst[k]) + acc[k]);
+  }
+}
+
 static inline int ew_grid(long long n, int threads) {
   long long b = (n + threads - 1) / threads;
   const long long cap = (long long)sm_count() * 32;
@@ -354,6 +379,16 @@ extern "C" int lyra_combine_rows_bwd(const void* rows, const void* dout, const l
   if (F <= 0) return 0;
   if (C % 8) return -42;
   combine_rows_bwd_kernel<<<F, 256, 0, S_(stream)>>>(CBFP(rows), CBFP(dout), dest, scores, BFP(d_rows), dscores, F, K, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_embedding_grad(const long long* sorted_ids, const long long* order, const void* g, void* grad, int grad_bf16, int F, int C,
+                                   void* stream) {
+  if (F <= 0) return 0;
+  if (C % 8) return -42;
+  if (grad_bf16) embedding_grad_kernel<__nv_bfloat16><<<F, 128, 0, S_(stream)>>>(sorted_ids, order, CBFP(g), BFP(grad), F, C);
+  else embedding_grad_kernel<float><<<F, 128, 0, S_(stream)>>>(sorted_ids, order, CBFP(g), reinterpret_cast<float*>(grad), F, C);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

@@ -26,6 +26,7 @@ from lyra_b200.config import Mode, ModelConfig
 from lyra_b200.nn.params import ArraySpec, Tag, init_weights, map_with_path
 from lyra_b200.nn.quant import QArray, dequantize, quantize, qupdate
 from lyra_b200.ops import api as ops
+from lyra_b200.ops import reference as ref_ops
 from lyra_b200.training.probe import NO_PROBE, Probe
 from lyra_b200.utils.nvtx import scope
 
@@ -288,7 +289,7 @@ def calculate_aux_loss(router_logits, expert_indices, config: ModelConfig, *, pr
     F_, E = router_logits.shape
     K = expert_indices.shape[-1]
     logits = router_logits.float()
-    counts = torch.bincount(expert_indices.reshape(-1), minlength=E).float()
+    counts = ref_ops.count_ids(expert_indices, E).float()
     assigned = torch.softmax(logits, dim=-1).sum(0) / F_
     assignments = (counts / (F_ * K)).detach()
     lb_term = E * (assigned * assignments).sum()
@@ -320,7 +321,7 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
     aux = calculate_aux_loss(logits, idx, c, probe=probe)
     if probe.enabled:
         probe.routing("routing", router_logits=logits, expert_scores=scores,
-                      group_sizes=torch.bincount(idx.reshape(-1), minlength=c.n_routed_experts),
+                      group_sizes=ref_ops.count_ids(idx, c.n_routed_experts),
                       n_experts=c.n_routed_experts, n_active=k)
     if c.n_shared_experts:
         shared = torch.arange(c.n_routed_experts, c.n_experts, device=idx.device, dtype=idx.dtype)

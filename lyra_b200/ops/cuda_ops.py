@@ -309,7 +309,7 @@ def moe_routing_layout(indices: torch.Tensor, n_experts: int):
     F_, K = indices.shape
     flat = indices.reshape(-1)
     R = ((F_ * K + 127) // 128 + n_experts) * 128
-    counts = torch.bincount(flat, minlength=n_experts)
+    counts = ref.count_ids(flat, n_experts)
     padded = (counts + 127) // 128 * 128
     offsets = torch.zeros(n_experts + 1, dtype=torch.int64, device=flat.device)
     offsets[1:] = torch.cumsum(padded, 0)

@@ -102,17 +102,49 @@ class _QKNormRope(torch.autograd.Function):
         return dx.to(x.dtype), dscale.to(scale.dtype), None, None, None
 
 
+class _QKNormRopeKernel(torch.autograd.Function):
+    """Kernel-backed version of :class:`_QKNormRope` for contiguous bf16 ``[B, T, N, D]`` inputs."""
+
+    @staticmethod
+    def forward(ctx, x, scale, cos, sin, eps):
+        D = x.shape[-1]
+        c2, s2 = cos.reshape(-1, D // 2).contiguous(), sin.reshape(-1, D // 2).contiguous()
+        ctx.save_for_backward(x, scale, c2, s2)
+        ctx.eps = eps
+        return _qknorm_rope_kernel(x, scale, c2, s2, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, scale, c2, s2 = ctx.saved_tensors
+        B, T, N, D = x.shape
+        dy = dy.contiguous()
+        dx = torch.empty_like(x)
+        max_blocks = 1184
+        partial = torch.empty(max_blocks, D, dtype=torch.float32, device=x.device) if scale is not None else None
+        sc = scale.detach().float().contiguous() if scale is not None else None
+        lib = _lib()
+        lib.lyra_qknorm_rope_bwd.restype = c_int
+        used = lib.lyra_qknorm_rope_bwd(ptr(x), ptr(sc), ptr(c2), ptr(s2), ptr(dy), ptr(dx), ptr(partial), c_int(B), c_int(T), c_int(N), c_int(D),
+                                        c_float(ctx.eps), c_int(max_blocks), native.stream_ptr())
+        if used < 0:
+            raise native.NativeError(f"qknorm_rope_bwd failed with code {used}")
+        native.count_launch()
+        dscale = partial[:used].sum(0).to(scale.dtype) if scale is not None else None
+        return dx, dscale, None, None, None
+
+
 def qk_norm_rope(q, k, qscale, kscale, cos, sin, eps):
-    if q.dtype == BF16 and _has("lyra_qknorm_rope_fwd") and not (q.requires_grad or k.requires_grad) and q.is_contiguous() and k.is_contiguous():
-        return _qknorm_rope_kernel(q, qscale, cos, sin, eps), _qknorm_rope_kernel(k, kscale, cos, sin, eps)
+    ok = (q.dtype == BF16 and k.dtype == BF16 and _has("lyra_qknorm_rope_bwd") and q.is_contiguous() and k.is_contiguous()
+          and q.shape[-1] in (64, 128) and q.dim() == 4)
+    if ok:
+        return _QKNormRopeKernel.apply(q, qscale, cos, sin, eps), _QKNormRopeKernel.apply(k, kscale, cos, sin, eps)
     return _QKNormRope.apply(q, qscale, cos, sin, eps), _QKNormRope.apply(k, kscale, cos, sin, eps)
 
 
-def _qknorm_rope_kernel(x, scale, cos, sin, eps):
+def _qknorm_rope_kernel(x, scale, c2, s2, eps):
     B, T, N, D = x.shape
     y = torch.empty_like(x)
     sc = scale.detach().float().contiguous() if scale is not None else None
-    c2, s2 = cos.reshape(-1, D // 2).contiguous(), sin.reshape(-1, D // 2).contiguous()
     native.check(_lib().lyra_qknorm_rope_fwd(ptr(x), ptr(sc), ptr(c2), ptr(s2), ptr(y), c_int(B), c_int(T), c_int(N), c_int(D), c_float(eps),
                                              native.stream_ptr()), "qknorm_rope_fwd")
     native.count_launch()
@@ -120,9 +152,56 @@ def _qknorm_rope_kernel(x, scale, cos, sin, eps):
 
 
 # --------------------------------------------------------------------------- output gate + XSA
+class _GateXSAKernel(torch.autograd.Function):
+    """``t, v`` token-major ``[B, T, N, D]`` bf16; ``logits [B, T, Nq]`` bf16 or None; ``alpha [Nq]`` or None."""
+
+    @staticmethod
+    def forward(ctx, t, logits, v, alpha):
+        B, T, Nq, D = t.shape
+        Nkv = v.shape[2]
+        out = torch.empty_like(t)
+        al = alpha.detach().float().contiguous() if alpha is not None else None
+        native.check(_lib().lyra_gate_xsa_fwd(ptr(t), ptr(logits), ptr(v), ptr(al), ptr(out), c_ll(B * T), c_int(Nq), c_int(Nkv), c_int(D),
+                                              native.stream_ptr()), "gate_xsa_fwd")
+        native.count_launch()
+        ctx.save_for_backward(t, logits, v, alpha)
+        return out
+
+    @staticmethod
+    def backward(ctx, d_out):
+        t, logits, v, alpha = ctx.saved_tensors
+        B, T, Nq, D = t.shape
+        Nkv = v.shape[2]
+        d_out = d_out.contiguous()
+        d_t = torch.empty_like(t)
+        d_logits = torch.empty_like(logits) if logits is not None else None
+        d_v = torch.empty_like(v) if alpha is not None else None
+        max_blocks = 1184
+        partial = torch.empty(max_blocks, Nq, dtype=torch.float32, device=t.device) if alpha is not None else None
+        al = alpha.detach().float().contiguous() if alpha is not None else None
+        lib = _lib()
+        lib.lyra_gate_xsa_bwd.restype = c_int
+        used = lib.lyra_gate_xsa_bwd(ptr(t), ptr(logits), ptr(v), ptr(al), ptr(d_out), ptr(d_t), ptr(d_logits), ptr(d_v), ptr(partial), c_ll(B * T),
+                                     c_int(Nq), c_int(Nkv), c_int(D), c_int(max_blocks), native.stream_ptr())
+        if used < 0:
+            raise native.NativeError(f"gate_xsa_bwd failed with code {used}")
+        native.count_launch()
+        d_alpha = partial[:used].sum(0).to(alpha.dtype) if alpha is not None else None
+        return d_t, d_logits, d_v, d_alpha
+
+
 def gate_xsa(t, h, w_gate, v, xsa_alpha):
-    """See ``ops.api.gate_xsa``. Autograd-differentiable composition; heads-first ``t [B, Nq, T, D]``."""
+    """See ``ops.api.gate_xsa``. Heads-first ``t [B, Nq, T, D]``; fused kernel when the storage is token-major bf16."""
     dtype = t.dtype
+    tt, vt = t.transpose(1, 2), v.transpose(1, 2)
+    if (dtype == BF16 and _has("lyra_gate_xsa_fwd") and tt.is_contiguous() and vt.is_contiguous() and t.shape[-1] in (64, 128)
+            and (w_gate is None or w_gate.shape[1] % 8 == 0)):
+        logits = None
+        if w_gate is not None:
+            from lyra_b200.ops import cuda_ops
+
+            logits = cuda_ops.linear(h, w_gate, None).contiguous()
+        return _GateXSAKernel.apply(tt, logits, vt, xsa_alpha).transpose(1, 2)
     if w_gate is not None:
         from lyra_b200.ops import cuda_ops
 
@@ -186,7 +265,7 @@ class Embedding(torch.autograd.Function):
     def forward(ctx, emb, tokens):
         ctx.save_for_backward(tokens)
         ctx.emb = emb
-        return emb.detach()[tokens]
+        return emb.detach()[tokens].to(BF16)  # bf16 activations, so the incoming gradient is bf16 too
 
     @staticmethod
     def backward(ctx, g):
@@ -194,18 +273,23 @@ class Embedding(torch.autograd.Function):
         emb = ctx.emb
         flat = tokens.reshape(-1).long()
         g2 = g.reshape(flat.shape[0], -1)
-        # deterministic: sorted segment-sum in fp32 (lyra/kernels/embs.py:22-29), accumulated into the gradient buffer
-        order = torch.argsort(flat, stable=True)
-        sorted_ids = flat[order]
-        uniq, counts = torch.unique_consecutive(sorted_ids, return_counts=True)
-        seg = torch.repeat_interleave(torch.arange(uniq.numel(), device=flat.device), counts)
-        sums = torch.zeros(uniq.numel(), g2.shape[1], dtype=torch.float32, device=g.device)
-        sums.index_add_(0, seg, g2[order].float())
         if emb.grad is None:
             from lyra_b200.ops import cuda_ops
 
             emb.grad = torch.zeros(emb.shape, dtype=cuda_ops.GRAD_DTYPE, device=emb.device)
-        emb.grad.index_add_(0, uniq, sums.to(emb.grad.dtype))
+        # deterministic: sorted segment-sum in fp32 (lyra/kernels/embs.py:22-29), accumulated into the gradient buffer
+        sorted_ids, order = torch.sort(flat, stable=True)
+        if g2.dtype == BF16 and _has("lyra_embedding_grad") and g2.shape[1] % 8 == 0 and emb.grad.dtype in (BF16, torch.float32):
+            g2 = g2.contiguous()
+            native.check(_lib().lyra_embedding_grad(ptr(sorted_ids), ptr(order), ptr(g2), ptr(emb.grad), c_int(int(emb.grad.dtype == BF16)),
+                                                    c_int(flat.shape[0]), c_int(g2.shape[1]), native.stream_ptr()), "embedding_grad")
+            native.count_launch()
+        else:
+            uniq, counts = torch.unique_consecutive(sorted_ids, return_counts=True)
+            seg = torch.repeat_interleave(torch.arange(uniq.numel(), device=flat.device), counts)
+            sums = torch.zeros(uniq.numel(), g2.shape[1], dtype=torch.float32, device=g.device)
+            sums.index_add_(0, seg, g2[order].float())
+            emb.grad.index_add_(0, uniq, sums.to(emb.grad.dtype))
         return None, None
 
 

@@ -68,7 +68,7 @@ def ptr(t: torch.Tensor | None) -> c_void_p:
 
 
 def stream_ptr() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    return c_void_p(torch._C._cuda_getCurrentRawStream(torch.cuda.current_device()))
 
 
 _status: dict[int, torch.Tensor] = {}

@@ -138,3 +138,10 @@ def softcap_free_topk(logits: torch.Tensor, k: int):
 
 def yarn_concentration(rope_scale: float) -> float:
     return 0.1 * math.log(rope_scale) + 1.0 if rope_scale > 1.0 else 1.0
+
+
+def count_ids(ids: torch.Tensor, n: int) -> torch.Tensor:
+    """``bincount(ids, minlength=n)`` without the device-to-host synchronisation ``torch.bincount`` needs to size its
+    output (integer scatter-add: exact and order-independent)."""
+    out = torch.zeros(n, dtype=torch.int64, device=ids.device)
+    return out.scatter_add_(0, ids.reshape(-1).long(), torch.ones(ids.numel(), dtype=torch.int64, device=ids.device))

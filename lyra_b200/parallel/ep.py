@@ -148,7 +148,7 @@ class _Exchange:
         dev = indices.device
         flat = indices.reshape(-1)
         self.expert_of = flat.to(torch.int32).contiguous()
-        counts = torch.bincount(flat, minlength=self.E).to(torch.int32)
+        counts = ref.count_ids(flat, self.E).to(torch.int32)
         order = torch.argsort(flat, stable=True)
         starts = torch.cumsum(counts, 0) - counts
         rie = torch.empty_like(order)

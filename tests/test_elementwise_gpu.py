@@ -112,3 +112,49 @@ def test_fused_optimizer_matches_reference_step():
     m = optimizer_step_cuda(p1, grads, s1, 2, tcfg)
     assert not bool(m["grad_is_finite"]) and int(s1.adam_count) == 2
     assert all(torch.equal(before[p], p1[p]) for p in p1)
+
+
+@pytest.mark.parametrize("D,use_norm", [(128, True), (64, False)])
+def test_qk_norm_rope_kernel(D, use_norm):
+    from lyra_b200.ops import elementwise as ew
+
+    torch.manual_seed(3)
+    B, T, N = 2, 96, 4
+    q = torch.randn(B, T, N, D, device="cuda").bfloat16()
+    k = torch.randn(B, T, 2, D, device="cuda").bfloat16()
+    cos, sin = torch.rand(1, T, 1, D // 2, device="cuda"), torch.rand(1, T, 1, D // 2, device="cuda")
+    qs = (torch.rand(D, device="cuda") + 0.5) if use_norm else None
+    ks = (torch.rand(D, device="cuda") + 0.5) if use_norm else None
+    dq, dk = torch.randn_like(q), torch.randn_like(k)
+    res = []
+    for fn in (lambda *a: (ew._QKNormRope.apply(a[0], a[2], cos, sin, 1e-5), ew._QKNormRope.apply(a[1], a[3], cos, sin, 1e-5)),
+               lambda *a: ew.qk_norm_rope(a[0], a[1], a[2], a[3], cos, sin, 1e-5)):
+        ins = [q.clone().requires_grad_(True), k.clone().requires_grad_(True)] + [s.clone().requires_grad_(True) if s is not None else None for s in (qs, ks)]
+        oq, ok = fn(*ins)
+        torch.autograd.backward([oq, ok], [dq, dk])
+        res.append([oq, ok] + [i.grad for i in ins if i is not None])
+    for a, b in zip(*res):
+        assert _rel(b, a) < 1.5e-2
+
+
+@pytest.mark.parametrize("gate,xsa", [(True, True), (True, False), (False, True)])
+def test_gate_xsa_kernel(gate, xsa):
+    from lyra_b200.ops import api
+
+    torch.manual_seed(4)
+    B, T, Nq, Nkv, D, C = 2, 80, 8, 2, 128, 256
+    t = torch.randn(B, T, Nq, D, device="cuda").bfloat16().transpose(1, 2)
+    v = torch.randn(B, T, Nkv, D, device="cuda").bfloat16().transpose(1, 2)
+    h = torch.randn(B, T, C, device="cuda").bfloat16()
+    wg = (torch.randn(C, Nq, device="cuda") * 0.1) if gate else None
+    al = (torch.randn(Nq, device="cuda") * 0.5) if xsa else None
+    d = torch.randn(B, T, Nq, D, device="cuda").bfloat16().transpose(1, 2)
+    res = []
+    for impl in ("torch", "auto"):
+        ins = [x.clone().requires_grad_(True) if x is not None else None for x in (t, h, wg, v, al)]
+        out = api.gate_xsa(ins[0], ins[1], ins[2], ins[3], ins[4], impl)
+        out.backward(d)
+        res.append([out] + [i.grad for i in ins if i is not None and i.grad is not None])
+    assert len(res[0]) == len(res[1])
+    for a, b in zip(*res):
+        assert _rel(b, a) < 2.5e-2
