@@ -166,7 +166,7 @@ def main() -> None:
     n_params = param_count(ModelWeights.spec(mcfg))
     local_params = n_params / world if rt is not None else n_params
     tight = local_params * 14 > 150e9
-    cuda_ops.set_memory_mode(keep_shadows=not tight, grad_dtype=torch.bfloat16 if tight else torch.float32)
+    cuda_ops.set_memory_mode(keep_shadows=not tight, grad_dtype=torch.bfloat16 if tight else torch.float32, save_preact=not tight)
 
     shard_fn = rt.shard_info if rt is not None else None
     weights = ModelWeights.init(mcfg.seed, mcfg, device=device, shard_fn=shard_fn)

@@ -25,6 +25,8 @@ namespace lyra {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int GEMM_THREADS_AG = 256;   // + two warps that pull the B operand from peer GPUs (all-gather fused GEMM)
+constexpr int AG_MAX_RANKS = 16;
 
 enum GroupMode : int { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2, GROUP_BATCH = 3 };
 enum Epilogue : int { EPI_STORE = 0, EPI_SWIGLU = 1, EPI_CE_FWD = 2, EPI_CE_DZ = 3 };
@@ -54,6 +56,17 @@ struct GemmParams {
   float* ce_tgt;            // [M] target logit                          (EPI_CE_FWD)
   const float* ce_lse;      // [M] log-sum-exp                           (EPI_CE_DZ)
   const float* ce_gscale;   // device scalar multiplying dZ              (EPI_CE_DZ)
+  // all-gather fused mode (ag_world > 0): B's K-rows live in peer GPUs' memory; two extra warps per CTA copy them in
+  // 64-row slabs into the local B buffer (the one the TMA map points at) and publish one flag per slab; the TMA
+  // producer waits for the slab's flag before loading it. TMA only ever reads local memory.
+  int ag_world;                      // 0 = off
+  int ag_rows_per_rank;              // K-rows held by each rank (K for a single owner, K / world for row shards)
+  int ag_my_rank;
+  long long ag_row_bytes;            // bytes per K-row (ldb * 2)
+  const void* ag_src[AG_MAX_RANKS];  // per-rank base of its rows (row index local to the rank)
+  void* ag_dst;                      // local B buffer base
+  int* ag_flags;                     // [ceil(K / 64)] local flags
+  int ag_epoch;                      // value that marks a slab as landed in this call
   int* status;
 };
 
@@ -109,7 +122,7 @@ __device__ __forceinline__ float swiglu_act(float g, float l, float beta, float 
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS_AG, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
   constexpr int A_BYTES = BM * BK * 2;
   constexpr int B_BYTES = BN * BK * 2;
@@ -179,6 +192,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           } else {
             tma_load_3d(sa, &tma_a, bar, k0, t.m0, t.ga);
           }
+          if (p.ag_world > 0) {  // the slab must have landed in local memory before TMA reads it
+            const int* flag = p.ag_flags + kb;
+            const long long t0 = clock64();
+            int v;
+            do {
+              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+              if (v != p.ag_epoch && (clock64() - t0 > WAIT_LIMIT_CYCLES || *abortp)) {
+                atomicExch(p.status, STATUS_TIMEOUT_PEER);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+            } while (v != p.ag_epoch);
+            if (!ok) break;
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+          }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j) {
@@ -237,6 +266,34 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         }
         if (ok) tc_commit(smem_u32(&tfull_bar[acc]));
         ++tile_it;
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------------------------------------ peer copy warps (all-gather fused mode only)
+    if (p.ag_world > 0) {
+      const int n_slabs = (p.K + BK - 1) / BK;
+      const int t = threadIdx.x - 6 * 32;  // 0..63
+      for (int slab = blockIdx.x; slab < n_slabs; slab += gridDim.x) {
+        const int row0 = slab * BK;
+        const int owner = row0 / p.ag_rows_per_rank;
+        const int rows = min(BK, p.K - row0);
+        if (owner != p.ag_my_rank || p.ag_src[owner] != p.ag_dst) {
+          const long long bytes = (long long)rows * p.ag_row_bytes;
+          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.ag_src[owner]) +
+                                                            (long long)(row0 - owner * p.ag_rows_per_rank) * p.ag_row_bytes);
+          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.ag_dst) + (long long)row0 * p.ag_row_bytes);
+          const long long n16 = bytes / 16;
+          long long i = t;
+          for (; i + 3 * 64 < n16; i += 4 * 64) {  // four 16-byte loads in flight per thread
+            const uint4 a = src[i], b = src[i + 64], c = src[i + 128], d = src[i + 192];
+            dst[i] = a; dst[i + 64] = b; dst[i + 128] = c; dst[i + 192] = d;
+          }
+          for (; i < n16; i += 64) dst[i] = src[i];
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        asm volatile("bar.sync 2, 64;" ::: "memory");
+        if (t == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.ag_flags + slab), "r"(p.ag_epoch) : "memory");
       }
     }
   } else {
@@ -467,7 +524,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
   }
   int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
   if (grid <= 0) return 0;
-  kern<<<grid, GEMM_THREADS, smem, stream>>>(ta, tb, p);
+  if (p.ag_world > 0) grid = sm_count();  // every slab needs a copier even if there are few tiles
+  kern<<<grid, p.ag_world > 0 ? GEMM_THREADS_AG : GEMM_THREADS, smem, stream>>>(ta, tb, p);
   LYRA_CHECK_LAUNCH();
   return 0;
 }
@@ -500,7 +558,7 @@ extern "C" int lyra_gemm_bf16(
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = bias_group_stride;
   p.group_mode = group_mode; p.tile_group = tile_group; p.group_offsets = group_offsets; p.num_groups = G;
   p.n_split = n_split; p.swiglu_beta = swiglu_beta; p.swiglu_limit = swiglu_limit; p.status = status;
-  p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
+  p.ag_world = 0; p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.m_tiles = (M + BM - 1) / BM;
   if (epilogue == EPI_SWIGLU) p.n_tiles = (n_split + BN / 2 - 1) / (BN / 2);
   else p.n_tiles = (N + BN - 1) / BN;
@@ -564,6 +622,7 @@ extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long lo
   p.alpha = 1.f; p.beta = 0.f; p.bias = nullptr; p.bias_group_stride = 0;
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
+  p.ag_world = 0;
   p.raster_n_major = 1;
   p.ce_y = y; p.ce_part_m = part_m; p.ce_part_l = part_l; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_gscale = gscale;
   p.m_tiles = (M + BM - 1) / BM;
@@ -622,4 +681,42 @@ extern "C" int lyra_ce_merge(const float* part_m, const float* part_l, const flo
   lyra::ce_merge_kernel<<<(M + 7) / 8, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(part_m, part_l, tgt, lse, row_loss, M, n_tiles);
   LYRA_CHECK_LAUNCH();
   return 0;
+}
+
+
+// y[M, N] = x[M, K] @ W[K, N] where W's rows live on peer GPUs (all-gather fused into the GEMM). `w_local` is this
+// rank's full-size [K, N] buffer that the kernel fills (rows owned by this rank must already be in place when
+// src[my_rank] == w_local); `src[r]` is rank r's peer-mapped base of its rows. `flags` holds ceil(K/64) ints and
+// `epoch` must differ from the values left by earlier calls on the same flags.
+extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_local, long long ldw, const long long* src, int world, int my_rank,
+                                        int rows_per_rank, void* y, long long ldy, int M, int N, int K, float alpha, const float* bias,
+                                        int* flags, int epoch, int* status, void* stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((ldx % 8) || (ldw % 8) || (ldy % 8) || world > AG_MAX_RANKS || world < 1) return -10;
+  constexpr int BN = 256;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = y; p.Cin = nullptr; p.ldc = ldy; p.c_group_stride = 0; p.out_fp32 = 0;
+  p.alpha = alpha; p.beta = 0.f; p.bias = bias; p.bias_group_stride = 0;
+  p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
+  p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
+  p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
+  p.ag_world = world; p.ag_rows_per_rank = rows_per_rank; p.ag_my_rank = my_rank; p.ag_row_bytes = ldw * 2;
+  for (int r = 0; r < AG_MAX_RANKS; ++r) p.ag_src[r] = r < world ? reinterpret_cast<const void*>(src[r]) : nullptr;
+  p.ag_dst = w_local; p.ag_flags = flags; p.ag_epoch = epoch;
+  p.m_tiles = (M + BM - 1) / BM;
+  p.n_tiles = (N + BN - 1) / BN;
+  p.total_tiles = p.m_tiles * p.n_tiles;
+  CUtensorMap ta, tb;
+  {
+    uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, 1}, strides[2] = {(uint64_t)ldx * 2, (uint64_t)M * ldx * 2};
+    uint32_t box[3] = {64, BM, 1};
+    if (make_tmap(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
+  }
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, 1}, strides[2] = {(uint64_t)ldw * 2, (uint64_t)K * ldw * 2};
+    uint32_t box[3] = {64, BK, 1};
+    if (make_tmap(&tb, w_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
+  }
+  return launch_gemm<BN, false, true, EPI_STORE>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }

@@ -29,11 +29,13 @@ BF16 = torch.bfloat16
 _SHADOW: dict[int, tuple[int, torch.Tensor, weakref.ref]] = {}
 KEEP_SHADOWS = True  # False: cast at every use instead (for models whose bf16 copy does not fit beside the optimizer state)
 GRAD_DTYPE = torch.float32
+SAVE_PREACT = True   # keep SwiGLU pre-activations for backward; False recomputes them (one more up-projection GEMM, less memory)
 
 
-def set_memory_mode(keep_shadows: bool, grad_dtype: torch.dtype = torch.float32) -> None:
-    global KEEP_SHADOWS, GRAD_DTYPE
+def set_memory_mode(keep_shadows: bool, grad_dtype: torch.dtype = torch.float32, save_preact: bool | None = None) -> None:
+    global KEEP_SHADOWS, GRAD_DTYPE, SAVE_PREACT
     KEEP_SHADOWS, GRAD_DTYPE = keep_shadows, grad_dtype
+    SAVE_PREACT = keep_shadows if save_preact is None else save_preact
     if not keep_shadows:
         _SHADOW.clear()
 
@@ -159,18 +161,23 @@ class _LinearSwiglu(torch.autograd.Function):
         x2 = x.reshape(-1, C).contiguous()
         wb = bf16_weight(w_up).view(C, 2 * H)
         b = bias.detach().float().reshape(2 * H) if bias is not None else None
-        y = G.gemm_swiglu(x2, wb, bias=b, swiglu_beta=beta, swiglu_limit=limit)
-        ctx.save_for_backward(x2, w_up)
+        if SAVE_PREACT and x.requires_grad:
+            pre = G.gemm(x2, wb, b_mn=True, bias=b)
+            y = ew.swiglu_fwd(pre, beta, limit)
+            ctx.save_for_backward(x2, w_up, pre)
+        else:
+            y = G.gemm_swiglu(x2, wb, bias=b, swiglu_beta=beta, swiglu_limit=limit)
+            ctx.save_for_backward(x2, w_up)
         ctx.bias, ctx.beta, ctx.limit, ctx.lead = bias, beta, limit, lead
         return y.reshape(*lead, H)
 
     @staticmethod
     def backward(ctx, dy):
-        x2, w_up = ctx.saved_tensors
+        x2, w_up, *saved = ctx.saved_tensors
         C, _, H = w_up.shape
         wb = bf16_weight(w_up).view(C, 2 * H)
         b = ctx.bias.detach().float().reshape(2 * H) if ctx.bias is not None else None
-        pre = G.gemm(x2, wb, b_mn=True, bias=b)                      # recompute [M, 2H]
+        pre = saved[0] if saved else G.gemm(x2, wb, b_mn=True, bias=b)   # kept, or recomputed [M, 2H]
         dpre = ew.swiglu_bwd(pre, dy.reshape(-1, H).contiguous(), ctx.beta, ctx.limit)
         del pre
         dx = G.gemm(dpre, wb).reshape(*ctx.lead, C) if ctx.needs_input_grad[0] else None

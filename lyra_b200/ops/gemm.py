@@ -156,3 +156,33 @@ def grouped_wgrad(x: torch.Tensor, dy: torch.Tensor, group_offsets: torch.Tensor
          out.dtype == torch.float32, K, N, 0, 1.0, 1.0, None, 0, GROUP_K, num_groups, None, group_offsets, R,
          EPI_STORE, 0, 0.0, 0.0)
     return out
+
+
+def gemm_allgather(x: torch.Tensor, w_local: torch.Tensor, src_ptrs: list[int], my_rank: int, rows_per_rank: int, flags: torch.Tensor, epoch: int, *,
+                   alpha: float = 1.0, bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``x [M, K] @ W [K, N]`` where the rows of ``W`` live in peer GPUs' memory: the all-gather is fused into the GEMM.
+
+    ``w_local [K, N]`` is this rank's full-size bf16 buffer, filled by the kernel slab by slab (64 rows) while the
+    tensor cores already work on the slabs that have landed; ``src_ptrs[r]`` is the peer-mapped address of rank r's rows
+    (``rows_per_rank`` each; a single owner is ``rows_per_rank = K`` with the owner's address in slot 0). ``flags`` is an
+    int32 tensor with at least ``ceil(K / 64)`` entries; ``epoch`` must differ from call to call on the same flags.
+    After the call ``w_local`` holds the whole matrix and can be used by ordinary GEMMs."""
+    import ctypes
+
+    _check2d(x)
+    M, K = x.shape
+    Kw, N = w_local.shape
+    assert K == Kw and w_local.dtype == torch.bfloat16 and w_local.stride(1) == 1
+    assert flags.dtype == torch.int32 and flags.numel() >= (K + 63) // 64
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
+    lib = native.kernels()
+    fn = lib.lyra_gemm_allgather_bf16
+    fn.restype = c_int
+    arr = (ctypes.c_longlong * len(src_ptrs))(*src_ptrs)
+    rc = fn(ptr(x), c_ll(x.stride(0)), ptr(w_local), c_ll(w_local.stride(0)), arr, c_int(len(src_ptrs)), c_int(my_rank), c_int(rows_per_rank),
+            ptr(out), c_ll(out.stride(0)), c_int(M), c_int(N), c_int(K), c_float(alpha), ptr(bias), ptr(flags), c_int(epoch),
+            ptr(native.status_word()), native.stream_ptr())
+    native.check(rc, "lyra_gemm_allgather_bf16")
+    native.count_launch()
+    return out

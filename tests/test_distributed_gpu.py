@@ -80,3 +80,61 @@ def test_peer_memory_runtime_matches_collective_runtime(tmp_path):
         cos = {k: torch.nn.functional.cosine_similarity(p0[k].reshape(-1), p1[k].reshape(-1), dim=0).item() for k in p0 if p0[k].numel() >= 4096}
         bad = {k: v for k, v in cos.items() if v < 0.9}
         assert cos and not bad, bad
+
+
+def _ag_worker(rank, world, port, tmp):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from lyra_b200.ops import gemm as G, native
+        from lyra_b200.parallel.comm import SymmetricSlab
+
+        M, K, N = 1024, 2048, 1536
+        g = torch.Generator(device="cuda").manual_seed(7)
+        w_full = (torch.randn(K, N, device=device, generator=g) / 32).bfloat16()     # same on every rank
+        x = torch.randn(M, K, device=device, generator=torch.Generator(device="cuda").manual_seed(rank)).bfloat16()
+        slab = SymmetricSlab(K * N * 2, device, dist.group.WORLD.group_name)
+        w_local = slab.view(0, K * N, torch.bfloat16).view(K, N)
+        rows = K // world
+        results = {}
+        # (a) row-sharded: every rank owns K / world rows
+        w_local.zero_()
+        w_local[rank * rows:(rank + 1) * rows] = w_full[rank * rows:(rank + 1) * rows]
+        torch.cuda.synchronize(); dist.barrier()
+        flags = torch.zeros(64, dtype=torch.int32, device=device)
+        src = [p + r * rows * N * 2 for r, p in enumerate(slab.peer_ptrs)]
+        y = G.gemm_allgather(x, w_local, src, rank, rows, flags, epoch=1)
+        torch.cuda.synchronize(); native.check_status()
+        ref = x.float() @ w_full.float()
+        results["rows"] = ((y.float() - ref).norm() / ref.norm()).item()
+        results["rows_filled"] = bool(torch.equal(w_local, w_full))
+        dist.barrier()
+        # (b) single owner: rank 0 holds the whole matrix
+        w_local.zero_()
+        if rank == 0:
+            w_local.copy_(w_full)
+        torch.cuda.synchronize(); dist.barrier()
+        y = G.gemm_allgather(x, w_local, [slab.peer_ptrs[0]], 0 if rank == 0 else 1, K, flags, epoch=2)
+        torch.cuda.synchronize(); native.check_status()
+        results["owner"] = ((y.float() - ref).norm() / ref.norm()).item()
+        results["owner_filled"] = bool(torch.equal(w_local, w_full))
+        dist.barrier()
+        torch.save(results, f"{tmp}/ag{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_allgather_fused_gemm(tmp_path):
+    import torch.multiprocessing as mp
+
+    port = 29800 + os.getpid() % 90
+    mp.spawn(_ag_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        res = torch.load(tmp_path / f"ag{r}.pt", weights_only=False)
+        assert res["rows"] < 1e-2 and res["owner"] < 1e-2, res
+        assert res["rows_filled"] and res["owner_filled"], res
