@@ -689,15 +689,15 @@ extern "C" int lyra_ce_merge(const float* part_m, const float* part_l, const flo
 // src[my_rank] == w_local); `src[r]` is rank r's peer-mapped base of its rows. `flags` holds ceil(K/64) ints and
 // `epoch` must differ from the values left by earlier calls on the same flags.
 extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_local, long long ldw, const long long* src, int world, int my_rank,
-                                        int rows_per_rank, void* y, long long ldy, int M, int N, int K, float alpha, const float* bias,
-                                        int* flags, int epoch, int* status, void* stream) {
+                                        int rows_per_rank, void* y, const void* c_in, long long ldy, int M, int N, int K, float alpha, float beta,
+                                        const float* bias, int* flags, int epoch, int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((ldx % 8) || (ldw % 8) || (ldy % 8) || world > AG_MAX_RANKS || world < 1) return -10;
   constexpr int BN = 256;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.C = y; p.Cin = nullptr; p.ldc = ldy; p.c_group_stride = 0; p.out_fp32 = 0;
-  p.alpha = alpha; p.beta = 0.f; p.bias = bias; p.bias_group_stride = 0;
+  p.C = y; p.Cin = c_in; p.ldc = ldy; p.c_group_stride = 0; p.out_fp32 = 0;
+  p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = 0;
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
   p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;

@@ -75,6 +75,20 @@ def invalidate_shadows() -> None:
         _SHADOW[key] = (-1, shadow, ref)
 
 
+AG_HOOK = None  # set by the sharding runtime: callable(weight) -> pending fused all-gather description or None
+
+
+def _forward_gemm(x2: torch.Tensor, w: torch.Tensor, wb2d: torch.Tensor, **kw) -> torch.Tensor:
+    """``x2 @ wb2d`` for a forward pass. If ``w`` is a sharded weight whose rows still sit on its owner, the pull over
+    NVLink is fused into this GEMM (``gemm_allgather``) and the local copy is complete afterwards."""
+    info = AG_HOOK(w) if AG_HOOK is not None else None
+    if info is None:
+        return G.gemm(x2, wb2d, b_mn=True, **kw)
+    y = G.gemm_allgather(x2, wb2d, info["src"], info["my_rank"], wb2d.shape[0], info["flags"], info["epoch"], **kw)
+    info["done"]()
+    return y
+
+
 def _accumulate_wgrad(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor, alpha: float = 1.0) -> None:
     """``w.grad += alpha * a^T @ b`` with ``a [M, K_in]``, ``b [M, N_out]`` (both MN-major operands), in the GEMM epilogue."""
     shape2d = (a.shape[1], b.shape[1])
@@ -110,8 +124,8 @@ class _Linear(torch.autograd.Function):
             b = bias.detach().float().reshape(-1)
             if alpha != 1.0:
                 b = b * alpha
-        y = G.gemm(x2.contiguous(), wb, b_mn=True, alpha=alpha, beta=1.0 if res2 is not None else 0.0,
-                   c_in=res2.contiguous() if res2 is not None else None, bias=b)
+        y = _forward_gemm(x2.contiguous(), w, wb, alpha=alpha, beta=1.0 if res2 is not None else 0.0,
+                          c_in=res2.contiguous() if res2 is not None else None, bias=b)
         ctx.save_for_backward(x2, w)
         ctx.alpha, ctx.has_res, ctx.bias = alpha, residual is not None, bias
         ctx.lead = lead
@@ -162,10 +176,12 @@ class _LinearSwiglu(torch.autograd.Function):
         wb = bf16_weight(w_up).view(C, 2 * H)
         b = bias.detach().float().reshape(2 * H) if bias is not None else None
         if SAVE_PREACT and x.requires_grad:
-            pre = G.gemm(x2, wb, b_mn=True, bias=b)
+            pre = _forward_gemm(x2, w_up, wb, bias=b)
             y = ew.swiglu_fwd(pre, beta, limit)
             ctx.save_for_backward(x2, w_up, pre)
         else:
+            if AG_HOOK is not None and AG_HOOK(w_up) is not None:   # land the weight first; the SwiGLU-epilogue GEMM has no fused pull
+                _forward_gemm(x2[:128], w_up, wb)
             y = G.gemm_swiglu(x2, wb, bias=b, swiglu_beta=beta, swiglu_limit=limit)
             ctx.save_for_backward(x2, w_up)
         ctx.bias, ctx.beta, ctx.limit, ctx.lead = bias, beta, limit, lead

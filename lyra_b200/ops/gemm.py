@@ -159,7 +159,8 @@ def grouped_wgrad(x: torch.Tensor, dy: torch.Tensor, group_offsets: torch.Tensor
 
 
 def gemm_allgather(x: torch.Tensor, w_local: torch.Tensor, src_ptrs: list[int], my_rank: int, rows_per_rank: int, flags: torch.Tensor, epoch: int, *,
-                   alpha: float = 1.0, bias: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                   alpha: float = 1.0, beta: float = 0.0, c_in: torch.Tensor | None = None, bias: torch.Tensor | None = None,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ W [K, N]`` where the rows of ``W`` live in peer GPUs' memory: the all-gather is fused into the GEMM.
 
     ``w_local [K, N]`` is this rank's full-size bf16 buffer, filled by the kernel slab by slab (64 rows) while the
@@ -181,7 +182,7 @@ def gemm_allgather(x: torch.Tensor, w_local: torch.Tensor, src_ptrs: list[int], 
     fn.restype = c_int
     arr = (ctypes.c_longlong * len(src_ptrs))(*src_ptrs)
     rc = fn(ptr(x), c_ll(x.stride(0)), ptr(w_local), c_ll(w_local.stride(0)), arr, c_int(len(src_ptrs)), c_int(my_rank), c_int(rows_per_rank),
-            ptr(out), c_ll(out.stride(0)), c_int(M), c_int(N), c_int(K), c_float(alpha), ptr(bias), ptr(flags), c_int(epoch),
+            ptr(out), ptr(c_in), c_ll(out.stride(0)), c_int(M), c_int(N), c_int(K), c_float(alpha), c_float(beta), ptr(bias), ptr(flags), c_int(epoch),
             ptr(native.status_word()), native.stream_ptr())
     native.check(rc, "lyra_gemm_allgather_bf16")
     native.count_launch()

@@ -7,6 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 import torch.distributed as dist
@@ -45,6 +46,7 @@ class Comm:
         self.world, self.rank, self.device = rt.world, rt.rank, rt.device
         self.p2p = rt.implementation == "b200"
         self.entries = entries
+        self.entries_by_name = {name: (shape, owner) for name, shape, owner in entries}
         self.grad_dtype = grad_dtype
         gsize = torch.empty((), dtype=grad_dtype).element_size()
         self.w_dtype = BF16 if rt.mcfg.compute_dtype == BF16 or self.p2p else rt.mcfg.compute_dtype
@@ -73,6 +75,11 @@ class Comm:
         else:
             self.w_buf = torch.zeros(max(w_total, ALIGN), dtype=torch.uint8, device=self.device)
             self.g_buf = torch.zeros(max(g_total, ALIGN), dtype=torch.uint8, device=self.device)
+        # "fused": eligible weights are not pulled eagerly; the first forward GEMM that uses one pulls it inside the kernel
+        self.fused_gather = self.p2p and os.environ.get("LYRA_GATHER", "fused") == "fused"
+        self.pending: dict[str, bool] = {}
+        self.ag_flags: dict[str, torch.Tensor] = {}
+        self.ag_epoch = 0
         self._grad_views: dict[int, torch.Tensor] = {}
         self._reduced: dict[str, torch.Tensor] = {}
         for name, shape, owner in entries:
@@ -124,9 +131,13 @@ class Comm:
         self.barrier()                                           # owners have written their bf16 copies
         stream = nat.stream_ptr()
         order = sorted(range(len(self.entries)), key=lambda i: ((self.entries[i][2] - self.rank - 1) % self.world, i))
+        self.ag_epoch += 1
         for i in order:                                          # start with the next rank's leaves: spreads the load over owners
             name, shape, owner = self.entries[i]
             if owner == self.rank:
+                continue
+            if self.fused_gather and self._fusable(name, shape):
+                self.pending[name] = True
                 continue
             off, n = self.w_off[name], self.numel[name]
             nbytes = (n * 2 + 15) // 16 * 16
@@ -134,6 +145,34 @@ class Comm:
                                              ctypes.c_longlong(nbytes), stream), "p2p_copy")
             nat.count_launch()
         self.barrier()                                           # nobody overwrites a copy that is still being pulled
+
+    def _fusable(self, name: str, shape: tuple[int, ...]) -> bool:
+        """Weights consumed as the ``[K, N]`` operand of a forward linear: K rows of N contiguous columns, K % 64 == 0."""
+        leaf = name.split("#")[0].split("/")[-1]
+        if leaf in ("emb", "unemb"):
+            return False
+        return len(shape) in (2, 3) and shape[0] % 64 == 0 and math.prod(shape[1:]) % 8 == 0
+
+    def ag_info(self, name: str):
+        """Description of the pending fused pull of ``name`` for ``ops.gemm.gemm_allgather``, or None."""
+        if not self.pending.get(name):
+            return None
+        K = self.entries_by_name[name][0][0]
+        if name not in self.ag_flags:
+            self.ag_flags[name] = torch.zeros((K + 63) // 64, dtype=torch.int32, device=self.device)
+        owner = self.owner[name]
+        return {"src": [self.w_slab.peer_ptrs[owner] + self.w_off[name]], "my_rank": 1, "flags": self.ag_flags[name], "epoch": self.ag_epoch,
+                "done": lambda: self.pending.__setitem__(name, False)}
+
+    def finish_pending(self) -> None:
+        """Pulls whatever was not touched by a forward pass (e.g. before a checkpoint of compute copies or an eval of part of the model)."""
+        nat = self.native
+        for name, todo in list(self.pending.items()):
+            if todo:
+                off, n, owner = self.w_off[name], self.numel[name], self.owner[name]
+                nat.check(self.lib.lyra_p2p_copy(ctypes.c_void_p(self.w_buf.data_ptr() + off), ctypes.c_void_p(self.w_slab.peer_ptrs[owner] + off),
+                                                 ctypes.c_longlong((n * 2 + 15) // 16 * 16), nat.stream_ptr()), "p2p_copy")
+                self.pending[name] = False
 
     # ------------------------------------------------------------------ gradients: everyone -> owner
     @torch.no_grad()
@@ -147,6 +186,8 @@ class Comm:
                     out[name] = g
             return out
         nat = self.native
+        if self.fused_gather:
+            self.finish_pending()                                # a leaf no forward touched is pulled before its owner may rewrite it
         self.barrier()                                           # every rank finished accumulating
         stream = nat.stream_ptr()
         in_bf16 = int(self.grad_dtype == BF16)

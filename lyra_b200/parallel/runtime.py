@@ -174,7 +174,14 @@ class Runtime:
             except Exception:
                 pass
             self._views[name] = w
+        self._name_of_view = {id(w): name for name, w in self._views.items()}
+        if self._comm.p2p:
+            cuda_ops.AG_HOOK = self._ag_hook
         self.refresh_weights()
+
+    def _ag_hook(self, w):
+        name = self._name_of_view.get(id(w))
+        return self._comm.ag_info(name) if name is not None else None
 
     def _master_of(self, name: str) -> torch.Tensor:
         if name in self._shared:
