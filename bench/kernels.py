@@ -1,7 +1,8 @@
 """Per-kernel device timings against the measured roofline denominators.
 
     python bench/kernels.py gemm            # tcgen05 GEMM family vs torch.matmul (cuBLAS)
-    python bench/kernels.py all
+    python bench/kernels.py attention | ce | elementwise | decode | all
+    python bench/kernels.py one <case>      # three launches of one small case, for a profiler capture (cases: see ONE)
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, an L2 flush (a 256 MB write) between
 timed runs, median of the timed runs. Peaks come from MEASURED_PEAKS.json at the repository root when it
@@ -114,8 +115,154 @@ def bench_attention():
 BENCHES["attention"] = bench_attention
 
 
+def bench_ce():
+    """Fused linear + cross-entropy (logits never stored) against torch's matmul + cross_entropy."""
+    from lyra_b200.ops import cuda_ops
+
+    for (M, C, V) in [(8192, 2048, 200064), (8192, 4096, 200064)]:
+        x = (torch.randn(M, C, device="cuda") / 4).bfloat16().requires_grad_()
+        w = (torch.randn(C, V, device="cuda") / 64).bfloat16().requires_grad_()
+        y = torch.randint(0, V - 64, (M,), device="cuda")
+        fl = 2.0 * M * C * V
+
+        def fwd():
+            with torch.no_grad():
+                return cuda_ops.linear_cross_entropy(x, w, y, V - 64)
+
+        def fwd_bwd():
+            x.grad = None
+            w.grad = None
+            cuda_ops.linear_cross_entropy(x, w, y, V - 64).backward()
+
+        report(f"linear-CE fwd M{M} C{C} V{V}", time_ms(fwd, iters=5), fl)
+        report(f"linear-CE fwd+bwd M{M} C{C} V{V}", time_ms(fwd_bwd, iters=5), 4.0 * fl)   # fwd + recompute + dX + dW
+        del x, w
+
+
+BENCHES["ce"] = bench_ce
+
+
+def bench_elementwise():
+    """Bandwidth-bound kernels: bytes are the algorithmic minimum (each tensor read or written once)."""
+    from lyra_b200.ops import elementwise as E
+
+    M, C = 32768, 4096
+    x = torch.randn(M, C, device="cuda").bfloat16()
+    scale = torch.ones(C, device="cuda")
+    dy = torch.randn(M, C, device="cuda").bfloat16()
+    report(f"rmsnorm fwd M{M} C{C}", time_ms(lambda: E.RMSNorm.apply(x, scale, 1e-6)), bytes_=2.0 * M * C * 2)
+    xr = x.clone().requires_grad_()
+    sr = scale.clone().requires_grad_()
+    out = E.RMSNorm.apply(xr, sr, 1e-6)
+    report(f"rmsnorm bwd M{M} C{C}", time_ms(lambda: torch.autograd.grad(out, (xr, sr), dy, retain_graph=True)), bytes_=3.0 * M * C * 2)
+    H = 8192
+    pre = torch.randn(M // 2, 2 * H, device="cuda").bfloat16()
+    dact = torch.randn(M // 2, H, device="cuda").bfloat16()
+    report(f"swiglu fwd M{M // 2} H{H}", time_ms(lambda: E.swiglu_fwd(pre, 1.702, 7.0)), bytes_=3.0 * (M // 2) * H * 2)
+    report(f"swiglu bwd M{M // 2} H{H}", time_ms(lambda: E.swiglu_bwd(pre, dact, 1.702, 7.0)), bytes_=5.0 * (M // 2) * H * 2)
+
+
+BENCHES["elementwise"] = bench_elementwise
+
+
+def bench_decode():
+    """Single-token attention over a KV cache: bytes = visible K and V rows read once."""
+    from lyra_b200.nn.quant import quantize
+    from lyra_b200.ops import decode
+
+    for (B, Nq, Nkv, S, D, name) in [(64, 64, 8, 2048, 64, "gpt-oss heads"), (8, 32, 8, 16384, 128, "lyra-medium heads"), (1, 32, 8, 32768, 128, "single sequence")]:
+        q = torch.randn(B, Nq, 1, D, device="cuda").bfloat16()
+        k = torch.randn(B, Nkv, S, D, device="cuda").bfloat16()
+        v = torch.randn(B, Nkv, S, D, device="cuda").bfloat16()
+        sinks = torch.zeros(Nq, device="cuda")
+        pos = S - 1
+        for window in (0, 128):
+            n_keys = min(window, pos + 1) if window else pos + 1
+            report(f"decode attention bf16 cache {name} B{B} {Nq}q/{Nkv}kv hd{D} S{S} window{window}",
+                   time_ms(lambda: decode.decode_attention(q, k, v, sinks, D ** -0.5, window, pos)), bytes_=2.0 * B * Nkv * n_keys * D * 2)
+        k8 = quantize(k, torch.float8_e4m3fn, block=(1, D))
+        v8 = quantize(v, torch.float8_e4m3fn, block=(1, D))
+        report(f"decode attention fp8 cache {name} B{B} {Nq}q/{Nkv}kv hd{D} S{S} window0",
+               time_ms(lambda: decode.decode_attention(q, k8, v8, sinks, D ** -0.5, 0, pos)), bytes_=2.0 * B * Nkv * (pos + 1) * (D + 4))
+        del k, v, k8, v8
+
+
+BENCHES["decode"] = bench_decode
+
+
+def _one_gemm():
+    from lyra_b200.ops import gemm as G
+    x = torch.randn(8192, 4096, device="cuda").bfloat16()
+    w = torch.randn(4096, 8192, device="cuda").bfloat16()
+    return lambda: G.gemm(x, w, b_mn=True)
+
+
+def _one_attention(backward: bool, window: int = 0):
+    from lyra_b200.ops import attention as A
+    B, Nq, Nkv, T, D = 2, 32, 8, 4096, 128
+    q, k, v, do = (torch.randn(B, T, n, D, device="cuda").bfloat16().transpose(1, 2) for n in (Nq, Nkv, Nkv, Nq))
+    sinks = torch.zeros(Nq, device="cuda")
+    out, lse = A.flash_fwd(q, k, v, sinks, D ** -0.5, window)
+    if backward:
+        return lambda: A.flash_bwd(q, k, v, out, do, lse, sinks, D ** -0.5, window)
+    return lambda: A.flash_fwd(q, k, v, sinks, D ** -0.5, window)
+
+
+def _one_ce():
+    from lyra_b200.ops import cuda_ops
+    M, C, V = 4096, 2048, 200064
+    x = (torch.randn(M, C, device="cuda") / 4).bfloat16().requires_grad_()
+    w = (torch.randn(C, V, device="cuda") / 64).bfloat16().requires_grad_()
+    y = torch.randint(0, V - 64, (M,), device="cuda")
+    return lambda: cuda_ops.linear_cross_entropy(x, w, y, V - 64).backward()
+
+
+def _one_rmsnorm():
+    from lyra_b200.ops import elementwise as E
+    x = torch.randn(32768, 4096, device="cuda").bfloat16()
+    scale = torch.ones(4096, device="cuda")
+    return lambda: E.RMSNorm.apply(x, scale, 1e-6)
+
+
+def _one_moe():
+    from lyra_b200.ops import gemm as G
+    M, Eg, K, H = 32768, 16, 2048, 2048
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(Eg, K, 2 * H, device="cuda") / 32).bfloat16()
+    tg = torch.arange(M // 128, device="cuda", dtype=torch.int32) // (M // 128 // Eg)
+    return lambda: G.grouped_gemm(x, w, tg, swiglu=True)
+
+
+def _one_decode():
+    from lyra_b200.ops import decode
+    B, Nq, Nkv, S, D = 16, 32, 8, 8192, 128
+    q = torch.randn(B, Nq, 1, D, device="cuda").bfloat16()
+    k = torch.randn(B, Nkv, S, D, device="cuda").bfloat16()
+    v = torch.randn(B, Nkv, S, D, device="cuda").bfloat16()
+    sinks = torch.zeros(Nq, device="cuda")
+    return lambda: decode.decode_attention(q, k, v, sinks, D ** -0.5, 0, S - 1)
+
+
+ONE = {"gemm": _one_gemm, "flash_fwd": lambda: _one_attention(False), "flash_bwd": lambda: _one_attention(True),
+       "flash_fwd_window": lambda: _one_attention(False, 128), "ce": _one_ce, "rmsnorm": _one_rmsnorm, "moe_up": _one_moe, "decode": lambda: _one_decode()}
+
+
+def run_one(case: str) -> None:
+    """Three launches of one case (inputs larger than L2 in total, well under 1 GB resident), then a synchronize."""
+    fn = ONE[case]()
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    from lyra_b200.ops import native
+    native.check_status()
+    print(json.dumps({"case": case, "ok": True}))
+
+
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "all"
+    if which == "one":
+        run_one(sys.argv[2])
+        sys.exit(0)
     for name, fn in BENCHES.items():
         if which in ("all", name):
             fn()

@@ -51,7 +51,17 @@ __device__ __forceinline__ bool wait_flag(const int* flag, int value) {
 
 // ------------------------------------------------------------------------------------------------ copies / reductions
 __global__ void p2p_copy_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long n16) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (long long)gridDim.x * blockDim.x) dst[i] = src[i];
+  // four independent 16-byte loads per thread and step: NVLink reads take microseconds, so bytes in flight set the rate
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    const uint4 a = src[i], b = src[i + stride], c = src[i + 2 * stride], d = src[i + 3 * stride];
+    dst[i] = a;
+    dst[i + stride] = b;
+    dst[i + 2 * stride] = c;
+    dst[i + 3 * stride] = d;
+  }
+  for (; i < n16; i += stride) dst[i] = src[i];
 }
 
 // fp32 or bf16 inputs on every rank, fp32 (or bf16) output; 8 elements per thread per step.

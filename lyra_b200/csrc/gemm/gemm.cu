@@ -25,7 +25,7 @@ namespace lyra {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
-constexpr int GEMM_THREADS_AG = 256;   // + two warps that pull the B operand from peer GPUs (all-gather fused GEMM)
+constexpr int GEMM_THREADS_AG = 320;   // + four warps that pull the B operand from peer GPUs (all-gather fused GEMM)
 constexpr int AG_MAX_RANKS = 16;
 
 enum GroupMode : int { GROUP_NONE = 0, GROUP_M = 1, GROUP_K = 2, GROUP_BATCH = 3 };
@@ -194,17 +194,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           }
           if (p.ag_world > 0) {  // the slab must have landed in local memory before TMA reads it
             const int* flag = p.ag_flags + kb;
+            const int want = p.ag_epoch * int((p.ag_row_bytes / 2 + 1023) / 1024);
             const long long t0 = clock64();
             int v;
             do {
               asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-              if (v != p.ag_epoch && (clock64() - t0 > WAIT_LIMIT_CYCLES || *abortp)) {
+              if (v < want && (clock64() - t0 > WAIT_LIMIT_CYCLES || *abortp)) {
                 atomicExch(p.status, STATUS_TIMEOUT_PEER);
                 abort_flag = 1;
                 ok = false;
                 break;
               }
-            } while (v != p.ag_epoch);
+            } while (v < want);
             if (!ok) break;
             asm volatile("fence.proxy.async.global;" ::: "memory");
           }
@@ -271,29 +272,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   } else if (warp >= 6) {
     // ------------------------------------------------------------ peer copy warps (all-gather fused mode only)
     if (p.ag_world > 0) {
+      // Work unit: a piece = 64 K-rows x AG_PIECE_COLS columns. Pieces are dealt round-robin over all CTAs in K order, so
+      // the first slabs complete first; each finished piece bumps its slab's counter, a slab is ready at epoch * pieces.
+      constexpr int AG_PIECE_COLS = 1024;                        // elements; 2 KB per row
       const int n_slabs = (p.K + BK - 1) / BK;
-      const int t = threadIdx.x - 6 * 32;  // 0..63
-      for (int slab = blockIdx.x; slab < n_slabs; slab += gridDim.x) {
+      const int row_elems = int(p.ag_row_bytes / 2);
+      const int pps = (row_elems + AG_PIECE_COLS - 1) / AG_PIECE_COLS;
+      const int t = threadIdx.x - 6 * 32;  // 0..127
+      for (int piece = blockIdx.x; piece < n_slabs * pps; piece += gridDim.x) {
+        const int slab = piece / pps, pc = piece - slab * pps;
         const int row0 = slab * BK;
         const int owner = row0 / p.ag_rows_per_rank;
         const int rows = min(BK, p.K - row0);
         if (owner != p.ag_my_rank || p.ag_src[owner] != p.ag_dst) {
-          const long long bytes = (long long)rows * p.ag_row_bytes;
-          const uint4* src = reinterpret_cast<const uint4*>(static_cast<const uint8_t*>(p.ag_src[owner]) +
-                                                            (long long)(row0 - owner * p.ag_rows_per_rank) * p.ag_row_bytes);
-          uint4* dst = reinterpret_cast<uint4*>(static_cast<uint8_t*>(p.ag_dst) + (long long)row0 * p.ag_row_bytes);
-          const long long n16 = bytes / 16;
-          long long i = t;
-          for (; i + 3 * 64 < n16; i += 4 * 64) {  // four 16-byte loads in flight per thread
-            const uint4 a = src[i], b = src[i + 64], c = src[i + 128], d = src[i + 192];
-            dst[i] = a; dst[i + 64] = b; dst[i + 128] = c; dst[i + 192] = d;
+          const int col0 = pc * AG_PIECE_COLS;
+          const int v_per_row = min(AG_PIECE_COLS, row_elems - col0) / 8;      // uint4 per row of this piece
+          const uint8_t* sbase = static_cast<const uint8_t*>(p.ag_src[owner]) + (long long)(row0 - owner * p.ag_rows_per_rank) * p.ag_row_bytes + col0 * 2;
+          uint8_t* dbase = static_cast<uint8_t*>(p.ag_dst) + (long long)row0 * p.ag_row_bytes + col0 * 2;
+          const int total = rows * v_per_row;
+          // NVLink round trips are microseconds: 16 loads of 16 bytes in flight per thread (32 KB per CTA) hide them
+          for (int i0 = t; i0 < total; i0 += 128 * 16) {
+            uint4 v[16];
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const int i = i0 + u * 128;
+              if (i < total) v[u] = *reinterpret_cast<const uint4*>(sbase + (long long)(i / v_per_row) * p.ag_row_bytes + (i % v_per_row) * 16);
+            }
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {
+              const int i = i0 + u * 128;
+              if (i < total) *reinterpret_cast<uint4*>(dbase + (long long)(i / v_per_row) * p.ag_row_bytes + (i % v_per_row) * 16) = v[u];
+            }
           }
-          for (; i < n16; i += 64) dst[i] = src[i];
         }
         __threadfence();
         asm volatile("fence.proxy.async.global;" ::: "memory");
-        asm volatile("bar.sync 2, 64;" ::: "memory");
-        if (t == 0) asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p.ag_flags + slab), "r"(p.ag_epoch) : "memory");
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (t == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_flags + slab) : "memory");
       }
     }
   } else {
@@ -687,7 +702,7 @@ extern "C" int lyra_ce_merge(const float* part_m, const float* part_l, const flo
 // y[M, N] = x[M, K] @ W[K, N] where W's rows live on peer GPUs (all-gather fused into the GEMM). `w_local` is this
 // rank's full-size [K, N] buffer that the kernel fills (rows owned by this rank must already be in place when
 // src[my_rank] == w_local); `src[r]` is rank r's peer-mapped base of its rows. `flags` holds ceil(K/64) ints and
-// `epoch` must differ from the values left by earlier calls on the same flags.
+// `epoch` counts the calls made on these flags (1, 2, ...; the flags start at zero and each call adds one per piece).
 extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_local, long long ldw, const long long* src, int world, int my_rank,
                                         int rows_per_rank, void* y, const void* c_in, long long ldy, int M, int N, int K, float alpha, float beta,
                                         const float* bias, int* flags, int epoch, int* status, void* stream) {

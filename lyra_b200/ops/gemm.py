@@ -166,7 +166,8 @@ def gemm_allgather(x: torch.Tensor, w_local: torch.Tensor, src_ptrs: list[int], 
     ``w_local [K, N]`` is this rank's full-size bf16 buffer, filled by the kernel slab by slab (64 rows) while the
     tensor cores already work on the slabs that have landed; ``src_ptrs[r]`` is the peer-mapped address of rank r's rows
     (``rows_per_rank`` each; a single owner is ``rows_per_rank = K`` with the owner's address in slot 0). ``flags`` is an
-    int32 tensor with at least ``ceil(K / 64)`` entries; ``epoch`` must differ from call to call on the same flags.
+    int32 tensor with at least ``ceil(K / 64)`` entries, zero before the first call; ``epoch`` is the number of this call on
+    those flags (1, 2, ...), always with the same ``N``.
     After the call ``w_local`` holds the whole matrix and can be used by ordinary GEMMs."""
     import ctypes
 

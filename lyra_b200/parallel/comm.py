@@ -79,7 +79,7 @@ class Comm:
         self.fused_gather = self.p2p and os.environ.get("LYRA_GATHER", "fused") == "fused"
         self.pending: dict[str, bool] = {}
         self.ag_flags: dict[str, torch.Tensor] = {}
-        self.ag_epoch = 0
+        self.ag_calls: dict[str, int] = {}
         self._grad_views: dict[int, torch.Tensor] = {}
         self._reduced: dict[str, torch.Tensor] = {}
         for name, shape, owner in entries:
@@ -131,7 +131,6 @@ class Comm:
         self.barrier()                                           # owners have written their bf16 copies
         stream = nat.stream_ptr()
         order = sorted(range(len(self.entries)), key=lambda i: ((self.entries[i][2] - self.rank - 1) % self.world, i))
-        self.ag_epoch += 1
         for i in order:                                          # start with the next rank's leaves: spreads the load over owners
             name, shape, owner = self.entries[i]
             if owner == self.rank:
@@ -160,9 +159,16 @@ class Comm:
         K = self.entries_by_name[name][0][0]
         if name not in self.ag_flags:
             self.ag_flags[name] = torch.zeros((K + 63) // 64, dtype=torch.int32, device=self.device)
+            self.ag_calls[name] = 0
         owner = self.owner[name]
-        return {"src": [self.w_slab.peer_ptrs[owner] + self.w_off[name]], "my_rank": 1, "flags": self.ag_flags[name], "epoch": self.ag_epoch,
-                "done": lambda: self.pending.__setitem__(name, False)}
+
+        def done():
+            self.pending[name] = False
+            self.ag_calls[name] += 1
+
+        # the kernel's slab counters grow by one per piece and call, so the epoch is this leaf's own call number
+        return {"src": [self.w_slab.peer_ptrs[owner] + self.w_off[name]], "my_rank": 1, "flags": self.ag_flags[name],
+                "epoch": self.ag_calls[name] + 1, "done": done}
 
     def finish_pending(self) -> None:
         """Pulls whatever was not touched by a forward pass (e.g. before a checkpoint of compute copies or an eval of part of the model)."""
