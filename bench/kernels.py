@@ -121,18 +121,18 @@ def bench_ce():
 
     for (M, C, V) in [(8192, 2048, 200064), (8192, 4096, 200064)]:
         x = (torch.randn(M, C, device="cuda") / 4).bfloat16().requires_grad_()
-        w = (torch.randn(C, V, device="cuda") / 64).bfloat16().requires_grad_()
+        w = (torch.randn(V, C, device="cuda") / 64).requires_grad_()   # [padded vocabulary, C], as the model stores it
         y = torch.randint(0, V - 64, (M,), device="cuda")
         fl = 2.0 * M * C * V
 
         def fwd():
             with torch.no_grad():
-                return cuda_ops.linear_cross_entropy(x, w, y, V - 64)
+                return cuda_ops.linear_cross_entropy(x, w, y, V - 64)[0]
 
         def fwd_bwd():
             x.grad = None
             w.grad = None
-            cuda_ops.linear_cross_entropy(x, w, y, V - 64).backward()
+            cuda_ops.linear_cross_entropy(x, w, y, V - 64)[0].backward()
 
         report(f"linear-CE fwd M{M} C{C} V{V}", time_ms(fwd, iters=5), fl)
         report(f"linear-CE fwd+bwd M{M} C{C} V{V}", time_ms(fwd_bwd, iters=5), 4.0 * fl)   # fwd + recompute + dX + dW
@@ -212,9 +212,9 @@ def _one_ce():
     from lyra_b200.ops import cuda_ops
     M, C, V = 4096, 2048, 200064
     x = (torch.randn(M, C, device="cuda") / 4).bfloat16().requires_grad_()
-    w = (torch.randn(C, V, device="cuda") / 64).bfloat16().requires_grad_()
+    w = (torch.randn(V, C, device="cuda") / 64).requires_grad_()
     y = torch.randint(0, V - 64, (M,), device="cuda")
-    return lambda: cuda_ops.linear_cross_entropy(x, w, y, V - 64).backward()
+    return lambda: cuda_ops.linear_cross_entropy(x, w, y, V - 64)[0].backward()
 
 
 def _one_rmsnorm():

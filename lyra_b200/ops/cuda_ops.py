@@ -318,7 +318,10 @@ class _LinearCE(torch.autograd.Function):
 
 
 def linear_cross_entropy(x, w, y, vocab_size, reduction="sum"):
+    """``w`` is ``[padded vocabulary, C]`` (row v = output embedding of token v); only the first ``vocab_size`` rows are read."""
     shape = x.shape
+    if w.ndim != 2 or w.shape[1] != shape[-1] or w.shape[0] < vocab_size:
+        raise ValueError(f"linear_cross_entropy: weight {tuple(w.shape)} does not match x {tuple(shape)} / vocab {vocab_size}")
     loss, lse = _LinearCE.apply(x.reshape(-1, shape[-1]), w, y, vocab_size, reduction)
     return loss, lse
 
