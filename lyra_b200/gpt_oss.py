@@ -22,6 +22,18 @@ FP4_VALUES = (0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2
 def dequantize_mxfp4(blocks: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
     """``blocks [..., G, 16] uint8``, ``scales [..., G] uint8`` -> bf16 ``[..., G * 32]``."""
     blocks = blocks.to(torch.uint8)
+    if blocks.is_cuda and blocks.shape[-1] == 16 and blocks.numel() > 0:
+        from lyra_b200.ops import native
+
+        if native.kernels_available():      # one pass on the GPU: 17 bytes in, 64 bytes out per block
+            import ctypes
+
+            blocks, scales = blocks.contiguous(), scales.to(torch.uint8).contiguous()
+            out = torch.empty(*blocks.shape[:-2], blocks.shape[-2] * 32, dtype=torch.bfloat16, device=blocks.device)
+            native.check(native.kernels().lyra_mxfp4_decode(native.ptr(blocks), native.ptr(scales), native.ptr(out),
+                                                            ctypes.c_longlong(blocks.numel() // 16), native.stream_ptr()), "mxfp4_decode")
+            native.count_launch()
+            return out
     lut = torch.tensor(FP4_VALUES, dtype=torch.bfloat16, device=blocks.device)
     lo, hi = lut[(blocks & 0x0F).long()], lut[(blocks >> 4).long()]
     unpacked = torch.stack((lo, hi), dim=-1)  # [..., G, 16, 2]

@@ -355,17 +355,17 @@ def moe_apply(x, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE,
         xn = xn.reshape(B * T, C)
         with scope("route_tokens"):
             scores, indices, aux = route_tokens(xn, w, c, probe=probe, rt=rt)
-        up, down = w.mlp_up, w.mlp_down
-        if isinstance(up, QArray):
-            up = dequantize(up, xn.dtype).reshape(c.n_experts, C, 2, -1)
-        if isinstance(down, QArray):
-            down = dequantize(down, xn.dtype)
         if rt is not None and rt.ep_size > 1:
             t = rt.ep_moe(xn, scores, indices, w, c)
         elif c.mode == Mode.DECODE and ops.use_kernels(xn, impl) and not xn.requires_grad:
             t = ops._cuda().decode_moe(xn, scores, indices, w.mlp_up, w.mlp_up_bias, w.mlp_down, w.mlp_down_bias,
                                        c.swiglu_beta, c.swiglu_limit)
         else:
+            up, down = w.mlp_up, w.mlp_down
+            if isinstance(up, QArray):
+                up = dequantize(up, xn.dtype).reshape(c.n_experts, C, 2, -1)
+            if isinstance(down, QArray):
+                down = dequantize(down, xn.dtype)
             with scope("experts"):
                 t = ops.moe_experts(xn, scores, indices, up, w.mlp_up_bias, down, w.mlp_down_bias,
                                     c.swiglu_beta, c.swiglu_limit, impl)

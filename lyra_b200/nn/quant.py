@@ -74,6 +74,9 @@ def quantize(x, dtype: torch.dtype, block: tuple[int, ...] = (128, 128), scale_d
     if is_scaled(scale_dtype):
         raise ValueError("scale dtype must be unscaled (fp32/bf16)")
     block = tuple(block)
+    fast = _quantize_kernel(x, dtype, block, scale_dtype)
+    if fast is not None:
+        return fast
     sdim = len(block)
     ldim = x.ndim - sdim
     axes = block_axes(ldim, sdim)
@@ -88,7 +91,78 @@ def quantize(x, dtype: torch.dtype, block: tuple[int, ...] = (128, 128), scale_d
     return QArray(qval, scale, block)
 
 
+def _kernel_lib(t: torch.Tensor):
+    """The CUDA kernel library when ``t`` lives on a GPU, else None (CPU tensors use the PyTorch formulas below)."""
+    if not t.is_cuda:
+        return None
+    from lyra_b200.ops import native
+
+    return native.kernels() if native.kernels_available() else None
+
+
+def _quantize_kernel(x: torch.Tensor, dtype, block: tuple[int, ...], scale_dtype) -> "QArray | None":
+    """CUDA path of ``quantize`` for e4m3 with a 2-D block over the last two axes (weights; KV rows when the block is (1, D))."""
+    if dtype != torch.float8_e4m3fn or scale_dtype != torch.float32 or len(block) != 2 or x.ndim < 2:
+        return None
+    if x.dtype not in (torch.float32, torch.bfloat16) or not x.is_contiguous() or x.numel() == 0:
+        return None
+    lib = _kernel_lib(x)
+    if lib is None:
+        return None
+    import ctypes
+
+    from lyra_b200.ops import native
+
+    R, C = x.shape[-2], x.shape[-1]
+    br, bc = block
+    if R % br or C % bc:
+        return None
+    L = x.numel() // (R * C)
+    q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scale = torch.empty(*x.shape[:-2], R // br, C // bc, dtype=torch.float32, device=x.device)
+    is_bf16 = ctypes.c_int(int(x.dtype == torch.bfloat16))
+    if br == 1 and bc == C and C % 32 == 0 and C <= 1024:
+        rc = lib.lyra_fp8_quantize_rows(native.ptr(x), is_bf16, native.ptr(q), native.ptr(scale), ctypes.c_longlong(L * R), ctypes.c_int(C),
+                                        ctypes.c_longlong(C), ctypes.c_longlong(C), native.stream_ptr())
+    elif L <= 65535 and R // br <= 65535:
+        rc = lib.lyra_fp8_quantize_2d(native.ptr(x), is_bf16, native.ptr(q), native.ptr(scale), ctypes.c_int(L), ctypes.c_int(R), ctypes.c_int(C),
+                                      ctypes.c_int(br), ctypes.c_int(bc), native.stream_ptr())
+    else:
+        return None
+    native.check(rc, "fp8 quantize")
+    native.count_launch()
+    return QArray(q, scale, block)
+
+
+def _dequantize_kernel(qx: "QArray", dtype) -> "torch.Tensor | None":
+    if dtype != torch.bfloat16 or qx.qval.dtype != torch.float8_e4m3fn or len(qx.block) != 2 or qx.qval.ndim < 2:
+        return None
+    if qx.scale.dtype != torch.float32 or not qx.qval.is_contiguous() or not qx.scale.is_contiguous() or qx.qval.numel() == 0:
+        return None
+    R, C = qx.qval.shape[-2], qx.qval.shape[-1]
+    br, bc = qx.block
+    if R % br or C % bc or bc % 16:
+        return None
+    lib = _kernel_lib(qx.qval)
+    if lib is None:
+        return None
+    import ctypes
+
+    from lyra_b200.ops import native
+
+    out = torch.empty(qx.qval.shape, dtype=torch.bfloat16, device=qx.qval.device)
+    L = qx.qval.numel() // (R * C)
+    rc = lib.lyra_fp8_dequantize_2d(native.ptr(qx.qval), native.ptr(qx.scale), native.ptr(out), ctypes.c_int(L), ctypes.c_int(R), ctypes.c_int(C),
+                                    ctypes.c_int(br), ctypes.c_int(bc), native.stream_ptr())
+    native.check(rc, "fp8 dequantize")
+    native.count_launch()
+    return out
+
+
 def dequantize(qx: QArray, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    fast = _dequantize_kernel(qx, dtype)
+    if fast is not None:
+        return fast
     axes = block_axes(qx.ldim, len(qx.block))
     tiled = tile(qx.qval.float(), qx.block)
     scale = qx.scale.float()

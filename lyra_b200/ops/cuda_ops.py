@@ -148,9 +148,19 @@ class _Linear(torch.autograd.Function):
         return dx, None, None, (dy if ctx.has_res else None), None
 
 
+SMALL_M_ROWS = 64   # at most this many rows (and no autograd): the weight-streaming small-M kernel, all SMs busy via K splits
+
+
 def linear(x, w, bias=None, *, residual=None, alpha: float = 1.0, out_dtype=None):
     N = w.shape[1]
-    if N % 8 or w.shape[0] % 8:
+    rows = x.numel() // x.shape[-1]
+    if (rows <= SMALL_M_ROWS and residual is None and alpha == 1.0 and N % 64 == 0 and w.shape[0] % 64 == 0 and w.ndim == 2
+            and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad)) and (AG_HOOK is None or AG_HOOK(w) is None)):
+        from lyra_b200.ops import decode as dec
+
+        x2 = x.reshape(rows, x.shape[-1]).to(BF16).contiguous()
+        y = dec.decode_gemm(x2, bf16_weight(w), bias=bias.reshape(1, N) if bias is not None else None).reshape(*x.shape[:-1], N)
+    elif N % 8 or w.shape[0] % 8:
         y = ref_linear(x, w, bias, residual, alpha)
     else:
         y = _Linear.apply(x, w, bias, residual, alpha)

@@ -74,14 +74,93 @@ def decode_attention(q, k_cache, v_cache, sinks, scale: float, window: int, pos,
     return o
 
 
-def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit):
-    """Expert MLP for a handful of tokens: weight-streaming small-M kernel when built, else the grouped-GEMM path."""
-    from lyra_b200.ops import cuda_ops
+def _gemm_splits(n_cols: int, groups_with_rows: int, k_chunks: int) -> int:
+    """K splits so that a layer with few column panels still spreads over the SMs (about two CTAs per SM)."""
+    ctas = max(1, (n_cols // 64) * max(1, groups_with_rows))
+    want = max(1, (2 * 148 + ctas - 1) // ctas)
+    best = 1
+    for s in range(1, k_chunks + 1):
+        if k_chunks % s == 0 and s <= want:
+            best = s
+    return best
 
-    if isinstance(w_up, QArray) or isinstance(w_down, QArray):
-        C = xn.shape[1]
-        if isinstance(w_up, QArray):
-            w_up = dequantize(w_up, BF16).reshape(w_up.shape[0], C, 2, -1)
-        if isinstance(w_down, QArray):
-            w_down = dequantize(w_down, BF16)
+
+def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, bias: torch.Tensor | None = None, swiglu: bool = False,
+                swiglu_beta: float = 1.702, swiglu_limit: float = 7.0, active_groups: int | None = None) -> torch.Tensor:
+    """``x [R, K]`` (rows sorted by group) times ``w [G, K, N]`` (bf16 tensor, or QArray of e4m3 values with 2-D block
+    scales) -> bf16 ``[R, N]`` (``[R, N/2]`` with SwiGLU). ``offsets [G+1]`` int32 row offsets on the device; ``None``
+    means one group (a dense layer, ``w [K, N]`` or ``[1, K, N]``). Rows per group beyond 64 cost another pass over that
+    group's weights, so this is the path for a few rows per expert."""
+    lib = native.kernels()
+    quant = isinstance(w, QArray)
+    wq = w.qval if quant else w
+    if wq.ndim == 2:
+        wq = wq.unsqueeze(0)
+    G, K, N = wq.shape
+    R = x.shape[0]
+    assert x.shape[1] == K and x.dtype == BF16 and x.is_contiguous() and wq.is_contiguous()
+    assert wq.dtype == (torch.float8_e4m3fn if quant else BF16), wq.dtype
+    bk = bn = 0
+    scale = None
+    if quant:
+        bk, bn = w.block[-2], w.block[-1]
+        scale = w.scale.float().contiguous()
+    splits = _gemm_splits(N, min(G, R) if active_groups is None else active_groups, K // 64)
+    part = torch.empty(splits, R, N, dtype=torch.float32, device=x.device)
+    out = torch.empty(R, N // 2 if swiglu else N, dtype=BF16, device=x.device)
+    b = bias.detach().float().contiguous() if bias is not None else None
+    lib.lyra_decode_gemm.restype = c_int
+    rc = lib.lyra_decode_gemm(ptr(x), ptr(wq), ptr(scale), c_int(int(quant)), c_int(bk), c_int(bn), ptr(offsets), ptr(b), ptr(part), ptr(out),
+                              c_int(R), c_int(K), c_int(N), c_int(G), c_int(splits), c_int(int(swiglu)), c_float(swiglu_beta),
+                              c_float(swiglu_limit), native.stream_ptr())
+    native.check(rc, "lyra_decode_gemm")
+    native.count_launch(2)
+    return out
+
+
+def decode_gemm_supported(K: int, N: int, w) -> bool:
+    if K % 64 or N % 64:
+        return False
+    if isinstance(w, QArray):
+        return (w.qval.dtype == torch.float8_e4m3fn and len(w.block) == 2 and w.block[0] % 64 == 0 and w.block[1] % 64 == 0
+                and K % w.block[0] == 0 and N % w.block[1] == 0)
+    return True
+
+
+DECODE_GEMM_MAX_ROWS = 512   # assignments (tokens x experts per token); above this the 128-row-tile tcgen05 grouped GEMM takes over
+
+
+def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit):
+    """Expert MLP for a handful of tokens (role of lyra/kernels/decode_gemm.py): rows sorted by expert without padding,
+    two weight-streaming products (SwiGLU fused into the first one's finishing pass), weighted combine."""
+    from lyra_b200.ops import cuda_ops
+    from lyra_b200.ops import elementwise as ew
+    from lyra_b200.ops import reference as ref
+
+    F_, K = indices.shape
+    C = xn.shape[1]
+    E = (w_up.qval if isinstance(w_up, QArray) else w_up).shape[0]
+    up_q, down_q = isinstance(w_up, QArray), isinstance(w_down, QArray)
+    wu = w_up if up_q else cuda_ops.bf16_weight(w_up).view(E, C, -1)
+    wd = w_down if down_q else cuda_ops.bf16_weight(w_down)
+    N_up = (wu.qval if up_q else wu).shape[-1]
+    H = N_up // 2
+    if F_ * K <= DECODE_GEMM_MAX_ROWS and decode_gemm_supported(C, N_up, wu) and decode_gemm_supported(H, C, wd):
+        flat = indices.reshape(-1)
+        counts = ref.count_ids(flat, E)
+        offsets = torch.zeros(E + 1, dtype=torch.int32, device=xn.device)
+        offsets[1:] = torch.cumsum(counts, 0)
+        order = torch.argsort(flat, stable=True)
+        dest = torch.empty_like(order)
+        dest[order] = torch.arange(order.numel(), device=order.device)
+        x_sorted = xn.to(BF16)[order // K].contiguous()
+        ub = up_bias.reshape(E, N_up) if up_bias is not None else None
+        db = down_bias.reshape(E, C) if down_bias is not None else None
+        act = decode_gemm(x_sorted, wu, offsets=offsets, bias=ub, swiglu=True, swiglu_beta=beta, swiglu_limit=limit, active_groups=min(E, F_ * K))
+        down = decode_gemm(act, wd, offsets=offsets, bias=db, active_groups=min(E, F_ * K))
+        return ew.combine_rows(down, dest, scores.float().contiguous(), F_, K)
+    if up_q:
+        w_up = dequantize(w_up, BF16).reshape(E, C, 2, -1)
+    if down_q:
+        w_down = dequantize(w_down, BF16)
     return cuda_ops.moe_experts(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit)
