@@ -1,0 +1,119 @@
+"""Batched prefill + decode throughput of a GPT-OSS-shaped model on one GPU (random bf16 weights, synthetic prompts).
+
+    python bench/serve.py                                  # gpt-oss-20b, batch 64, 1024-token prompts, 128 new tokens
+    python bench/serve.py --variant lyra-small --batch 8 --prompt 256 --new 64
+    python bench/serve.py --layers 4 --new 8 --no-graph    # a small case (e.g. under a profiler)
+
+Prints one JSON line: prefill tokens/s, decode tokens/s with the per-token launch sequence replayed from a CUDA graph and
+launched eagerly, and the decode step time against the time to read the active weights and the KV cache once at the
+measured HBM bandwidth. Device timings are CUDA events around the whole prefill / the whole decode loop after one
+untimed round; the working set (weights + cache) is far larger than L2.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import sys
+from dataclasses import replace
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
+
+
+def hbm_gbs() -> tuple[float, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    return (json.loads(p.read_text())["hbm_gbs"], "measured") if p.exists() else (6650.0, "fallback")
+
+
+def timed(fn) -> tuple[float, object]:
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    s.record()
+    out = fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e), out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--variant", default="gpt-oss-20b")
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--prompt", type=int, default=1024)
+    ap.add_argument("--new", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (0 = all)")
+    ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights and an e4m3 KV cache")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+
+    from lyra_b200.generate import BatchedGenerator
+    from lyra_b200.model import ModelWeights
+    from lyra_b200.nn.params import param_count, tree_leaves
+    from lyra_b200.nn.quant import QArray
+    from lyra_b200.ops import native
+    from lyra_b200.variants import model_variant
+
+    dev = torch.device("cuda")
+    mcfg = replace(model_variant(args.variant), param_dtype=torch.bfloat16, sample_temperature=0.0)
+    if args.layers:
+        mcfg = replace(mcfg, n_layers=args.layers, mlp_map=mcfg.mlp_map[: args.layers])
+    if args.fp8:
+        mcfg = replace(mcfg, quantize_mlp=True, quantize_cache=True, gemm_dtype=torch.float8_e4m3fn, quant_block=(64, 64))
+    model = ModelWeights.init(0, mcfg, device=dev)
+    if args.fp8:
+        model = ModelWeights.quantize(model, mcfg)
+    capacity = args.prompt + args.new
+    prompts = torch.randint(0, mcfg.vocab_size, (args.batch, args.prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+
+    results = {}
+    for mode in (["eager"] if args.no_graph else ["graph", "eager"]):
+        gen = BatchedGenerator(model, mcfg, batch=args.batch, capacity=capacity, device=dev, use_cuda_graph=(mode == "graph"))
+        first = gen.prefill(prompts)                       # untimed round: one-time set-up, graph capture
+        gen.decode(first, min(args.new, 4))
+        t_pre, first = timed(lambda: gen.prefill(prompts))
+        l0 = native.launches()
+        t_dec, toks = timed(lambda: gen.decode(first, args.new))
+        native.check_status()
+        results[mode] = {"prefill_ms": t_pre, "decode_ms": t_dec, "tokens": toks, "launches_per_token": (native.launches() - l0) / max(1, args.new - 1)}
+        del gen
+        torch.cuda.empty_cache()
+
+    best = "eager" if args.no_graph else "graph"
+    if not args.no_graph:
+        same = bool(torch.equal(results["graph"]["tokens"], results["eager"]["tokens"]))
+    steps = args.new - 1
+    # bytes one decode step must read: every weight that takes part (all attention weights, the router, the experts that
+    # received a token: at most min(E, batch * k) per layer) and the visible KV rows
+    def nbytes(t):
+        return (t.qval.numel() + t.scale.numel() * 4) if isinstance(t, QArray) else t.numel() * t.element_size()
+    total_w = sum(nbytes(t) for t in tree_leaves(model))
+    expert_w = sum(nbytes(t) for l in model.layers for t in (l.mlp.mlp_up, l.mlp.mlp_down) if hasattr(l.mlp, "router"))
+    frac_active = min(1.0, args.batch * mcfg.n_active_experts / max(1, mcfg.n_experts))
+    kv_el = 1 if args.fp8 else 2
+    mean_pos = args.prompt + args.new / 2
+    kv = sum(2 * args.batch * mcfg.n_kv_heads * min(mean_pos, mcfg.layer_window(i) or mean_pos) * mcfg.head_dim * kv_el for i in range(mcfg.n_layers))
+    step_bytes = total_w - expert_w * (1 - frac_active) + kv
+    bw, kind = hbm_gbs()
+    step_ms = results[best]["decode_ms"] / steps
+    line = {
+        "bench": "batched serve", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch": args.batch,
+        "prompt_len": args.prompt, "new_tokens": args.new, "dtype": "bf16" + (" + e4m3 experts and KV" if args.fp8 else ""), "data": "synthetic tokens, random-init weights",
+        "prefill_tokens_per_s": round(args.batch * args.prompt / results[best]["prefill_ms"] * 1e3, 1),
+        "decode_tokens_per_s": round(args.batch * steps / results[best]["decode_ms"] * 1e3, 1),
+        "decode_ms_per_step": round(step_ms, 3),
+        "decode_bytes_per_step_gb": round(step_bytes / 1e9, 3),
+        f"decode_frac_of_{kind}_hbm": round(step_bytes / (step_ms * 1e-3) / 1e9 / bw, 3),
+        "own_kernel_launches_per_token_eager": round(results["eager"]["launches_per_token"], 1) if "eager" in results else None,
+    }
+    if not args.no_graph:
+        line["decode_tokens_per_s_eager"] = round(args.batch * steps / results["eager"]["decode_ms"] * 1e3, 1)
+        line["graph_equals_eager"] = same
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()

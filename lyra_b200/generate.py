@@ -151,12 +151,56 @@ class BatchedGenerator:
 
     @torch.no_grad()
     def decode(self, first: torch.Tensor, n: int) -> torch.Tensor:
+        if self.use_cuda_graph and self.rt is None and self.decode_cfg.sample_temperature <= 0:
+            return self._decode_graph(first, n)
         out = [first]
         tok = first
         for _ in range(n - 1):
             tok = self.decode_step(tok)
             out.append(tok)
         return torch.stack(out, dim=1)
+
+    def _graph_step(self) -> None:
+        """One greedy token from ``_static_tok`` at the device-resident position; advances both in place."""
+        hidden, _, cache = model_apply(self._static_tok.reshape(self.batch, 1), self.model, self.cache, self.decode_cfg,
+                                       return_hidden_states=True, rt=None)
+        nxt = self._next_from_hidden(hidden[:, -1])
+        self._static_tok.copy_(nxt)
+        self.cache.pos_dev.add_(1)
+
+    @torch.no_grad()
+    def _decode_graph(self, first: torch.Tensor, n: int) -> torch.Tensor:
+        """Greedy decode with the per-token launch sequence captured once in a CUDA graph and replayed: the position
+        lives in device memory (cache writes, RoPE row, attention bounds read it there), so every replay is identical
+        on the host side and costs one launch instead of a few hundred."""
+        start = self.cache.pos
+        if start + n - 1 > self.capacity:
+            raise ValueError(f"cache capacity {self.capacity} too small for {start} + {n - 1} positions")
+        if self._graph is None:
+            self._static_tok = torch.zeros(self.batch, dtype=torch.long, device=self.device)
+            self.cache.pos_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self._out = None
+            # a first eager step on a side stream: one-time kernel set-up and allocator warm-up must not be captured
+            self._static_tok.copy_(first)
+            self.cache.pos_dev.fill_(start)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self._graph_step()
+            torch.cuda.current_stream(self.device).wait_stream(side)
+            torch.cuda.synchronize(self.device)
+            self._graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self._graph):
+                self._graph_step()
+        self._static_tok.copy_(first)
+        self.cache.pos_dev.fill_(start)
+        out = torch.empty(self.batch, n, dtype=torch.long, device=self.device)
+        out[:, 0] = first
+        for i in range(1, n):
+            self._graph.replay()
+            out[:, i] = self._static_tok
+        self.cache.pos = start + n - 1
+        return out
 
 
 # --------------------------------------------------------------------------- REPL

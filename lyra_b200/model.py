@@ -90,8 +90,20 @@ class LayerCache:
     v: Any
 
 
-def cache_update(cache: LayerCache, k: torch.Tensor, v: torch.Tensor, start_pos: int) -> LayerCache:
-    """Writes ``k, v [B, Nkv, T, D]`` at ``start_pos`` (in place). fp8 caches quantise per (position, head)."""
+def cache_update(cache: LayerCache, k: torch.Tensor, v: torch.Tensor, start_pos: int, pos_dev: torch.Tensor | None = None) -> LayerCache:
+    """Writes ``k, v [B, Nkv, T, D]`` at ``start_pos`` (in place). fp8 caches quantise per (position, head).
+    With ``pos_dev`` (int device scalar, T == 1) the position is read on the device, so the call can be replayed."""
+    if pos_dev is not None:
+        at = pos_dev.reshape(1).long()
+        if isinstance(cache.k, QArray):
+            for dst, new in ((cache.k, k), (cache.v, v)):
+                qn = quantize(new.contiguous(), dst.dtype, dst.block, dst.stype)
+                dst.qval.view(torch.uint8).index_copy_(2, at, qn.qval.view(torch.uint8))   # index_copy_ has no fp8 kernel
+                dst.scale.index_copy_(2, at, qn.scale)
+            return cache
+        cache.k.index_copy_(2, at, k.to(cache.k.dtype))
+        cache.v.index_copy_(2, at, v.to(cache.v.dtype))
+        return cache
     if isinstance(cache.k, QArray):
         start = (0, 0, int(start_pos), 0)
         return LayerCache(k=qupdate(cache.k, k, start), v=qupdate(cache.v, v, start))
@@ -105,6 +117,7 @@ def cache_update(cache: LayerCache, k: torch.Tensor, v: torch.Tensor, start_pos:
 class ModelCache:
     layers: tuple[LayerCache, ...]
     pos: int
+    pos_dev: Any = None  # optional int32 device scalar mirroring ``pos``: single-token decode then reads the position on the device
 
     @staticmethod
     def create(config: ModelConfig, batch: int, capacity: int, device, n_kv_local: int | None = None) -> "ModelCache":
@@ -177,7 +190,7 @@ def _dq(w, dtype):
 
 
 def attention_apply(x, w: AttentionWeights, idx: int, pos: int, freq_cis, cache: LayerCache | None, config: ModelConfig,
-                    *, probe: Probe = NO_PROBE, rt=None):
+                    *, probe: Probe = NO_PROBE, rt=None, pos_dev=None):
     """Pre-norm attention block with residual (lyra/model.py:285-374). ``x [B, T, C]`` in the compute dtype."""
     c = config
     impl = c.implementation
@@ -211,9 +224,9 @@ def attention_apply(x, w: AttentionWeights, idx: int, pos: int, freq_cis, cache:
                 t = ops.attention(q, k, v, sinks, c.head_dim**-0.5, window, 0, impl)
             else:
                 assert cache is not None
-                updated_cache = cache_update(cache, k, v, pos)
+                updated_cache = cache_update(cache, k, v, pos, pos_dev)
                 if c.mode == Mode.DECODE:
-                    t = ops.decode_attention(q, updated_cache.k, updated_cache.v, sinks, c.head_dim**-0.5, window, pos, impl)
+                    t = ops.decode_attention(q, updated_cache.k, updated_cache.v, sinks, c.head_dim**-0.5, window, pos, impl, pos_dev=pos_dev)
                 else:
                     t = ops.attention(q, k, v, sinks, c.head_dim**-0.5, window, pos, impl) if pos == 0 else \
                         ops.decode_attention(q, updated_cache.k, updated_cache.v, sinks, c.head_dim**-0.5, window, pos, impl)
@@ -526,7 +539,12 @@ def model_apply(tokens, model: ModelWeights, cache: ModelCache | None, config: M
         probe.tensor("embs", h)
         start_pos = cache.pos if cache is not None else 0
         cos, sin = rope_tables(c, h.device)
-        freq_cis = (cos[start_pos:start_pos + T][None, :, None, :], sin[start_pos:start_pos + T][None, :, None, :])
+        pos_dev = cache.pos_dev if (cache is not None and c.mode == Mode.DECODE and T == 1) else None
+        if pos_dev is not None:
+            at = pos_dev.reshape(1).long()
+            freq_cis = (cos.index_select(0, at)[None, :, None, :], sin.index_select(0, at)[None, :, None, :])
+        else:
+            freq_cis = (cos[start_pos:start_pos + T][None, :, None, :], sin[start_pos:start_pos + T][None, :, None, :])
 
         aux_loss = torch.zeros((), dtype=torch.float32, device=h.device)
         caches = []
@@ -536,13 +554,13 @@ def model_apply(tokens, model: ModelWeights, cache: ModelCache | None, config: M
                 if rt is not None:
                     rt.begin_layer(idx)
                 lc = cache.layers[idx] if cache is not None else None
-                h, lc = attention_apply(h, layer.attn, idx, start_pos, freq_cis, lc, c, probe=lp.scope("attn"), rt=rt)
+                h, lc = attention_apply(h, layer.attn, idx, start_pos, freq_cis, lc, c, probe=lp.scope("attn"), rt=rt, pos_dev=pos_dev)
                 h, layer_aux = mlp_apply(h, layer.mlp, c, probe=lp.scope("mlp"), rt=rt)
             aux_loss = aux_loss + layer_aux
             caches.append(lc)
         if c.n_moe_layers:
             aux_loss = aux_loss / c.n_moe_layers
-        updated = None if cache is None else ModelCache(layers=tuple(caches), pos=start_pos + T)
+        updated = None if cache is None else ModelCache(layers=tuple(caches), pos=start_pos + T, pos_dev=cache.pos_dev)
 
         head = probe.scope("head")
         head.tensor("pre_norm", h)

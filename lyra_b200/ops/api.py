@@ -99,13 +99,15 @@ def attention(q, k, v, sinks, scale: float, window: int, q_start=0, implementati
     return ref.attention(q, k, v, sinks, scale, window, q_start)[0]
 
 
-def decode_attention(q, k_cache, v_cache, sinks, scale: float, window: int, pos, implementation: str = "auto"):
+def decode_attention(q, k_cache, v_cache, sinks, scale: float, window: int, pos, implementation: str = "auto", *, pos_dev=None):
     """Attention of ``T`` new query tokens (usually 1) starting at position ``pos`` over a KV cache
     (dense bf16 or fp8 ``QArray`` with one scale per (sequence, head, position))."""
     from lyra_b200.nn.quant import QArray, dequantize
 
     if use_kernels(q, implementation):
-        return _cuda().decode_attention(q, k_cache, v_cache, sinks, scale, window, pos)
+        return _cuda().decode_attention(q, k_cache, v_cache, sinks, scale, window, pos, pos_dev=pos_dev)
+    if pos_dev is not None:
+        pos = int(pos_dev.item())
     k = dequantize(k_cache, q.dtype) if isinstance(k_cache, QArray) else k_cache
     v = dequantize(v_cache, q.dtype) if isinstance(v_cache, QArray) else v_cache
     return ref.attention(q, k, v, sinks, scale, window, pos)[0]

@@ -242,10 +242,10 @@ def flash_attention(q, k, v, sinks, scale, window, q_start):
     return attn_k.flash_attention(q, k, v, sinks, scale, window, int(q_start))
 
 
-def decode_attention(q, k_cache, v_cache, sinks, scale, window, pos):
+def decode_attention(q, k_cache, v_cache, sinks, scale, window, pos, pos_dev=None):
     from lyra_b200.ops import decode as dec
 
-    return dec.decode_attention(q, k_cache, v_cache, sinks, scale, window, int(pos))
+    return dec.decode_attention(q, k_cache, v_cache, sinks, scale, window, int(pos), pos_dev=pos_dev)
 
 
 def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit):

@@ -67,6 +67,8 @@ def decode_attention(q, k_cache, v_cache, sinks, scale: float, window: int, pos,
         native.check(rc, "lyra_decode_attention")
         native.count_launch(2 if splits > 1 else 1)
         return out
+    if pos_dev is not None:
+        raise ValueError("a device-resident position needs the single-token kernel (T == 1, head dim 64 or 128, bf16 or e4m3 cache)")
     k = dequantize(k_cache, BF16) if quant else k_cache
     v = dequantize(v_cache, BF16) if quant else v_cache
     S = min(k.shape[2], (int(pos) + T + 127) // 128 * 128)

@@ -69,3 +69,29 @@ def test_serve_repl_plain_chat(monkeypatch):
     serve_model(w, c, InferenceConfig(weights="x", max_new_tokens=3, max_cache_length=24), input_fn=lambda _: next(prompts),
                 output_fn=lambda *a, **k: printed.append(a))
     assert printed and "Type a prompt" in printed[0][0]
+
+
+@pytest.mark.parametrize("fp8_cache", [False, True])
+def test_decode_with_device_resident_position_matches_host_position(fp8_cache):
+    """The position of a single-token decode step may live in a device scalar (what CUDA-graph replay needs)."""
+    from dataclasses import replace
+
+    from lyra_b200.generate import BatchedGenerator
+    from lyra_b200.model import ModelWeights
+    from lyra_b200.variants import model_variant
+
+    c = replace(model_variant("dev"), sample_temperature=0.0, quantize_cache=fp8_cache)
+    m = ModelWeights.init(0, c)
+    B, P, N = 2, 8, 5
+    prompts = torch.randint(0, c.vocab_size, (B, P), generator=torch.Generator().manual_seed(0))
+    g = BatchedGenerator(m, c, batch=B, capacity=P + N, device="cpu")
+    want = g.decode(g.prefill(prompts), N)
+    g2 = BatchedGenerator(m, c, batch=B, capacity=P + N, device="cpu")
+    tok = g2.prefill(prompts)
+    g2.cache.pos_dev = torch.tensor([g2.cache.pos], dtype=torch.int32)
+    got = [tok]
+    for _ in range(N - 1):
+        tok = g2.decode_step(tok)
+        g2.cache.pos_dev += 1
+        got.append(tok)
+    assert torch.equal(want, torch.stack(got, dim=1))
