@@ -1,7 +1,7 @@
 """Per-kernel device timings against the measured roofline denominators.
 
     python bench/kernels.py gemm            # tcgen05 GEMM family vs torch.matmul (cuBLAS)
-    python bench/kernels.py attention | ce | elementwise | decode | all
+    python bench/kernels.py attention | ce | elementwise | decode | decode_gemm | all
     python bench/kernels.py one <case>      # three launches of one small case, for a profiler capture (cases: see ONE)
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, an L2 flush (a 256 MB write) between
@@ -188,6 +188,35 @@ def bench_decode():
 
 
 BENCHES["decode"] = bench_decode
+
+
+def bench_decode_gemm():
+    """Small-M expert products of one decode step: bytes = weights of the experts that have rows, read once."""
+    import os
+
+    from lyra_b200.nn.quant import quantize
+    from lyra_b200.ops import decode
+
+    for (G, K, N, rows_per, name) in [(32, 2880, 5760, 8, "gpt-oss up"), (32, 2880, 2880, 8, "gpt-oss down"), (16, 4096, 4096, 4, "lyra-medium expert"),
+                                      (1, 4096, 6144, 64, "dense qkv, 64 rows")]:
+        R = G * rows_per
+        x = torch.randn(R, K, device="cuda").bfloat16()
+        w = (torch.randn(G, K, N, device="cuda") / K ** 0.5).bfloat16()
+        offsets = (torch.arange(G + 1, device="cuda", dtype=torch.int32) * rows_per) if G > 1 else None
+        for panel in (64, 128, 192):
+            if N % panel:
+                continue
+            os.environ["LYRA_DECODE_PANEL"] = str(panel)
+            report(f"decode gemm bf16 {name} G{G} K{K} N{N} rows/group {rows_per} panel{panel}",
+                   time_ms(lambda: decode.decode_gemm(x, w, offsets=offsets)), bytes_=2.0 * G * K * N)
+        os.environ.pop("LYRA_DECODE_PANEL", None)
+        w8 = quantize(w, torch.float8_e4m3fn, block=(64, 64))
+        report(f"decode gemm e4m3 {name} G{G} K{K} N{N} rows/group {rows_per}",
+               time_ms(lambda: decode.decode_gemm(x, w8, offsets=offsets)), bytes_=1.0 * G * K * N)
+        del w, w8
+
+
+BENCHES["decode_gemm"] = bench_decode_gemm
 
 
 def _one_gemm():

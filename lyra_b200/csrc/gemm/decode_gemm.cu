@@ -6,9 +6,9 @@
 // dequantise-then-matmul). Unlike the reference kernel there is no K, N % 128 restriction: 64 is enough, so the 2880-wide
 // GPT-OSS layers take this path too.
 //
-// Design: a CTA owns one 64-column panel of one group's weight matrix (and one K range when the K axis is split so that a
-// dense layer still fills 148 SMs); 64 x 64 weight tiles and the matching activation tile arrive through a four-stage
-// cp.async ring; four warps each own 16 columns and up to four 16-row blocks of the group (warp-level m16n8k16 MMAs: a
+// Design: a CTA owns one 64/128/192-column panel of one group's weight matrix (and one K range when the K axis is split so that a
+// dense layer still fills 148 SMs); 64-row weight tiles and the matching activation tile arrive through a four-stage
+// cp.async ring; four warps each own a quarter of the panel's columns and up to four 16-row blocks of the group (warp-level m16n8k16 MMAs: a
 // tcgen05 tile would need M >= 64 rows per expert, which decode does not have; groups with more than 64 rows are covered
 // by further CTAs along grid.z). fp32 partials go to a scratch buffer; a finishing kernel sums the K splits, adds the
 // bias and applies the clamped SwiGLU.
@@ -20,9 +20,9 @@
 
 namespace {
 
-constexpr int TN = 64, TKC = 64, MROWS = 64, NST = 4, THREADS = 128;
-constexpr int ROWB = TN * 2 + 16;          // padded bf16 tile row (ldmatrix rows in distinct banks)
-constexpr int TILE_B = TKC * ROWB;         // 9216
+constexpr int TKC = 64, MROWS = 64, NST = 4, THREADS = 128;
+constexpr int XROWB = TKC * 2 + 16;        // padded bf16 activation-tile row (ldmatrix rows in distinct banks)
+constexpr int XTILE_B = MROWS * XROWB;     // 9216
 
 struct DGParams {
   const __nv_bfloat16* x;   // [R, K], rows sorted by group
@@ -61,16 +61,21 @@ __device__ __forceinline__ uint32_t fp8x2_to_bf16x2(uint16_t two, float scale) {
   return pack2(f.x * scale, f.y * scale);
 }
 
-template <bool FP8>
+// TN = columns per CTA (64, 128 or 192): wider panels read longer contiguous pieces of each weight row.
+template <bool FP8, int TN>
 struct Geo {
+  static constexpr int ROWB = TN * 2 + 16;                     // padded bf16 weight-tile row
+  static constexpr int TILE_B = TKC * ROWB;
   static constexpr int WRAW_B = FP8 ? TKC * TN : TILE_B;       // weight tile as it arrives
-  static constexpr int STAGE_B = WRAW_B + TILE_B;              // + activation tile [64 rows][64 k]
+  static constexpr int STAGE_B = WRAW_B + XTILE_B;             // + activation tile [64 rows][64 k]
   static constexpr int SMEM_B = NST * STAGE_B + (FP8 ? TILE_B : 0);
 };
 
-template <bool FP8>
+template <bool FP8, int TN>
 __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) {
-  using G_ = Geo<FP8>;
+  using G_ = Geo<FP8, TN>;
+  constexpr int ROWB = G_::ROWB;
+  constexpr int WN = TN / 4, NT = WN / 8;                       // columns and n8 tiles per warp
   extern __shared__ __align__(128) uint8_t smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int n0 = blockIdx.x * TN, g = blockIdx.y;
@@ -100,15 +105,15 @@ __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) 
     for (int j = 0; j < MROWS * 8 / THREADS; ++j) {
       const int ch = tid + THREADS * j, row = ch >> 3, col = ch & 7;
       const bool ok = row < cnt;
-      cp16(s32(xt + row * ROWB + col * 16), p.x + static_cast<size_t>(r0 + (ok ? row : 0)) * p.K + k0 + col * 8, ok ? 16 : 0);
+      cp16(s32(xt + row * XROWB + col * 16), p.x + static_cast<size_t>(r0 + (ok ? row : 0)) * p.K + k0 + col * 8, ok ? 16 : 0);
     }
   };
 
-  float acc[4][2][4];
+  float acc[4][NT][4];
 #pragma unroll
   for (int a = 0; a < 4; ++a)
 #pragma unroll
-    for (int b = 0; b < 2; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f;
+    for (int b = 0; b < NT; ++b) acc[a][b][0] = acc[a][b][1] = acc[a][b][2] = acc[a][b][3] = 0.f;
 
 #pragma unroll
   for (int s = 0; s < NST - 1; ++s) {
@@ -126,10 +131,12 @@ __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) 
     if (FP8) {
       wt = smem + NST * G_::STAGE_B;
       const int k0 = kbeg + c * TKC;
-      const float sc = p.wscale[(static_cast<size_t>(g) * (p.K / p.bk) + k0 / p.bk) * (p.N / p.bn) + n0 / p.bn];
+      const float* srow = p.wscale + (static_cast<size_t>(g) * (p.K / p.bk) + k0 / p.bk) * (p.N / p.bn);
+      constexpr int CPR = TN / 16;
 #pragma unroll
-      for (int j = 0; j < TKC * (TN / 16) / THREADS; ++j) {
-        const int ch = tid + THREADS * j, row = ch >> 2, col = ch & 3;
+      for (int j = 0; j < TKC * CPR / THREADS; ++j) {
+        const int ch = tid + THREADS * j, row = ch / CPR, col = ch % CPR;
+        const float sc = srow[(n0 + col * 16) / p.bn];
         const uint4 raw = *reinterpret_cast<const uint4*>(st + row * TN + col * 16);
         const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
         uint32_t o[8];
@@ -144,31 +151,35 @@ __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) 
       }
       __syncthreads();
     }
-    const uint32_t waddr = s32(wt) + (((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (warp * 16 + (lane >> 4) * 8) * 2;
-    const uint32_t xaddr = s32(xt) + (((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (lane >> 4) * 16;
+    const uint32_t waddr = s32(wt) + (((lane >> 3) & 1) * 8 + (lane & 7)) * ROWB + (warp * WN + (lane >> 4) * 8) * 2;
+    const uint32_t xaddr = s32(xt) + (((lane >> 3) & 1) * 8 + (lane & 7)) * XROWB + (lane >> 4) * 16;
 #pragma unroll
     for (int ks = 0; ks < TKC / 16; ++ks) {
-      uint32_t b[4];
-      ldsm4t(b, waddr + ks * 16 * ROWB);
+      uint32_t b[NT / 2][4];
+#pragma unroll
+      for (int np = 0; np < NT / 2; ++np) ldsm4t(b[np], waddr + ks * 16 * ROWB + np * 32);
 #pragma unroll
       for (int mt = 0; mt < 4; ++mt) {
         if (mt < n_mt) {
           uint32_t a[4];
-          ldsm4(a, xaddr + mt * 16 * ROWB + ks * 32);
-          mma16816(acc[mt][0], a, b[0], b[1]);
-          mma16816(acc[mt][1], a, b[2], b[3]);
+          ldsm4(a, xaddr + mt * 16 * XROWB + ks * 32);
+#pragma unroll
+          for (int np = 0; np < NT / 2; ++np) {
+            mma16816(acc[mt][2 * np], a, b[np][0], b[np][1]);
+            mma16816(acc[mt][2 * np + 1], a, b[np][2], b[np][3]);
+          }
         }
       }
     }
   }
   cp_wait<0>();
   float* out = p.part + static_cast<size_t>(split) * p.R * p.N;
-  const int col = n0 + warp * 16 + (lane & 3) * 2;
+  const int col = n0 + warp * WN + (lane & 3) * 2;
 #pragma unroll
   for (int mt = 0; mt < 4; ++mt) {
     const int ra = mt * 16 + (lane >> 2), rb = ra + 8;
 #pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
+    for (int nt = 0; nt < NT; ++nt) {
       if (ra < cnt) *reinterpret_cast<float2*>(out + static_cast<size_t>(r0 + ra) * p.N + col + nt * 8) = make_float2(acc[mt][nt][0], acc[mt][nt][1]);
       if (rb < cnt) *reinterpret_cast<float2*>(out + static_cast<size_t>(r0 + rb) * p.N + col + nt * 8) = make_float2(acc[mt][nt][2], acc[mt][nt][3]);
     }
@@ -205,19 +216,26 @@ __global__ void decode_gemm_finish_kernel(const float* __restrict__ part, const 
   }
 }
 
-template <bool FP8>
+template <bool FP8, int TN>
 int launch(const DGParams& p, cudaStream_t stream) {
-  constexpr int smem = Geo<FP8>::SMEM_B;
+  constexpr int smem = Geo<FP8, TN>::SMEM_B;
   static bool configured[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 64 && !configured[dev]) {
-    if (cudaFuncSetAttribute(decode_gemm_kernel<FP8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -91;
+    if (cudaFuncSetAttribute(decode_gemm_kernel<FP8, TN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -91;
     configured[dev] = true;
   }
   dim3 grid(p.N / TN, p.G, p.splits * p.zblocks);
-  decode_gemm_kernel<FP8><<<grid, THREADS, smem, stream>>>(p);
+  decode_gemm_kernel<FP8, TN><<<grid, THREADS, smem, stream>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -92;
+}
+
+template <bool FP8>
+int launch_tn(const DGParams& p, int tn, cudaStream_t stream) {
+  if (tn == 192) return launch<FP8, 192>(p, stream);
+  if (tn == 128) return launch<FP8, 128>(p, stream);
+  return launch<FP8, 64>(p, stream);
 }
 
 }  // namespace
@@ -225,12 +243,15 @@ int launch(const DGParams& p, cudaStream_t stream) {
 // x [R, K] bf16 (rows sorted by group); w [G, K, N] bf16 (quant = 0) or e4m3 with wscale [G, K/bk, N/bn] (quant = 1);
 // offsets [G+1] int32 on the device (null: a single group); part: fp32 scratch [splits, R, N]; out bf16 [R, N] or, with
 // swiglu, [R, N/2]. bias fp32 [G, N] or null. K and N must be multiples of 64, K / splits a multiple of 64.
+// `panel` = columns per CTA: 64, 128 or 192, a divisor of N (0: 128 if it divides N, else 64).
 extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscale, int quant, int bk, int bn, const int* offsets, const float* bias,
                                 float* part, void* out, int R, int K, int N, int G, int splits, int swiglu, float swiglu_beta, float swiglu_limit,
-                                cudaStream_t stream) {
+                                int panel, cudaStream_t stream) {
   if (R <= 0) return 0;
-  if (K % TKC || N % TN || splits < 1 || (K / TKC) % splits || G < 1 || (!offsets && G != 1)) return -90;
-  if (quant && (!wscale || bk % TKC || bn % TN || K % bk || N % bn)) return -90;
+  if (panel == 0) panel = N % 128 == 0 ? 128 : 64;
+  if ((panel != 64 && panel != 128 && panel != 192) || N % panel) return -90;
+  if (K % TKC || splits < 1 || (K / TKC) % splits || G < 1 || (!offsets && G != 1)) return -90;
+  if (quant && (!wscale || bk % TKC || bn % 16 || K % bk || N % bn)) return -90;
   if (swiglu && (N / 2) % 2) return -90;
   DGParams p;
   p.x = static_cast<const __nv_bfloat16*>(x);
@@ -247,7 +268,7 @@ extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscal
   p.bk = bk;
   p.bn = bn;
   p.zblocks = (R + MROWS - 1) / MROWS;
-  const int rc = quant ? launch<true>(p, stream) : launch<false>(p, stream);
+  const int rc = quant ? launch_tn<true>(p, panel, stream) : launch_tn<false>(p, panel, stream);
   if (rc) return rc;
   decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,
                                                    swiglu_limit);

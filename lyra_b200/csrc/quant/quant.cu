@@ -69,12 +69,12 @@ __global__ void fp8_quantize_2d_kernel(const T* __restrict__ x, uint8_t* __restr
   float amax = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) amax = fmaxf(amax, fabsf(ldf(x, base + (long long)(i / bc) * C + i % bc)));
   amax = block_max(amax, red);
-  const float sc = amax > 0.f ? amax / 448.f : 1.f;
-  const float inv = 1.f / sc;
+  const float sc = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;   // IEEE division: the build uses fast-math, the scales must match the CPU formula
+  const float inv = __frcp_rn(sc);
   if (threadIdx.x == 0) scale[((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x] = sc;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const long long at = base + (long long)(i / bc) * C + i % bc;
-    const float v = fminf(fmaxf(ldf(x, at) * inv, -448.f), 448.f);
+    const float v = fminf(fmaxf(__fmul_rn(ldf(x, at), inv), -448.f), 448.f);
     q[at] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
   }
 }
@@ -117,11 +117,11 @@ __global__ void fp8_quantize_rows_kernel(const T* __restrict__ x, uint8_t* __res
   for (int c = lane; c < D; c += 32) amax = fmaxf(amax, fabsf(ldf(x, row * x_row_stride + c)));
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-  const float sc = amax > 0.f ? amax / 448.f : 1.f;
-  const float inv = 1.f / sc;
+  const float sc = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;   // IEEE division: the build uses fast-math, the scales must match the CPU formula
+  const float inv = __frcp_rn(sc);
   if (lane == 0) scale[row] = sc;
   for (int c = lane; c < D; c += 32) {
-    const float v = fminf(fmaxf(ldf(x, row * x_row_stride + c) * inv, -448.f), 448.f);
+    const float v = fminf(fmaxf(__fmul_rn(ldf(x, row * x_row_stride + c), inv), -448.f), 448.f);
     q[row * q_row_stride + c] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3));
   }
 }
