@@ -66,7 +66,7 @@ def main():
         w.copy_((torch.randn(K, N, device=dev) / 64).bfloat16())
         local = torch.empty_like(w)
         x = torch.randn(M, K, device=dev).bfloat16()
-        flags = torch.zeros((K + 63) // 64, dtype=torch.int32, device=dev)
+        flags = torch.zeros((N + 255) // 256, dtype=torch.int32, device=dev)
         ep = [0]
 
         def fused():

@@ -48,6 +48,7 @@ struct GemmParams {
   int num_groups;
   int n_split;              // SwiGLU: column where the linear half starts in B (= hidden size)
   float swiglu_beta, swiglu_limit;
+  int raster_group;         // > 0: grouped raster with bands of this many M-tiles (takes precedence over raster_n_major)
   int raster_n_major;       // 1: consecutive tiles walk M first (the B operand is streamed once; used by the vocabulary GEMMs)
   // fused linear cross-entropy epilogues (B = the [V, C] head, N = real vocabulary size)
   const int* ce_y;          // [M] target ids
@@ -56,17 +57,18 @@ struct GemmParams {
   float* ce_tgt;            // [M] target logit                          (EPI_CE_FWD)
   const float* ce_lse;      // [M] log-sum-exp                           (EPI_CE_DZ)
   const float* ce_gscale;   // device scalar multiplying dZ              (EPI_CE_DZ)
-  // all-gather fused mode (ag_world > 0): B's K-rows live in peer GPUs' memory; two extra warps per CTA copy them in
-  // 64-row slabs into the local B buffer (the one the TMA map points at) and publish one flag per slab; the TMA
-  // producer waits for the slab's flag before loading it. TMA only ever reads local memory.
+  // all-gather fused mode (ag_world > 0): B's K-rows live in peer GPUs' memory; four extra warps per CTA copy them,
+  // one 256-column panel after the other, into the local B buffer (the one the TMA map points at) and count the
+  // finished pieces per panel; the TMA producer waits for a tile's panel before loading it. TMA only ever reads
+  // local memory.
   int ag_world;                      // 0 = off
   int ag_rows_per_rank;              // K-rows held by each rank (K for a single owner, K / world for row shards)
   int ag_my_rank;
   long long ag_row_bytes;            // bytes per K-row (ldb * 2)
   const void* ag_src[AG_MAX_RANKS];  // per-rank base of its rows (row index local to the rank)
   void* ag_dst;                      // local B buffer base
-  int* ag_flags;                     // [ceil(K / 64)] local flags
-  int ag_epoch;                      // value that marks a slab as landed in this call
+  int* ag_flags;                     // [ceil(N / 256)] local counters, one per column panel of B
+  int ag_epoch;                      // number of this call on these counters (1, 2, ...)
   int* status;
 };
 
@@ -98,7 +100,15 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
     }
   }
   int m_blk, n_blk;
-  if (p.raster_n_major) {
+  if (p.raster_group > 0) {
+    // grouped raster: tiles walk N inside a band of `raster_group` M-tiles, so a wave of CTAs shares a small set of A row
+    // panels and a run of B column panels (both stay in L2) instead of one operand in full
+    const int band = p.raster_group * p.n_tiles;
+    const int grp = local / band, within = local - grp * band;
+    const int gm = min(p.raster_group, p.m_tiles - grp * p.raster_group);
+    n_blk = within / gm;
+    m_blk = grp * p.raster_group + (within - n_blk * gm);
+  } else if (p.raster_n_major) {
     n_blk = local / p.m_tiles;
     m_blk = local - n_blk * p.m_tiles;
   } else {
@@ -172,6 +182,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const TileInfo t = decode_tile<BN, EPI>(p, tile);
         if (!t.valid) continue;
+        if (p.ag_world > 0) {  // this tile's 256-column panel of B must have landed in local memory before TMA reads it
+          const int* flag = p.ag_flags + t.n0 / BN;
+          const int want = p.ag_epoch * ((p.K + BK - 1) / BK);
+          const long long t0 = clock64();
+          int v;
+          do {
+            asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+            if (v < want && (clock64() - t0 > WAIT_LIMIT_CYCLES || *abortp)) {
+              atomicExch(p.status, STATUS_TIMEOUT_PEER);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+          } while (v < want);
+          if (!ok) break;
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < t.num_kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
@@ -191,23 +218,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * (BK * 128), &tma_a, bar, t.m0 + j * 64, k0, t.ga);
           } else {
             tma_load_3d(sa, &tma_a, bar, k0, t.m0, t.ga);
-          }
-          if (p.ag_world > 0) {  // the slab must have landed in local memory before TMA reads it
-            const int* flag = p.ag_flags + kb;
-            const int want = p.ag_epoch * int((p.ag_row_bytes / 2 + 1023) / 1024);
-            const long long t0 = clock64();
-            int v;
-            do {
-              asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-              if (v < want && (clock64() - t0 > WAIT_LIMIT_CYCLES || *abortp)) {
-                atomicExch(p.status, STATUS_TIMEOUT_PEER);
-                abort_flag = 1;
-                ok = false;
-                break;
-              }
-            } while (v < want);
-            if (!ok) break;
-            asm volatile("fence.proxy.async.global;" ::: "memory");
           }
           if (B_MN) {
 #pragma unroll
@@ -272,21 +282,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
   } else if (warp >= 6) {
     // ------------------------------------------------------------ peer copy warps (all-gather fused mode only)
     if (p.ag_world > 0) {
-      // Work unit: a piece = 64 K-rows x AG_PIECE_COLS columns. Pieces are dealt round-robin over all CTAs in K order, so
-      // the first slabs complete first; each finished piece bumps its slab's counter, a slab is ready at epoch * pieces.
-      constexpr int AG_PIECE_COLS = 1024;                        // elements; 2 KB per row
+      // Work unit: a piece = 64 K-rows x one 256-column panel (32 KB: one 16-byte load per thread and unrolled step).
+      // Pieces are numbered panel by panel and dealt round-robin over the CTAs, so B lands in the order in which the
+      // (column-panel-major) tile raster consumes it: the first tiles start after a few MB, the rest of the transfer
+      // hides behind the MMAs. Each finished piece bumps its panel's counter; a panel is ready at epoch * slabs.
       const int n_slabs = (p.K + BK - 1) / BK;
       const int row_elems = int(p.ag_row_bytes / 2);
-      const int pps = (row_elems + AG_PIECE_COLS - 1) / AG_PIECE_COLS;
+      const int n_panels = (p.N + BN - 1) / BN;
       const int t = threadIdx.x - 6 * 32;  // 0..127
-      for (int piece = blockIdx.x; piece < n_slabs * pps; piece += gridDim.x) {
-        const int slab = piece / pps, pc = piece - slab * pps;
+      for (int piece = blockIdx.x; piece < n_slabs * n_panels; piece += gridDim.x) {
+        const int panel = piece / n_slabs, slab = piece - panel * n_slabs;
         const int row0 = slab * BK;
         const int owner = row0 / p.ag_rows_per_rank;
         const int rows = min(BK, p.K - row0);
         if (owner != p.ag_my_rank || p.ag_src[owner] != p.ag_dst) {
-          const int col0 = pc * AG_PIECE_COLS;
-          const int v_per_row = min(AG_PIECE_COLS, row_elems - col0) / 8;      // uint4 per row of this piece
+          const int col0 = panel * BN;
+          const int v_per_row = min(BN, row_elems - col0) / 8;      // uint4 per row of this piece
           const uint8_t* sbase = static_cast<const uint8_t*>(p.ag_src[owner]) + (long long)(row0 - owner * p.ag_rows_per_rank) * p.ag_row_bytes + col0 * 2;
           uint8_t* dbase = static_cast<uint8_t*>(p.ag_dst) + (long long)row0 * p.ag_row_bytes + col0 * 2;
           const int total = rows * v_per_row;
@@ -308,7 +319,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         __threadfence();
         asm volatile("fence.proxy.async.global;" ::: "memory");
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (t == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_flags + slab) : "memory");
+        if (t == 0) asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(p.ag_flags + panel) : "memory");
       }
     }
   } else {
@@ -553,6 +564,21 @@ using namespace lyra;
 //   K-major  operand: rows = M (or N), cols = K        -> mn_major = 0
 //   MN-major operand: rows = K,        cols = M (or N)  -> mn_major = 1
 // `ld` = elements between rows, `group_stride` = elements between stacked matrices (0 if not stacked).
+// Band height (in 128-row tiles) of the grouped tile raster. Measured on B200 (8192 x N x 4096, bf16): bands of 8 take
+// N = 12288 from 1244 to 1430 TFLOP/s (forward) and from 1139 to 1305 (weight gradient) and change nothing at N = 4096, where
+// a wave of 148 tiles already spans every column panel; so bands are used from 32 column panels on.
+// LYRA_GEMM_RASTER_GROUP overrides the choice for every shape (0 = plain M-major).
+static int default_raster_group(int n_tiles) {
+  static int forced = -2;
+  if (forced == -2) {
+    const char* e = getenv("LYRA_GEMM_RASTER_GROUP");
+    forced = e ? atoi(e) : -1;
+    if (forced < -1 || forced > 1024) forced = -1;
+  }
+  if (forced >= 0) return forced;
+  return n_tiles >= 32 ? 8 : 0;
+}
+
 extern "C" int lyra_gemm_bf16(
     const void* A, long long lda, long long a_group_stride, int a_mn,
     const void* B, long long ldb, long long b_group_stride, int b_mn,
@@ -573,11 +599,12 @@ extern "C" int lyra_gemm_bf16(
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = bias_group_stride;
   p.group_mode = group_mode; p.tile_group = tile_group; p.group_offsets = group_offsets; p.num_groups = G;
   p.n_split = n_split; p.swiglu_beta = swiglu_beta; p.swiglu_limit = swiglu_limit; p.status = status;
-  p.ag_world = 0; p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
+  p.ag_world = 0; p.raster_n_major = 0; p.raster_group = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.m_tiles = (M + BM - 1) / BM;
   if (epilogue == EPI_SWIGLU) p.n_tiles = (n_split + BN / 2 - 1) / (BN / 2);
   else p.n_tiles = (N + BN - 1) / BN;
   p.total_tiles = p.m_tiles * p.n_tiles * ((group_mode == GROUP_K || group_mode == GROUP_BATCH) ? G : 1);
+  p.raster_group = default_raster_group(p.n_tiles);
 
   // Tensor maps (3-D: inner, rows, group). Row counts seen by TMA:
   //  A K-major : dims {K, rows_a, Ga};  A MN-major: dims {M, krows, Ga}
@@ -638,7 +665,7 @@ extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long lo
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
   p.ag_world = 0;
-  p.raster_n_major = 1;
+  p.raster_n_major = 1; p.raster_group = 0;
   p.ce_y = y; p.ce_part_m = part_m; p.ce_part_l = part_l; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_gscale = gscale;
   p.m_tiles = (M + BM - 1) / BM;
   p.n_tiles = (vocab + BN - 1) / BN;
@@ -701,8 +728,8 @@ extern "C" int lyra_ce_merge(const float* part_m, const float* part_l, const flo
 
 // y[M, N] = x[M, K] @ W[K, N] where W's rows live on peer GPUs (all-gather fused into the GEMM). `w_local` is this
 // rank's full-size [K, N] buffer that the kernel fills (rows owned by this rank must already be in place when
-// src[my_rank] == w_local); `src[r]` is rank r's peer-mapped base of its rows. `flags` holds ceil(K/64) ints and
-// `epoch` counts the calls made on these flags (1, 2, ...; the flags start at zero and each call adds one per piece).
+// src[my_rank] == w_local); `src[r]` is rank r's peer-mapped base of its rows. `flags` holds ceil(N/256) counters and
+// `epoch` counts the calls made on them (1, 2, ...; they start at zero and each call adds ceil(K/64) to each).
 extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_local, long long ldw, const long long* src, int world, int my_rank,
                                         int rows_per_rank, void* y, const void* c_in, long long ldy, int M, int N, int K, float alpha, float beta,
                                         const float* bias, int* flags, int epoch, int* status, void* stream) {
@@ -715,7 +742,9 @@ extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_lo
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = 0;
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
-  p.raster_n_major = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
+  p.raster_group = 0;
+  p.raster_n_major = 1;  // tiles walk M first, column panel by column panel: the order in which the panels of B arrive
+  p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.ag_world = world; p.ag_rows_per_rank = rows_per_rank; p.ag_my_rank = my_rank; p.ag_row_bytes = ldw * 2;
   for (int r = 0; r < AG_MAX_RANKS; ++r) p.ag_src[r] = r < world ? reinterpret_cast<const void*>(src[r]) : nullptr;
   p.ag_dst = w_local; p.ag_flags = flags; p.ag_epoch = epoch;

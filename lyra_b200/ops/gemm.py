@@ -163,11 +163,11 @@ def gemm_allgather(x: torch.Tensor, w_local: torch.Tensor, src_ptrs: list[int], 
                    out: torch.Tensor | None = None) -> torch.Tensor:
     """``x [M, K] @ W [K, N]`` where the rows of ``W`` live in peer GPUs' memory: the all-gather is fused into the GEMM.
 
-    ``w_local [K, N]`` is this rank's full-size bf16 buffer, filled by the kernel slab by slab (64 rows) while the
-    tensor cores already work on the slabs that have landed; ``src_ptrs[r]`` is the peer-mapped address of rank r's rows
+    ``w_local [K, N]`` is this rank's full-size bf16 buffer, filled by the kernel one 256-column panel after the other
+    while the tensor cores already work on the panels that have landed; ``src_ptrs[r]`` is the peer-mapped address of rank r's rows
     (``rows_per_rank`` each; a single owner is ``rows_per_rank = K`` with the owner's address in slot 0). ``flags`` is an
-    int32 tensor with at least ``ceil(K / 64)`` entries, zero before the first call; ``epoch`` is the number of this call on
-    those flags (1, 2, ...), always with the same ``N``.
+    int32 tensor with at least ``ceil(N / 256)`` entries, zero before the first call; ``epoch`` is the number of this call on
+    those flags (1, 2, ...), always with the same ``K`` and ``N``.
     After the call ``w_local`` holds the whole matrix and can be used by ordinary GEMMs."""
     import ctypes
 
@@ -175,7 +175,7 @@ def gemm_allgather(x: torch.Tensor, w_local: torch.Tensor, src_ptrs: list[int], 
     M, K = x.shape
     Kw, N = w_local.shape
     assert K == Kw and w_local.dtype == torch.bfloat16 and w_local.stride(1) == 1
-    assert flags.dtype == torch.int32 and flags.numel() >= (K + 63) // 64
+    assert flags.dtype == torch.int32 and flags.numel() >= (N + 255) // 256
     if out is None:
         out = torch.empty(M, N, dtype=torch.bfloat16, device=x.device)
     lib = native.kernels()

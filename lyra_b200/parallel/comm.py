@@ -156,9 +156,9 @@ class Comm:
         """Description of the pending fused pull of ``name`` for ``ops.gemm.gemm_allgather``, or None."""
         if not self.pending.get(name):
             return None
-        K = self.entries_by_name[name][0][0]
         if name not in self.ag_flags:
-            self.ag_flags[name] = torch.zeros((K + 63) // 64, dtype=torch.int32, device=self.device)
+            n_cols = self.numel[name] // self.entries_by_name[name][0][0]
+            self.ag_flags[name] = torch.zeros((n_cols + 255) // 256, dtype=torch.int32, device=self.device)
             self.ag_calls[name] = 0
         owner = self.owner[name]
 
