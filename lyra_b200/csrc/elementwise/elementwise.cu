@@ -137,8 +137,12 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
 // ------------------------------------------------------------------------------------------------ SwiGLU
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
 
-__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ out, long long M, int H, float beta, float limit) {
+// `rows_dev` (optional): device-resident number of leading rows that hold data; rows beyond it are left untouched (the
+// expert-parallel receive buffers are sized for the worst case and mostly empty).
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bfloat16* __restrict__ out, long long M, int H, float beta, float limit,
+                                  const int* __restrict__ rows_dev) {
   const int hv = H / 8;
+  if (rows_dev) M = min(M, (long long)*rows_dev);
   const long long total = M * hv;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long m = i / hv;
@@ -156,8 +160,9 @@ __global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ pre, __nv_bf
 }
 
 __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ pre, const __nv_bfloat16* __restrict__ dact, __nv_bfloat16* __restrict__ dpre,
-                                  long long M, int H, float beta, float limit) {
+                                  long long M, int H, float beta, float limit, const int* __restrict__ rows_dev) {
   const int hv = H / 8;
+  if (rows_dev) M = min(M, (long long)*rows_dev);
   const long long total = M * hv;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
     const long long m = i / hv;
@@ -336,14 +341,30 @@ extern "C" int lyra_rmsnorm_bwd(const void* x, const float* scale, const float* 
 
 extern "C" int lyra_swiglu_fwd(const void* pre, void* out, long long M, int H, float beta, float limit, void* stream) {
   if (M <= 0) return 0;
-  swiglu_fwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), BFP(out), M, H, beta, limit);
+  swiglu_fwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), BFP(out), M, H, beta, limit, nullptr);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+// As above for the first *rows_dev rows only (rows_dev: int32 on the device, read by the kernel).
+extern "C" int lyra_swiglu_fwd_rows(const void* pre, void* out, long long M, int H, float beta, float limit, const int* rows_dev, void* stream) {
+  if (M <= 0) return 0;
+  swiglu_fwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), BFP(out), M, H, beta, limit, rows_dev);
   LYRA_CHECK_LAUNCH();
   return 0;
 }
 
 extern "C" int lyra_swiglu_bwd(const void* pre, const void* dact, void* dpre, long long M, int H, float beta, float limit, void* stream) {
   if (M <= 0) return 0;
-  swiglu_bwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), CBFP(dact), BFP(dpre), M, H, beta, limit);
+  swiglu_bwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), CBFP(dact), BFP(dpre), M, H, beta, limit, nullptr);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_swiglu_bwd_rows(const void* pre, const void* dact, void* dpre, long long M, int H, float beta, float limit, const int* rows_dev,
+                                    void* stream) {
+  if (M <= 0) return 0;
+  swiglu_bwd_kernel<<<ew_grid(M * (H / 8), 256), 256, 0, S_(stream)>>>(CBFP(pre), CBFP(dact), BFP(dpre), M, H, beta, limit, rows_dev);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

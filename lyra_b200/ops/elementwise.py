@@ -228,24 +228,35 @@ def gate_xsa(t, h, w_gate, v, xsa_alpha):
 
 
 # --------------------------------------------------------------------------- SwiGLU
-def swiglu_fwd(pre: torch.Tensor, beta: float, limit: float) -> torch.Tensor:
-    """``pre [M, 2H]`` (gate columns then linear columns) -> ``[M, H]``."""
+def swiglu_fwd(pre: torch.Tensor, beta: float, limit: float, rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """``pre [M, 2H]`` (gate columns then linear columns) -> ``[M, H]``. With ``rows_dev`` (int32 device scalar) only that
+    many leading rows are computed and the rest of the output is left uninitialised."""
     M, H2 = pre.shape
     H = H2 // 2
     if pre.dtype == BF16 and _has("lyra_swiglu_fwd") and H % 8 == 0:
         out = torch.empty(M, H, dtype=BF16, device=pre.device)
+        if rows_dev is not None:
+            native.check(_lib().lyra_swiglu_fwd_rows(ptr(pre), ptr(out), c_ll(M), c_int(H), c_float(beta), c_float(limit), ptr(rows_dev),
+                                                     native.stream_ptr()), "swiglu_fwd_rows")
+            native.count_launch()
+            return out
         native.check(_lib().lyra_swiglu_fwd(ptr(pre), ptr(out), c_ll(M), c_int(H), c_float(beta), c_float(limit), native.stream_ptr()), "swiglu_fwd")
         native.count_launch()
         return out
     return ref.swiglu(pre.float().view(M, 2, H), beta, limit).to(pre.dtype)
 
 
-def swiglu_bwd(pre: torch.Tensor, dact: torch.Tensor, beta: float, limit: float) -> torch.Tensor:
-    """Gradient w.r.t. ``pre [M, 2H]`` given ``dact [M, H]``; clamped regions pass no gradient."""
+def swiglu_bwd(pre: torch.Tensor, dact: torch.Tensor, beta: float, limit: float, rows_dev: torch.Tensor | None = None) -> torch.Tensor:
+    """Gradient w.r.t. ``pre [M, 2H]`` given ``dact [M, H]``; clamped regions pass no gradient. ``rows_dev`` as in ``swiglu_fwd``."""
     M, H2 = pre.shape
     H = H2 // 2
     if pre.dtype == BF16 and dact.dtype == BF16 and _has("lyra_swiglu_bwd") and H % 8 == 0:
         out = torch.empty_like(pre)
+        if rows_dev is not None:
+            native.check(_lib().lyra_swiglu_bwd_rows(ptr(pre), ptr(dact.contiguous()), ptr(out), c_ll(M), c_int(H), c_float(beta), c_float(limit),
+                                                     ptr(rows_dev), native.stream_ptr()), "swiglu_bwd_rows")
+            native.count_launch()
+            return out
         native.check(_lib().lyra_swiglu_bwd(ptr(pre), ptr(dact.contiguous()), ptr(out), c_ll(M), c_int(H), c_float(beta), c_float(limit),
                                             native.stream_ptr()), "swiglu_bwd")
         native.count_launch()

@@ -219,9 +219,11 @@ class _EPMoEKernel(torch.autograd.Function):
         x_recv = ex.dispatch(xn, K, bufs["recv"], bufs["meta"])
         wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
         cap = ex.buf.cap
+        # The receive buffer is sized for the worst case; only the 128-row tiles that belong to an expert are computed,
+        # and only those rows are read afterwards, so the outputs need no zero fill.
         act = G.grouped_gemm(x_recv, wu, ex.tile_group, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
-                             out=torch.zeros(cap, H, dtype=BF16, device=xn.device))
-        down = G.grouped_gemm(act, wd, ex.tile_group, out=torch.zeros(cap, C, dtype=BF16, device=xn.device))
+                             out=torch.empty(cap, H, dtype=BF16, device=xn.device))
+        down = G.grouped_gemm(act, wd, ex.tile_group, out=torch.empty(cap, C, dtype=BF16, device=xn.device))
         ret = ex.collect(down, bufs["meta"], bufs["ret"])
         ident = torch.arange(F_ * K, device=xn.device)
         out = ew.combine_rows(ret, ident, scores, F_, K)
@@ -244,24 +246,24 @@ class _EPMoEKernel(torch.autograd.Function):
         d_down = ex.dispatch(d_ret, 1, ex.buf.scratch_recv[par], None)
         x_recv = bufs["recv"].view(0, cap * C, BF16).view(cap, C)
         wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
-        pre = G.grouped_gemm(x_recv, wu, ex.tile_group, out=torch.zeros(cap, 2 * H, dtype=BF16, device=dev))
-        act = ew.swiglu_fwd(pre, beta, limit)
+        pre = G.grouped_gemm(x_recv, wu, ex.tile_group, out=torch.empty(cap, 2 * H, dtype=BF16, device=dev))
+        act = ew.swiglu_fwd(pre, beta, limit, rows_dev=ex.total)
         gd = cuda_ops.GRAD_DTYPE
         if w_down.requires_grad:
             if w_down.grad is None:
                 w_down.grad = G.grouped_wgrad(act, d_down, ex.offsets, El).to(gd)
             else:
                 G.grouped_wgrad(act, d_down, ex.offsets, El, out=w_down.grad, accumulate=True)
-        d_act = G.grouped_gemm(d_down, wd, ex.tile_group, w_kmajor=True, out=torch.zeros(cap, H, dtype=BF16, device=dev))
+        d_act = G.grouped_gemm(d_down, wd, ex.tile_group, w_kmajor=True, out=torch.empty(cap, H, dtype=BF16, device=dev))
         del act
-        d_pre = ew.swiglu_bwd(pre, d_act, beta, limit)
+        d_pre = ew.swiglu_bwd(pre, d_act, beta, limit, rows_dev=ex.total)
         del pre, d_act
         if w_up.requires_grad:
             if w_up.grad is None:
                 w_up.grad = G.grouped_wgrad(x_recv, d_pre, ex.offsets, El).view(w_up.shape).to(gd)
             else:
                 G.grouped_wgrad(x_recv, d_pre, ex.offsets, El, out=w_up.grad.view(El, C, 2 * H), accumulate=True)
-        dx_recv = G.grouped_gemm(d_pre, wu, ex.tile_group, w_kmajor=True, out=torch.zeros(cap, C, dtype=BF16, device=dev))
+        dx_recv = G.grouped_gemm(d_pre, wu, ex.tile_group, w_kmajor=True, out=torch.empty(cap, C, dtype=BF16, device=dev))
         dx_a = ex.collect(dx_recv, bufs["meta"], ex.buf.scratch_ret[par])
         dxn = ew.gather_sum_rows(dx_a, ident, F_, K)
         return dxn, dscores, None, None, None, None, None

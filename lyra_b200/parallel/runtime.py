@@ -63,12 +63,34 @@ class Plan:
                 dense.append((n, path))
             else:
                 plan.replicated.add(path)
-        load = [0] * world
-        for n, path in sorted(dense, key=lambda x: (-x[0], x[1])):
+        # Owners are balanced by the estimated time of the owner's optimizer work, not by size: a Muon matrix costs five
+        # Newton-Schulz iterations of tensor-core GEMMs (about 25k FLOP per element at 4096 x 4096), an Adam leaf (the
+        # embeddings) only a few bytes of HBM traffic per element, so equal sizes would leave the embedding owners idle.
+        load = [0.0] * world
+        costed = [(_owner_cost(path, plan.specs[path]), n, path) for n, path in dense]
+        for cost, n, path in sorted(costed, key=lambda x: (-x[0], x[2])):
             r = min(range(world), key=lambda i: (load[i], i))
             plan.owner[path] = r
-            load[r] += n
+            load[r] += cost
         return plan
+
+
+def _owner_cost(path: str, spec: ArraySpec) -> float:
+    """Seconds (nominal) the owning rank spends on one optimizer step of this leaf."""
+    from lyra_b200.training.optimizer import is_mlp_up
+
+    n = math.prod(spec.shape)
+    if spec.tag != Tag.MATRIX:
+        return n * 20.0 / 6.0e12                                   # Adam: parameter, gradient, two moments, bf16 copy
+    if is_mlp_up(path):
+        *lead, rows, two, cols = spec.shape
+        mats = (math.prod(lead) if lead else 1) * two
+    else:
+        *lead, rows, cols = spec.shape
+        mats = math.prod(lead) if lead else 1
+    m, k = min(rows, cols), max(rows, cols)
+    ns_flops = 5.0 * (4.0 * m * m * k + 2.0 * m ** 3) * mats
+    return ns_flops / 1.3e15 + n * 14.0 / 6.0e12
 
 
 class Runtime:
