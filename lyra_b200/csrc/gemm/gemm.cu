@@ -25,6 +25,8 @@ namespace lyra {
 constexpr int BM = 128;
 constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
+constexpr int MIRROR_LD = 136;           // row length (elements) of the 32 x 128 staging tile used to mirror symmetric results
+constexpr int MIRROR_BYTES = 32 * MIRROR_LD * 2;
 constexpr int GEMM_THREADS_AG = 320;   // + four warps that pull the B operand from peer GPUs (all-gather fused GEMM)
 constexpr int AG_MAX_RANKS = 16;
 
@@ -48,6 +50,9 @@ struct GemmParams {
   int num_groups;
   int n_split;              // SwiGLU: column where the linear half starts in B (= hidden size)
   float swiglu_beta, swiglu_limit;
+  int sym_tiles;            // tiles per matrix that are enumerated when sym_upper is set
+  int sym_upper;            // 1: the result is symmetric (A A^T): tiles wholly below the diagonal are not enumerated; bf16 outputs are mirrored by
+                            //    the epilogue of the upper tiles, fp32 outputs by `lyra_symmetrize`
   int raster_group;         // > 0: grouped raster with bands of this many M-tiles (takes precedence over raster_n_major)
   int raster_n_major;       // 1: consecutive tiles walk M first (the B operand is streamed once; used by the vocabulary GEMMs)
   // fused linear cross-entropy epilogues (B = the [V, C] head, N = real vocabulary size)
@@ -87,7 +92,7 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
   t.num_kb = (p.K + BK - 1) / BK;
   int local = tile;
   if (p.group_mode == GROUP_K || p.group_mode == GROUP_BATCH) {
-    const int per = p.m_tiles * p.n_tiles;
+    const int per = p.sym_upper ? p.sym_tiles : p.m_tiles * p.n_tiles;
     const int g = tile / per;
     local = tile - g * per;
     t.gc = g;
@@ -100,7 +105,19 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
     }
   }
   int m_blk, n_blk;
-  if (p.raster_group > 0) {
+  if (p.sym_upper) {
+    // symmetric result: only tiles that reach the diagonal or lie above it are enumerated (row m starts at column tile
+    // m * BM / NSTEP), so the persistent CTAs share the real work evenly instead of drawing skipped tiles
+    int m = 0, acc = 0;
+    for (;;) {
+      const int cnt = p.n_tiles - min(p.n_tiles, m * BM / NSTEP);
+      if (local < acc + cnt || m + 1 >= p.m_tiles) break;
+      acc += cnt;
+      ++m;
+    }
+    m_blk = m;
+    n_blk = m * BM / NSTEP + (local - acc);
+  } else if (p.raster_group > 0) {
     // grouped raster: tiles walk N inside a band of `raster_group` M-tiles, so a wave of CTAs shares a small set of A row
     // panels and a run of B column panels (both stay in L2) instead of one operand in full
     const int band = p.raster_group * p.n_tiles;
@@ -359,6 +376,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             for (int i = 0; i < 32; ++i) r[i] = 0u;
           }
           const int col = t.n0 + c * 32;
+          const bool mirror = p.sym_upper && !p.out_fp32 && col < p.N && BN * (t.m0 / BN + 1) <= BM * (col / BM);   // same for all 4 warps
           if (row_ok && col < p.N) {
             float v[32];
 #pragma unroll
@@ -406,7 +424,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
                   *reinterpret_cast<uint4*>(dst + q * 8) = o;
                 }
               }
+              if (mirror) {   // stage this row's 32 values column-wise: stg[j][row_in_tile]
+                __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * STAGE_BYTES);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) stg[i * MIRROR_LD + row_in_tile] = __float2bfloat16(v[i]);
+              }
             }
+          }
+          // Symmetric result: the mirror image of this 32-column piece lies in a tile that was skipped iff that tile is
+          // wholly below the diagonal. The four epilogue warps then write it from the staged copy, 16 bytes per store:
+          // C[col + j][m0 .. m0 + 127] = stg[j][0 .. 127].
+          if (mirror) {
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const __nv_bfloat16* stg = reinterpret_cast<const __nv_bfloat16*>(smem + STAGES * STAGE_BYTES);
+            __nv_bfloat16* cbase = reinterpret_cast<__nv_bfloat16*>(p.C) + (long long)t.gc * p.c_group_stride;
+#pragma unroll
+            for (int pass = 0; pass < 4; ++pass) {
+              const int piece = row_in_tile + 128 * pass, j = piece >> 4, part = piece & 15;
+              if (col + j < p.N && t.m0 + part * 8 < p.M)
+                *reinterpret_cast<uint4*>(cbase + (long long)(col + j) * p.ldc + t.m0 + part * 8) =
+                    *reinterpret_cast<const uint4*>(stg + j * MIRROR_LD + part * 8);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
           }
         }
       } else if (EPI == EPI_CE_FWD) {
@@ -536,7 +575,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 
 template <int BN>
 constexpr int gemm_smem_bytes() {
-  return ((BN == 256) ? 4 : 6) * (BM * BK * 2 + BN * BK * 2) + 1024;
+  return ((BN == 256) ? 4 : 6) * (BM * BK * 2 + BN * BK * 2) + 1024 + MIRROR_BYTES;
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
@@ -586,10 +625,11 @@ extern "C" int lyra_gemm_bf16(
     int M, int N, int K, float alpha, float beta,
     const float* bias, long long bias_group_stride,
     int group_mode, int num_groups, const int* tile_group, const int* group_offsets, int total_rows,
-    int epilogue, int n_split, float swiglu_beta, float swiglu_limit,
+    int epilogue, int n_split, float swiglu_beta, float swiglu_limit, int sym_upper,
     int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8))) return -10;
+  if (sym_upper && (M != N || epilogue != EPI_STORE || group_mode == GROUP_M || group_mode == GROUP_K)) return -14;
   const int G = num_groups > 0 ? num_groups : 1;
   constexpr int BN = 256;
 
@@ -599,12 +639,17 @@ extern "C" int lyra_gemm_bf16(
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = bias_group_stride;
   p.group_mode = group_mode; p.tile_group = tile_group; p.group_offsets = group_offsets; p.num_groups = G;
   p.n_split = n_split; p.swiglu_beta = swiglu_beta; p.swiglu_limit = swiglu_limit; p.status = status;
-  p.ag_world = 0; p.raster_n_major = 0; p.raster_group = 0; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
+  p.ag_world = 0; p.raster_n_major = 0; p.raster_group = 0; p.sym_upper = sym_upper; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.m_tiles = (M + BM - 1) / BM;
   if (epilogue == EPI_SWIGLU) p.n_tiles = (n_split + BN / 2 - 1) / (BN / 2);
   else p.n_tiles = (N + BN - 1) / BN;
   p.total_tiles = p.m_tiles * p.n_tiles * ((group_mode == GROUP_K || group_mode == GROUP_BATCH) ? G : 1);
   p.raster_group = default_raster_group(p.n_tiles);
+  p.sym_tiles = 0;
+  if (sym_upper) {
+    for (int m = 0; m < p.m_tiles; ++m) p.sym_tiles += p.n_tiles - (p.n_tiles < m * BM / BN ? p.n_tiles : m * BM / BN);
+    p.total_tiles = p.sym_tiles * (group_mode == GROUP_BATCH ? G : 1);
+  }
 
   // Tensor maps (3-D: inner, rows, group). Row counts seen by TMA:
   //  A K-major : dims {K, rows_a, Ga};  A MN-major: dims {M, krows, Ga}
@@ -650,6 +695,35 @@ extern "C" int lyra_gemm_bf16(
 }
 
 
+// Mirrors the upper triangle of G stacked n x n matrices into the lower one: C[r][c] = C[c][r] for r > c (32 x 32 tiles through
+// shared memory so that both the read and the write are row-contiguous). Completes a product launched with `sym_upper`.
+template <typename T>
+__global__ void symmetrize_kernel(T* __restrict__ C, long long ld, long long group_stride, int n) {
+  __shared__ T tile[32][33];
+  const int bi = blockIdx.y, bj = blockIdx.x;   // destination block (rows bi, columns bj), bi >= bj
+  if (bj > bi) return;
+  T* base = C + (long long)blockIdx.z * group_stride;
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {   // source block: rows bj*32.., columns bi*32..
+    const int sr = bj * 32 + r, sc = bi * 32 + threadIdx.x;
+    if (sr < n && sc < n) tile[r][threadIdx.x] = base[(long long)sr * ld + sc];
+  }
+  __syncthreads();
+  for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+    const int dr = bi * 32 + r, dc = bj * 32 + threadIdx.x;
+    if (dr < n && dc < n && dr > dc) base[(long long)dr * ld + dc] = tile[threadIdx.x][r];
+  }
+}
+
+extern "C" int lyra_symmetrize(void* C, long long ld, long long group_stride, int n, int G, int is_fp32, void* stream) {
+  if (n <= 0 || G <= 0) return 0;
+  dim3 grid((n + 31) / 32, (n + 31) / 32, G), block(32, 8);
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  if (is_fp32) symmetrize_kernel<float><<<grid, block, 0, s>>>(static_cast<float*>(C), ld, group_stride, n);
+  else symmetrize_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(static_cast<__nv_bfloat16*>(C), ld, group_stride, n);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
 // Fused output head + cross entropy, forward: x [M, K] bf16, w [V, K] bf16 (first `vocab` rows used).
 // Writes per-tile partial (max, sum-exp) [ceil(vocab/256), M] and the target logit [M]; `lyra_ce_merge` finishes.
 // mode 0 = forward partials; mode 1 = dZ[M, vocab] (ld = ldz) = (softmax - onehot) * (*gscale).
@@ -665,7 +739,7 @@ extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long lo
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
   p.ag_world = 0;
-  p.raster_n_major = 1; p.raster_group = 0;
+  p.raster_n_major = 1; p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0;
   p.ce_y = y; p.ce_part_m = part_m; p.ce_part_l = part_l; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_gscale = gscale;
   p.m_tiles = (M + BM - 1) / BM;
   p.n_tiles = (vocab + BN - 1) / BN;
@@ -742,7 +816,7 @@ extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_lo
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = 0;
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
-  p.raster_group = 0;
+  p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0;
   p.raster_n_major = 1;  // tiles walk M first, column panel by column panel: the order in which the panels of B arrive
   p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.ag_world = world; p.ag_rows_per_rank = rows_per_rank; p.ag_my_rank = my_rank; p.ag_row_bytes = ldw * 2;

@@ -23,7 +23,7 @@ TILE_M = 128
 
 def _raw(
     a, lda, a_gs, a_mn, b, ldb, b_gs, b_mn, c, c_in, ldc, c_gs, out_fp32, M, N, K, alpha, beta, bias, bias_gs,
-    group_mode, num_groups, tile_group, group_offsets, total_rows, epilogue, n_split, swiglu_beta, swiglu_limit,
+    group_mode, num_groups, tile_group, group_offsets, total_rows, epilogue, n_split, swiglu_beta, swiglu_limit, sym_upper=False,
 ):
     lib = native.kernels()
     fn = lib.lyra_gemm_bf16
@@ -35,7 +35,7 @@ def _raw(
         c_int(M), c_int(N), c_int(K), c_float(alpha), c_float(beta),
         ptr(bias), c_ll(bias_gs),
         c_int(group_mode), c_int(num_groups), ptr(tile_group), ptr(group_offsets), c_int(total_rows),
-        c_int(epilogue), c_int(n_split), c_float(swiglu_beta), c_float(swiglu_limit),
+        c_int(epilogue), c_int(n_split), c_float(swiglu_beta), c_float(swiglu_limit), c_int(int(sym_upper)),
         ptr(native.status_word()), native.stream_ptr(),
     )
     native.check(rc, "lyra_gemm_bf16")
@@ -91,8 +91,13 @@ def gemm_swiglu(x: torch.Tensor, w: torch.Tensor, *, bias: torch.Tensor | None =
     return out
 
 
-def batched_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, out=None, alpha=1.0, beta=0.0, c_in=None) -> torch.Tensor:
-    """Stacked independent products, ``a``/``b`` are ``[G, rows, cols]`` bf16 with the per-matrix meaning of ``gemm``."""
+def batched_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, out=None, alpha=1.0, beta=0.0, c_in=None,
+                 symmetric: bool = False) -> torch.Tensor:
+    """Stacked independent products, ``a``/``b`` are ``[G, rows, cols]`` bf16 with the per-matrix meaning of ``gemm``.
+
+    ``symmetric=True`` declares the result symmetric (``X X^T``, ``X^T X``, ``A A`` with ``A`` symmetric, and ``c_in``
+    symmetric too): the tiles wholly below the diagonal (47 % of them at 4096 x 4096) are not computed but mirrored from the
+    upper triangle (by the epilogue of the upper tiles for bf16 results, by a second kernel for fp32 ones)."""
     G = a.shape[0]
     K, M = a.shape[1:] if a_mn else a.shape[1:][::-1]
     Kb, N = b.shape[1:] if b_mn else b.shape[1:][::-1]
@@ -100,7 +105,13 @@ def batched_gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn=False, b_mn=False, ou
     if out is None:
         out = torch.empty(G, M, N, dtype=torch.bfloat16, device=a.device)
     _raw(a, a.stride(1), a.stride(0), a_mn, b, b.stride(1), b.stride(0), b_mn, out, c_in, out.stride(1), out.stride(0),
-         out.dtype == torch.float32, M, N, K, alpha, beta, None, 0, GROUP_BATCH, G, None, None, 0, EPI_STORE, 0, 0.0, 0.0)
+         out.dtype == torch.float32, M, N, K, alpha, beta, None, 0, GROUP_BATCH, G, None, None, 0, EPI_STORE, 0, 0.0, 0.0,
+         sym_upper=symmetric and M == N and M >= 512)
+    if symmetric and M == N and M >= 512 and out.dtype == torch.float32:   # bf16 results are mirrored inside the GEMM epilogue
+        lib = native.kernels()
+        native.check(lib.lyra_symmetrize(ptr(out), c_ll(out.stride(1)), c_ll(out.stride(0)), c_int(M), c_int(G), c_int(int(out.dtype == torch.float32)),
+                                         native.stream_ptr()), "lyra_symmetrize")
+        native.count_launch()
     return out
 
 

@@ -43,12 +43,12 @@ def newtonschulz_gemm(X: torch.Tensor) -> torch.Tensor:
     Y = torch.empty_like(X)
     for a, b, c in POLAR_EXPRESS_COEFFS:
         if tall:
-            G.batched_gemm(X, X, a_mn=True, b_mn=True, out=A)            # X^T X
-            G.batched_gemm(A, A, out=B, alpha=c, beta=b, c_in=A)         # bA + cA^2  (A symmetric)
+            G.batched_gemm(X, X, a_mn=True, b_mn=True, out=A, symmetric=True)            # X^T X
+            G.batched_gemm(A, A, out=B, alpha=c, beta=b, c_in=A, symmetric=True)         # bA + cA^2  (A symmetric)
             G.batched_gemm(X, B, out=Y, alpha=1.0, beta=a, c_in=X)       # aX + X B   (B symmetric)
         else:
-            G.batched_gemm(X, X, out=A)                                  # X X^T
-            G.batched_gemm(A, A, out=B, alpha=c, beta=b, c_in=A)
+            G.batched_gemm(X, X, out=A, symmetric=True)                                  # X X^T
+            G.batched_gemm(A, A, out=B, alpha=c, beta=b, c_in=A, symmetric=True)
             G.batched_gemm(B, X, b_mn=True, out=Y, alpha=1.0, beta=a, c_in=X)
         X, Y = Y, X
     return X

@@ -113,3 +113,42 @@ def test_batched_gemm():
     assert _rel(a, x.float() @ x.float().transpose(1, 2)) < 1e-2
     y = G.batched_gemm(a, x, b_mn=True, alpha=0.5, beta=2.0, c_in=x)  # 0.5 A X + 2 X
     assert _rel(y, 0.5 * (a.float() @ x.float()) + 2 * x.float()) < 1e-2
+
+
+@pytest.mark.parametrize("shape", [(2, 1024, 1536), (1, 2048, 512), (3, 640, 640)])
+def test_symmetric_products_skip_lower_tiles(shape):
+    """X X^T and X^T X declared symmetric: upper-triangle tiles computed, lower ones mirrored; equals the full product."""
+    from lyra_b200.ops import gemm as G, native
+
+    Gn, m, n = shape
+    torch.manual_seed(0)
+    X = (torch.randn(Gn, m, n, device="cuda") / n ** 0.5).bfloat16()
+    full = G.batched_gemm(X, X)
+    sym = torch.full_like(full, float("nan"))
+    G.batched_gemm(X, X, out=sym, symmetric=True)
+    native.check_status()
+    assert torch.isfinite(sym.float()).all()
+    assert torch.equal(sym, sym.transpose(1, 2)) or (sym.float() - sym.float().transpose(1, 2)).abs().max().item() < 1e-2
+    assert (sym.float() - full.float()).abs().max().item() < 2e-2
+    full_t = G.batched_gemm(X, X, a_mn=True, b_mn=True)
+    sym_t = torch.full_like(full_t, float("nan"))
+    G.batched_gemm(X, X, a_mn=True, b_mn=True, out=sym_t, symmetric=True)
+    assert (sym_t.float() - full_t.float()).abs().max().item() < 2e-2
+    # B = c A A + b A with A symmetric
+    A = sym.clone()
+    ref = 0.5 * (A.float() @ A.float()) - 1.5 * A.float()
+    B = torch.full_like(A, float("nan"))
+    G.batched_gemm(A, A, out=B, alpha=0.5, beta=-1.5, c_in=A, symmetric=True)
+    assert (B.float() - ref).abs().max().item() < 5e-2 * max(1.0, ref.abs().max().item())
+
+
+def test_newton_schulz_gemm_matches_torch():
+    from lyra_b200.training.optimizer_cuda import _ns_unnormalised, newtonschulz_gemm
+
+    torch.manual_seed(1)
+    for shape in [(2, 1024, 2048), (1, 2048, 1024)]:
+        X = torch.randn(*shape, device="cuda")
+        X = (X / (X.norm(dim=(1, 2), keepdim=True) * 1.01)).bfloat16()
+        ref = _ns_unnormalised(X.float())
+        got = newtonschulz_gemm(X.clone()).float()      # the iteration ping-pongs between its input buffer and a scratch one
+        assert (got - ref).abs().max().item() < 0.05, (got - ref).abs().max().item()
