@@ -14,7 +14,8 @@
 
 namespace lyra {
 
-constexpr int FB_THREADS = 192;
+constexpr int FB_THREADS = 320;   // dQ kernel: TMA warp, MMA warp and two groups of four elementwise warps (two 32-key chunks of a tile each)
+constexpr int DKV_THREADS = 320;  // dK/dV kernel: the same roles, one 32-query chunk of a tile per group
 constexpr float B_LOG2E = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------------------------- delta
@@ -90,8 +91,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       mbar_init(smem_u32(&kv_empty[s]), 1);
     }
     mbar_init(smem_u32(&sdp_full), 1);
-    mbar_init(smem_u32(&sdp_empty), 128);
-    mbar_init(smem_u32(&ds_full), 128);
+    mbar_init(smem_u32(&sdp_empty), 256);
+    mbar_init(smem_u32(&ds_full), 256);
     mbar_init(smem_u32(&ds_empty), 1);
     mbar_init(smem_u32(&dq_full), 1);
     abort_flag = 0;
@@ -173,6 +174,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     }
   } else {
     const int quarter = warp & 3;
+    const int wg = (warp - 2) >> 2;                       // two groups of four warps share each tile's key columns
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const int qpos = p.q_start + q0 + row;
@@ -189,18 +191,26 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       const int hi = min(qpos, p.S - 1);
       const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = wg * (BKV / 64); c < (wg + 1) * (BKV / 64); ++c) {
         uint32_t rs[32], rp[32];
         tmem_ld32(tmem + lane_addr + S_COL + c * 32, rs);
         tmem_ld32(tmem + lane_addr + DP_COL + c * 32, rp);
         tmem_ld_wait();
         float ds[32];
+        const int kfirst = k0 + c * 32;
+        if (kfirst >= lo && kfirst + 31 <= hi) {           // whole chunk visible (all but the diagonal / band-edge tiles)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int kk = k0 + c * 32 + i;
-          const float z = __uint_as_float(rs[i]) * p.scale_log2;
-          const float pr = (kk > hi || kk < lo) ? 0.f : exp2f(z - lse2);
-          ds[i] = pr * (__uint_as_float(rp[i]) - delta);
+          for (int i = 0; i < 32; ++i) {
+            const float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+            ds[i] = pr * (__uint_as_float(rp[i]) - delta);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kk = kfirst + i;
+            const float pr = (kk > hi || kk < lo) ? 0.f : exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+            ds[i] = pr * (__uint_as_float(rp[i]) - delta);
+          }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
@@ -226,7 +236,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       tc_fence_after();
       __nv_bfloat16* orow = p.dq + (((long long)b * p.T + (q0 + row)) * p.Nq + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = wg; c < D / 32; c += 2) {
         uint32_t r[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem + lane_addr + DQ_COL + c * 32, r);
@@ -264,7 +274,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 
 // ---------------------------------------------------------------------------------------------- dK, dV
 template <int D>
-__global__ void __launch_bounds__(FB_THREADS, 1)
+__global__ void __launch_bounds__(DKV_THREADS, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                      const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const BwdParams p) {
   constexpr int BKV = 128, BQ = 64;
@@ -287,7 +297,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   uint8_t* sPT = sQD + 4 * QTILE;
   uint8_t* sDST = sPT + PT_BYTES;
   __shared__ uint64_t kv_full, qd_full[2], qd_empty[2], st_full[2], st_empty[2], stat_full[2], pt_full, pt_empty, acc_full;
-  __shared__ float s_lse2[2][BQ], s_delta[2][BQ];
+  __shared__ __align__(16) float s_lse2[2][BQ], s_delta[2][BQ];
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -309,10 +319,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
       mbar_init(smem_u32(&qd_full[s]), 1);
       mbar_init(smem_u32(&qd_empty[s]), 1);
       mbar_init(smem_u32(&st_full[s]), 1);
-      mbar_init(smem_u32(&st_empty[s]), 128);
-      mbar_init(smem_u32(&stat_full[s]), 128);
+      mbar_init(smem_u32(&st_empty[s]), 256);
+      mbar_init(smem_u32(&stat_full[s]), 256);
     }
-    mbar_init(smem_u32(&pt_full), 128);
+    mbar_init(smem_u32(&pt_full), 256);
     mbar_init(smem_u32(&pt_empty), 1);
     mbar_init(smem_u32(&acc_full), 1);
     abort_flag = 0;
@@ -407,44 +417,69 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   } else {
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                  // key row
-    const int tid = threadIdx.x - 64;                     // 0..127 among the softmax threads
+    const int tid = threadIdx.x - 64;                     // 0..255 among the elementwise threads
+    const int wg = tid >> 7;                              // group 0 takes query columns 0..31 of a tile, group 1 columns 32..63
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const int kk = k0 + row;
     const bool key_valid = kk < p.S;
     bool failed = false;
+    // per-query statistics (log-sum-exp, delta) of tile `it`, one value per thread of the first group; they are fetched one
+    // iteration ahead so that the global-load latency is off the per-iteration critical path
+    auto load_stat = [&](int it) -> float {
+      const int head = kvh * rep + it / tiles_per_head;
+      const int qi = (it_begin + it % tiles_per_head) * BQ + (tid & 63);
+      const long long idx = ((long long)b * p.Nq + head) * p.T + qi;
+      if (tid < 64) return qi < p.T ? p.lse[idx] * B_LOG2E : INFINITY;
+      if (tid < 128) return qi < p.T ? p.delta[idx] : 0.f;
+      return 0.f;
+    };
+    auto publish_stat = [&](int buf, float v) {
+      if (tid < 64) s_lse2[buf][tid] = v;
+      else if (tid < 128) s_delta[buf][tid - 64] = v;
+      mbar_arrive(smem_u32(&stat_full[buf]));
+    };
+    if (n_iter > 0) publish_stat(0, load_stat(0));
     for (int it = 0; it < n_iter; ++it) {
       const int s = it & 1;
       const uint32_t ph = (it >> 1) & 1;
-      const int head = kvh * rep + it / tiles_per_head;
       const int qi0 = (it_begin + it % tiles_per_head) * BQ;
-      // per-query statistics of this tile
-      {
-        const int qi = qi0 + (tid & 63);
-        const long long idx = ((long long)b * p.Nq + head) * p.T + qi;
-        if (tid < 64) s_lse2[s][tid] = qi < p.T ? p.lse[idx] * B_LOG2E : INFINITY;
-        else s_delta[s][tid - 64] = qi < p.T ? p.delta[idx] : 0.f;
-      }
-      mbar_arrive(smem_u32(&stat_full[s]));
+      const float next_stat = it + 1 < n_iter ? load_stat(it + 1) : 0.f;
       if (!mbar_wait(smem_u32(&stat_full[s]), ph, abortp)) { failed = true; break; }
       if (!mbar_wait(smem_u32(&st_full[s]), ph, abortp)) { failed = true; break; }
-      if (it > 0 && !mbar_wait(smem_u32(&pt_empty), (it - 1) & 1, abortp)) { failed = true; break; }
       tc_fence_after();
-#pragma unroll 1
-      for (int c = 0; c < BQ / 32; ++c) {
+      {
+        const int c = wg;                                 // BQ / 32 = 2 column chunks, one per group
         uint32_t rs[32], rp[32];
         tmem_ld32(tmem + lane_addr + ST_COL + s * BQ + c * 32, rs);
         tmem_ld32(tmem + lane_addr + DPT_COL + s * BQ + c * 32, rp);
         tmem_ld_wait();
         float pr[32], ds[32];
+        float lse_c[32], del_c[32];                         // this chunk's statistics, fetched 16 bytes at a time
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int qcol = c * 32 + i;
-          const int qpos = p.q_start + qi0 + qcol;
-          const bool vis = key_valid && kk <= qpos && (p.window == 0 || kk > qpos - p.window);
-          const float z = __uint_as_float(rs[i]) * p.scale_log2;
-          pr[i] = vis ? exp2f(z - s_lse2[s][qcol]) : 0.f;
-          ds[i] = pr[i] * (__uint_as_float(rp[i]) - s_delta[s][qcol]);
+        for (int i = 0; i < 8; ++i) {
+          const float4 a = reinterpret_cast<const float4*>(&s_lse2[s][c * 32])[i];
+          const float4 d = reinterpret_cast<const float4*>(&s_delta[s][c * 32])[i];
+          lse_c[4 * i] = a.x; lse_c[4 * i + 1] = a.y; lse_c[4 * i + 2] = a.z; lse_c[4 * i + 3] = a.w;
+          del_c[4 * i] = d.x; del_c[4 * i + 1] = d.y; del_c[4 * i + 2] = d.z; del_c[4 * i + 3] = d.w;
         }
+        const int qfirst = p.q_start + qi0 + c * 32;
+        if (key_valid && kk <= qfirst && (p.window == 0 || kk > qfirst + 31 - p.window)) {   // whole chunk visible
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            pr[i] = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse_c[i]));
+            ds[i] = pr[i] * (__uint_as_float(rp[i]) - del_c[i]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int qpos = qfirst + i;
+            const bool vis = key_valid && kk <= qpos && (p.window == 0 || kk > qpos - p.window);
+            pr[i] = vis ? exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse_c[i])) : 0.f;
+            ds[i] = pr[i] * (__uint_as_float(rp[i]) - del_c[i]);
+          }
+        }
+        // the previous tile's dV / dK products must have consumed P^T and dS^T before they are overwritten
+        if (it > 0 && !mbar_wait(smem_u32(&pt_empty), (it - 1) & 1, abortp)) failed = true;
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
           const int c16 = c * 4 + q;
@@ -461,10 +496,13 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
           *reinterpret_cast<uint4*>(sDST + swz128(row, c16)) = o;
         }
       }
+      if (failed) break;
       tc_fence_before();
       mbar_arrive(smem_u32(&st_empty[s]));
       fence_proxy_async_smem();
       mbar_arrive(smem_u32(&pt_full));
+      // everyone who passed this iteration's stat_full wait has finished iteration it - 1, the last reader of the other buffer
+      if (it + 1 < n_iter) publish_stat(s ^ 1, next_stat);
     }
     if (!failed && n_iter > 0 && !mbar_wait(smem_u32(&acc_full), 0, abortp)) failed = true;
     if (failed) {
@@ -473,8 +511,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     } else {
       tc_fence_after();
       const long long o_off = (((long long)b * p.S + kk) * p.Nkv + kvh) * D;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
+      {
+        const int which = wg;                             // group 0 writes dK, group 1 writes dV
         __nv_bfloat16* orow = (which == 0 ? p.dk : p.dv) + o_off;
         const float mul = which == 0 ? p.scale : 1.0f;
         const uint32_t col0 = which == 0 ? DK_COL : DV_COL;
@@ -542,7 +580,7 @@ static int launch_bwd(const void* q, const long long* qs, const void* k, const l
     once = true;
   }
   flash_bwd_dq_kernel<D><<<dim3((p.T + 127) / 128, p.Nq, p.B), FB_THREADS, smem_dq, s>>>(tq, tk, tv, tdo, p);
-  flash_bwd_dkv_kernel<D><<<dim3((p.S + 127) / 128, p.Nkv, p.B), FB_THREADS, smem_dkv, s>>>(tq64, tk, tv, tdo64, p);
+  flash_bwd_dkv_kernel<D><<<dim3((p.S + 127) / 128, p.Nkv, p.B), DKV_THREADS, smem_dkv, s>>>(tq64, tk, tv, tdo64, p);
   return 0;
 }
 

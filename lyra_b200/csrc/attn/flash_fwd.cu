@@ -187,16 +187,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         uint32_t r[32];
         tmem_ld32(s_addr + c * 32, r);
         tmem_ld_wait();
+        if (!need_mask) {   // interior tile: the maximum of the raw scores, scaled once below (the scale is positive)
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float z = __uint_as_float(r[i]) * p.scale_log2;
-          if (need_mask) {
+          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
             const int kk = k0 + c * 32 + i;
-            if (kk > hi || kk < lo) z = -INFINITY;
+            if (kk <= hi && kk >= lo) mx = fmaxf(mx, __uint_as_float(r[i]));
           }
-          mx = fmaxf(mx, z);
         }
       }
+      mx *= p.scale_log2;
       // lazy rescale: keep the old reference max unless the new one exceeds it by more than 2^8
       float factor = 1.0f;
       if (mx > m + 8.0f) {
@@ -229,15 +231,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         tmem_ld32(s_addr + c * 32, r);
         tmem_ld_wait();
         float pv[32];
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float z = __uint_as_float(r[i]) * p.scale_log2;
-          if (need_mask) {
-            const int kk = k0 + c * 32 + i;
-            if (kk > hi || kk < lo) z = -INFINITY;
+          for (int i = 0; i < 32; ++i) {
+            pv[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m));
+            sum += pv[i];
           }
-          pv[i] = exp2f(z - m);
-          sum += pv[i];
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int kk = k0 + c * 32 + i;
+            pv[i] = (kk > hi || kk < lo) ? 0.f : exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m));
+            sum += pv[i];
+          }
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
