@@ -40,10 +40,10 @@ __device__ __forceinline__ long long now_ns() {
   return t;
 }
 // Spins until *flag >= value or the time limit passes. Returns false on timeout.
-__device__ __forceinline__ bool wait_flag(const int* flag, int value) {
+__device__ __forceinline__ bool wait_flag(const int* flag, int value, long long limit_ns = PEER_WAIT_NS) {
   const long long start = now_ns();
   while (ld_acquire_sys(flag) < value) {
-    if (now_ns() - start > PEER_WAIT_NS) return false;
+    if (now_ns() - start > limit_ns) return false;
     __nanosleep(200);
   }
   return true;
@@ -109,9 +109,9 @@ __global__ void signal_kernel(PeerPtrs flag_arrays, int world, int my_rank, int 
   }
 }
 // Thread r waits until slot [r] of the local flag array reaches `value`.
-__global__ void wait_kernel(const int* __restrict__ flags, int world, int value, int* status) {
+__global__ void wait_kernel(const int* __restrict__ flags, int world, int value, int* status, long long limit_ns) {
   const int r = threadIdx.x;
-  if (r < world && !wait_flag(flags + r, value)) atomicExch(status, STATUS_PEER_TIMEOUT);
+  if (r < world && !wait_flag(flags + r, value, limit_ns)) atomicExch(status, STATUS_PEER_TIMEOUT);
 }
 
 // ------------------------------------------------------------------------------------------------ expert-parallel exchange
@@ -270,7 +270,18 @@ extern "C" int lyra_signal(const long long* flag_arrays, int world, int my_rank,
 }
 
 extern "C" int lyra_wait(const int* flags, int world, int value, int* status, void* stream) {
-  wait_kernel<<<1, 32, 0, ST(stream)>>>(flags, world, value, status);
+  wait_kernel<<<1, 32, 0, ST(stream)>>>(flags, world, value, status, PEER_WAIT_NS);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+// The same wait with a caller-chosen limit (clamped to the 2 s default): a peer that never raises its flag makes the kernel
+// give up after `limit_ms`, record the peer-timeout code in `status` and return, so the host can tell a dead peer from a
+// slow one and the CUDA context stays usable.
+extern "C" int lyra_wait_limit(const int* flags, int world, int value, int* status, int limit_ms, void* stream) {
+  long long ns = (long long)limit_ms * 1000000LL;
+  if (ns <= 0 || ns > PEER_WAIT_NS) ns = PEER_WAIT_NS;
+  wait_kernel<<<1, 32, 0, ST(stream)>>>(flags, world, value, status, ns);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

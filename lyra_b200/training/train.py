@@ -78,6 +78,8 @@ class TrainingConfig:
     numerics_every: int | None = None
     checkpoint_every: int = 1000
     checkpoint_keep: int = 2
+    peer_timeout_seconds: float = 600.0
+    """Multi-rank runs: how long a rank waits at a step boundary for the others' heartbeat before it gives up (an addition; the reference has no failure detection)."""
 
     sample_prompts: tuple[str, ...] = DEFAULT_SAMPLE_PROMPTS
     sample_tokens: int = 128
@@ -240,9 +242,22 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
         if tcfg.sample_every is not None:
             sample(start_step)
 
+    # With several ranks every step starts with a host-side roll call through the rendezvous store: a rank that died or left
+    # is noticed before the next kernels (which would wait for it) are launched.
+    heartbeat = None
+    if rt is not None and rt.world > 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+        from torch.distributed.distributed_c10d import _get_default_store
+
+        from lyra_b200.parallel.health import Heartbeat
+
+        heartbeat = Heartbeat(_get_default_store(), rt.rank, rt.world)
+
     run_start = time.perf_counter()
     try:
         for step in range(start_step + 1, tcfg.steps + 1):
+            if heartbeat is not None:
+                heartbeat.beat(step)
+                heartbeat.check(step, timeout=float(tcfg.peer_timeout_seconds))
             xs, ys = (np.stack(arrays) for arrays in zip(*(next(loader) for _ in range(acc))))
             xs, ys = local_rows(xs), local_rows(ys)
             if probe is not None and (step == 1 or due(tcfg.numerics_every, step)):
