@@ -3,6 +3,8 @@
     python bench/serve.py                                  # gpt-oss-20b, batch 64, 1024-token prompts, 128 new tokens
     python bench/serve.py --variant lyra-small --batch 8 --prompt 256 --new 64
     python bench/serve.py --layers 4 --new 8 --no-graph    # a small case (e.g. under a profiler)
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 bench/serve.py --variant gpt-oss-120b
+                                                           # experts sharded over the ranks, every rank serves its own batch
 
 Prints one JSON line: prefill tokens/s, decode tokens/s with the per-token launch sequence replayed from a CUDA graph and
 launched eagerly, and the decode step time against the time to read the active weights and the KV cache once at the
@@ -14,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from dataclasses import replace
 from pathlib import Path
@@ -57,27 +60,47 @@ def main() -> None:
     from lyra_b200.ops import native
     from lyra_b200.variants import model_variant
 
-    dev = torch.device("cuda")
+    world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
     mcfg = replace(model_variant(args.variant), param_dtype=torch.bfloat16, sample_temperature=0.0)
     if args.layers:
         mcfg = replace(mcfg, n_layers=args.layers, mlp_map=mcfg.mlp_map[: args.layers])
     if args.fp8:
         mcfg = replace(mcfg, quantize_mlp=True, quantize_cache=True, gemm_dtype=torch.float8_e4m3fn, quant_block=(64, 64))
-    model = ModelWeights.init(0, mcfg, device=dev)
+    rt = None
+    if world > 1:   # expert parallel: experts sharded over the ranks, attention replicated, one batch per rank
+        import torch.distributed as dist
+
+        from lyra_b200.parallel.runtime import Runtime
+
+        dist.init_process_group("nccl", device_id=dev)
+        rt = Runtime.create(world_size=world, rank=rank, device=dev, implementation="b200", mcfg=mcfg)
+        model = ModelWeights.init(0, mcfg, device=dev, shard_fn=rt.shard_info)
+        rt.register(model)
+        rt.finish_weight_pulls()
+        args.no_graph = True            # the exchange kernels take their epochs from the host: eager launches
+    else:
+        model = ModelWeights.init(0, mcfg, device=dev)
     if args.fp8:
         model = ModelWeights.quantize(model, mcfg)
     capacity = args.prompt + args.new
-    prompts = torch.randint(0, mcfg.vocab_size, (args.batch, args.prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(1))
+    prompts = torch.randint(0, mcfg.vocab_size, (args.batch, args.prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(1 + rank))
 
     results = {}
     for mode in (["eager"] if args.no_graph else ["graph", "eager"]):
-        gen = BatchedGenerator(model, mcfg, batch=args.batch, capacity=capacity, device=dev, use_cuda_graph=(mode == "graph"))
+        gen = BatchedGenerator(model, mcfg, batch=args.batch, capacity=capacity, device=dev, rt=rt, use_cuda_graph=(mode == "graph"))
         first = gen.prefill(prompts)                       # untimed round: one-time set-up, graph capture
         gen.decode(first, min(args.new, 4))
         t_pre, first = timed(lambda: gen.prefill(prompts))
         l0 = native.launches()
         t_dec, toks = timed(lambda: gen.decode(first, args.new))
         native.check_status()
+        if world > 1:   # the job's time is the slowest rank's
+            t = torch.tensor([t_pre, t_dec], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            t_pre, t_dec = float(t[0]), float(t[1])
         results[mode] = {"prefill_ms": t_pre, "decode_ms": t_dec, "tokens": toks, "launches_per_token": (native.launches() - l0) / max(1, args.new - 1)}
         del gen
         torch.cuda.empty_cache()
@@ -100,10 +123,10 @@ def main() -> None:
     bw, kind = hbm_gbs()
     step_ms = results[best]["decode_ms"] / steps
     line = {
-        "bench": "batched serve", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch": args.batch,
+        "bench": "batched serve", "n_gpus": world, "parallelism": f"ep{world} + data-parallel attention" if world > 1 else "single", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch": args.batch,
         "prompt_len": args.prompt, "new_tokens": args.new, "dtype": "bf16" + (" + e4m3 experts and KV" if args.fp8 else ""), "data": "synthetic tokens, random-init weights",
-        "prefill_tokens_per_s": round(args.batch * args.prompt / results[best]["prefill_ms"] * 1e3, 1),
-        "decode_tokens_per_s": round(args.batch * steps / results[best]["decode_ms"] * 1e3, 1),
+        "prefill_tokens_per_s": round(world * args.batch * args.prompt / results[best]["prefill_ms"] * 1e3, 1),
+        "decode_tokens_per_s": round(world * args.batch * steps / results[best]["decode_ms"] * 1e3, 1),
         "decode_ms_per_step": round(step_ms, 3),
         "decode_bytes_per_step_gb": round(step_bytes / 1e9, 3),
         f"decode_frac_of_{kind}_hbm": round(step_bytes / (step_ms * 1e-3) / 1e9 / bw, 3),
@@ -112,7 +135,10 @@ def main() -> None:
     if not args.no_graph:
         line["decode_tokens_per_s_eager"] = round(args.batch * steps / results["eager"]["decode_ms"] * 1e3, 1)
         line["graph_equals_eager"] = same
-    print(json.dumps(line), flush=True)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -212,6 +212,23 @@ __global__ void ep_return_kernel(const __nv_bfloat16* __restrict__ rows, const i
   for (int c = threadIdx.x; c < C / 8; c += blockDim.x) o[c] = s[c];
 }
 
+// dest[row] = meta[row] (source rank << 24 | slot) for real rows of the receive buffer, -1 for expert padding and unused rows:
+// the scatter map of the GEMM whose epilogue returns expert outputs straight into the source ranks' buffers.
+__global__ void ep_row_dest_kernel(const int* __restrict__ meta, const int* __restrict__ recv_offsets, const int* __restrict__ counts, int world,
+                                   int my_rank, int n_experts, int e_local, int cap_rows, int* __restrict__ dest) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= cap_rows) return;
+  int out = -1;
+  if (row < recv_offsets[e_local]) {
+    int j = 0;
+    while (j + 1 < e_local && row >= recv_offsets[j + 1]) ++j;
+    int valid = 0;
+    for (int s = 0; s < world; ++s) valid += counts[s * n_experts + my_rank * e_local + j];
+    if (row - recv_offsets[j] < valid) out = meta[row];
+  }
+  dest[row] = out;
+}
+
 // Zeroes the padding rows of the receive buffer (rows of an expert beyond its real count), so they contribute nothing to dW.
 __global__ void ep_zero_pad_kernel(__nv_bfloat16* __restrict__ rows, const int* __restrict__ recv_offsets, const int* __restrict__ counts, int world,
                                    int my_rank, int n_experts, int e_local, int C) {
@@ -318,6 +335,13 @@ extern "C" int lyra_ep_return(const void* rows, const int* meta, const int* recv
                               int e_local, const long long* ret_bufs, int cap_rows, int C, void* stream) {
   ep_return_kernel<<<cap_rows, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(rows), meta, recv_offsets, counts, world, my_rank,
                                                      n_experts, e_local, make_ptrs(ret_bufs, world), C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_row_dest(const int* meta, const int* recv_offsets, const int* counts, int world, int my_rank, int n_experts, int e_local,
+                                int cap_rows, int* dest, void* stream) {
+  ep_row_dest_kernel<<<(cap_rows + 255) / 256, 256, 0, ST(stream)>>>(meta, recv_offsets, counts, world, my_rank, n_experts, e_local, cap_rows, dest);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

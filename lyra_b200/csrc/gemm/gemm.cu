@@ -50,6 +50,10 @@ struct GemmParams {
   int num_groups;
   int n_split;              // SwiGLU: column where the linear half starts in B (= hidden size)
   float swiglu_beta, swiglu_limit;
+  // scattered output (expert-parallel return fused into the GEMM): row r of the result is stored to row (row_dest[r] & 0xFFFFFF)
+  // of the buffer peer_out[row_dest[r] >> 24] (another GPU's memory, plain 16-byte stores); rows with row_dest < 0 are dropped
+  const int* row_dest;
+  void* peer_out[AG_MAX_RANKS];
   int sym_tiles;            // tiles per matrix that are enumerated when sym_upper is set
   int sym_upper;            // 1: the result is symmetric (A A^T): tiles wholly below the diagonal are not enumerated; bf16 outputs are mirrored by
                             //    the epilogue of the upper tiles, fp32 outputs by `lyra_symmetrize`
@@ -362,6 +366,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const int row = t.m0 + row_in_tile;
       const bool row_ok = row < p.M;
       const long long c_off = (long long)t.gc * p.c_group_stride + (long long)row * p.ldc;
+      const int rdest = (p.row_dest && row < p.M) ? p.row_dest[row] : -1;   // scattered-output mode only
       const float* bias = p.bias ? p.bias + (long long)(p.group_mode == GROUP_M ? t.gb : t.gc) * p.bias_group_stride : nullptr;
 
       if (EPI == EPI_STORE) {
@@ -402,10 +407,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
               }
             } else {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
+              if (p.row_dest)
+                dst = rdest >= 0 ? reinterpret_cast<__nv_bfloat16*>(p.peer_out[rdest >> 24]) + (long long)(rdest & 0xFFFFFF) * p.ldc + col : nullptr;
               const __nv_bfloat16* src = p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + c_off + col : nullptr;
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                if (col + q * 8 < p.N) {
+                if (col + q * 8 < p.N && dst) {
                   if (src) {
                     const uint4 s4 = *reinterpret_cast<const uint4*>(src + q * 8);
                     const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&s4);
@@ -626,10 +633,12 @@ extern "C" int lyra_gemm_bf16(
     const float* bias, long long bias_group_stride,
     int group_mode, int num_groups, const int* tile_group, const int* group_offsets, int total_rows,
     int epilogue, int n_split, float swiglu_beta, float swiglu_limit, int sym_upper,
+    const int* row_dest, const long long* peer_out, int n_peers,
     int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8))) return -10;
   if (sym_upper && (M != N || epilogue != EPI_STORE || group_mode == GROUP_M || group_mode == GROUP_K)) return -14;
+  if (row_dest && (epilogue != EPI_STORE || out_fp32 || Cin || !peer_out || n_peers < 1 || n_peers > AG_MAX_RANKS || sym_upper)) return -15;
   const int G = num_groups > 0 ? num_groups : 1;
   constexpr int BN = 256;
 
@@ -639,12 +648,13 @@ extern "C" int lyra_gemm_bf16(
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = bias_group_stride;
   p.group_mode = group_mode; p.tile_group = tile_group; p.group_offsets = group_offsets; p.num_groups = G;
   p.n_split = n_split; p.swiglu_beta = swiglu_beta; p.swiglu_limit = swiglu_limit; p.status = status;
-  p.ag_world = 0; p.raster_n_major = 0; p.raster_group = 0; p.sym_upper = sym_upper; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
+  p.ag_world = 0; p.raster_n_major = 0; p.raster_group = 0; p.sym_upper = sym_upper; p.row_dest = row_dest; p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.m_tiles = (M + BM - 1) / BM;
   if (epilogue == EPI_SWIGLU) p.n_tiles = (n_split + BN / 2 - 1) / (BN / 2);
   else p.n_tiles = (N + BN - 1) / BN;
   p.total_tiles = p.m_tiles * p.n_tiles * ((group_mode == GROUP_K || group_mode == GROUP_BATCH) ? G : 1);
   p.raster_group = default_raster_group(p.n_tiles);
+  for (int r = 0; r < AG_MAX_RANKS; ++r) p.peer_out[r] = (row_dest && r < n_peers) ? reinterpret_cast<void*>(peer_out[r]) : nullptr;
   p.sym_tiles = 0;
   if (sym_upper) {
     for (int m = 0; m < p.m_tiles; ++m) p.sym_tiles += p.n_tiles - (p.n_tiles < m * BM / BN ? p.n_tiles : m * BM / BN);
@@ -739,7 +749,7 @@ extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long lo
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
   p.ag_world = 0;
-  p.raster_n_major = 1; p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0;
+  p.raster_n_major = 1; p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0; p.row_dest = nullptr;
   p.ce_y = y; p.ce_part_m = part_m; p.ce_part_l = part_l; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_gscale = gscale;
   p.m_tiles = (M + BM - 1) / BM;
   p.n_tiles = (vocab + BN - 1) / BN;
@@ -816,7 +826,7 @@ extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_lo
   p.alpha = alpha; p.beta = beta; p.bias = bias; p.bias_group_stride = 0;
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
-  p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0;
+  p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0; p.row_dest = nullptr;
   p.raster_n_major = 1;  // tiles walk M first, column panel by column panel: the order in which the panels of B arrive
   p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.ag_world = world; p.ag_rows_per_rank = rows_per_rank; p.ag_my_rank = my_rank; p.ag_row_bytes = ldw * 2;

@@ -23,11 +23,14 @@ TILE_M = 128
 
 def _raw(
     a, lda, a_gs, a_mn, b, ldb, b_gs, b_mn, c, c_in, ldc, c_gs, out_fp32, M, N, K, alpha, beta, bias, bias_gs,
-    group_mode, num_groups, tile_group, group_offsets, total_rows, epilogue, n_split, swiglu_beta, swiglu_limit, sym_upper=False,
+    group_mode, num_groups, tile_group, group_offsets, total_rows, epilogue, n_split, swiglu_beta, swiglu_limit, sym_upper=False, row_dest=None, peer_out=None,
 ):
+    import ctypes
+
     lib = native.kernels()
     fn = lib.lyra_gemm_bf16
     fn.restype = c_int
+    peers = (ctypes.c_longlong * len(peer_out))(*peer_out) if peer_out else None
     rc = fn(
         ptr(a), c_ll(lda), c_ll(a_gs), c_int(int(a_mn)),
         ptr(b), c_ll(ldb), c_ll(b_gs), c_int(int(b_mn)),
@@ -36,6 +39,7 @@ def _raw(
         ptr(bias), c_ll(bias_gs),
         c_int(group_mode), c_int(num_groups), ptr(tile_group), ptr(group_offsets), c_int(total_rows),
         c_int(epilogue), c_int(n_split), c_float(swiglu_beta), c_float(swiglu_limit), c_int(int(sym_upper)),
+        ptr(row_dest), peers, c_int(len(peer_out) if peer_out else 0),
         ptr(native.status_word()), native.stream_ptr(),
     )
     native.check(rc, "lyra_gemm_bf16")
@@ -126,8 +130,14 @@ def grouped_gemm(
     swiglu_beta: float = 1.702,
     swiglu_limit: float = 7.0,
     out: torch.Tensor | None = None,
-) -> torch.Tensor:
+    row_dest: torch.Tensor | None = None,
+    peer_out: list[int] | None = None,
+) -> torch.Tensor | None:
     """Ragged grouped GEMM over rows sorted by group and padded so every 128-row tile has one group.
+
+    With ``row_dest [R]`` (int32: ``rank << 24 | row``, negative = drop the row) and ``peer_out`` (one peer-mapped buffer
+    address per rank, rows of ``N`` bf16) the epilogue stores every result row straight into that rank's buffer over
+    NVLink instead of a local output: the return leg of the expert-parallel exchange fused into the product.
 
     ``x [R, K]``; ``tile_group [R/128]`` int32 (-1 marks unused tiles, whose output rows are left untouched);
     ``w [G, K, N]`` (forward, MN-major) or, with ``w_kmajor``, ``w [G, N, K]`` (data gradient of an ``[in, out]`` weight).
@@ -142,6 +152,12 @@ def grouped_gemm(
         Kw, N = w.shape[1], w.shape[2]
     assert Kw == K
     n_out = N // 2 if swiglu else N
+    if row_dest is not None:
+        assert not swiglu and peer_out and row_dest.dtype == torch.int32 and row_dest.numel() >= R
+        _raw(x, x.stride(0), 0, False, w, w.stride(1), w.stride(0), not w_kmajor, x, None, N, 0, False,
+             R, N, K, 1.0, 0.0, bias, (bias.stride(0) if bias is not None else 0), GROUP_M, G, tile_group, None, 0,
+             EPI_STORE, 0, swiglu_beta, swiglu_limit, row_dest=row_dest, peer_out=peer_out)
+        return None
     if out is None:
         out = torch.empty(R, n_out, dtype=torch.bfloat16, device=x.device)
     _raw(x, x.stride(0), 0, False, w, w.stride(1), w.stride(0), not w_kmajor, out, None, out.stride(0), 0, False,

@@ -23,6 +23,7 @@ from lyra_b200.ops import api as ops
 from lyra_b200.ops import reference as ref
 
 BF16 = torch.bfloat16
+FUSED_RETURN = os.environ.get("LYRA_EP_FUSED_RETURN", "1") != "0"   # expert outputs leave through the GEMM epilogue (peer stores), no return kernel
 CAPACITY = float(os.environ.get("LYRA_EP_CAPACITY", "4.0"))  # receive-buffer rows as a multiple of the balanced load (never above the world size)
 
 
@@ -30,7 +31,7 @@ def ep_moe_forward(rt, xn, scores, indices, w, c: ModelConfig):
     Kr = c.n_active_routed_experts
     r_scores, r_idx = scores[:, :Kr].contiguous(), indices[:, :Kr].contiguous()
     if rt.implementation == "b200" and xn.is_cuda:
-        out = _EPMoEKernel.apply(xn.contiguous(), r_scores.float(), r_idx, w.mlp_up, w.mlp_down, rt, c)
+        out = _EPMoEKernel.apply(xn.contiguous(), r_scores.float(), r_idx, w.mlp_up, w.mlp_down, w.mlp_up_bias, w.mlp_down_bias, rt, c)
     else:
         out = _ep_moe_collectives(rt, xn, r_scores, r_idx, w, c)
     for j in range(c.n_shared_experts):
@@ -197,6 +198,23 @@ class _Exchange:
         nat.count_launch(2)
         return recv
 
+    def build_row_dest(self, meta_slab) -> torch.Tensor:
+        """Scatter map of this exchange's receive buffer: ``rank << 24 | slot`` of the assignment each real row came from, -1
+        for padding (valid once the dispatch phase has completed; the return leg of forward and backward both use it)."""
+        nat = self.nat
+        self.row_dest = torch.empty(self.buf.cap, dtype=torch.int32, device=self.offsets.device)
+        meta = meta_slab.view(0, self.buf.cap, torch.int32)
+        nat.check(self.lib.lyra_ep_row_dest(nat.ptr(meta), nat.ptr(self.offsets), nat.ptr(self.counts_mat), self.W, self.rank, self.E, self.El,
+                                            self.buf.cap, nat.ptr(self.row_dest), nat.stream_ptr()), "ep_row_dest")
+        nat.count_launch()
+        return self.row_dest
+
+    def returned(self, ret_slab) -> torch.Tensor:
+        """After a product whose epilogue stored its rows into the source ranks' return buffers: wait until every rank's
+        stores have landed, then view this rank's buffer ``[F*K, C]``."""
+        self._phase(192)
+        return ret_slab.view(0, self.F * self.K * self.C, BF16).view(self.F * self.K, self.C)
+
     def collect(self, rows: torch.Tensor, meta_slab, ret_slab) -> torch.Tensor:
         nat = self.nat
         meta = meta_slab.view(0, self.buf.cap, torch.int32)
@@ -209,11 +227,13 @@ class _Exchange:
 
 class _EPMoEKernel(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, xn, scores, indices, w_up, w_down, rt, c):
+    def forward(ctx, xn, scores, indices, w_up, w_down, up_bias, down_bias, rt, c):
         from lyra_b200.ops import cuda_ops, elementwise as ew, gemm as G
 
         F_, K = indices.shape
         El, C, _, H = w_up.shape
+        ub = up_bias.detach().float().reshape(El, 2 * H) if up_bias is not None else None      # local experts' biases (GPT-OSS)
+        db = down_bias.detach().float().reshape(El, C) if down_bias is not None else None
         ex = _Exchange(rt, indices, C)
         bufs = ex.buf.for_layer(rt._layer)
         x_recv = ex.dispatch(xn, K, bufs["recv"], bufs["meta"])
@@ -221,14 +241,20 @@ class _EPMoEKernel(torch.autograd.Function):
         cap = ex.buf.cap
         # The receive buffer is sized for the worst case; only the 128-row tiles that belong to an expert are computed,
         # and only those rows are read afterwards, so the outputs need no zero fill.
-        act = G.grouped_gemm(x_recv, wu, ex.tile_group, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
+        act = G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
                              out=torch.empty(cap, H, dtype=BF16, device=xn.device))
-        down = G.grouped_gemm(act, wd, ex.tile_group, out=torch.empty(cap, C, dtype=BF16, device=xn.device))
-        ret = ex.collect(down, bufs["meta"], bufs["ret"])
+        if FUSED_RETURN:   # down-projection whose epilogue stores each row straight into its source rank's return buffer
+            ex.build_row_dest(bufs["meta"])
+            G.grouped_gemm(act, wd, ex.tile_group, bias=db, row_dest=ex.row_dest, peer_out=bufs["ret"].peer_ptrs)
+            ret = ex.returned(bufs["ret"])
+        else:
+            down = G.grouped_gemm(act, wd, ex.tile_group, bias=db, out=torch.empty(cap, C, dtype=BF16, device=xn.device))
+            ret = ex.collect(down, bufs["meta"], bufs["ret"])
         ident = torch.arange(F_ * K, device=xn.device)
         out = ew.combine_rows(ret, ident, scores, F_, K)
         ctx.save_for_backward(scores, w_up, w_down, ident)
         ctx.ex, ctx.bufs, ctx.cfg, ctx.rt = ex, bufs, (c.swiglu_beta, c.swiglu_limit), rt
+        ctx.biases = (up_bias, down_bias)
         return out
 
     @staticmethod
@@ -246,7 +272,9 @@ class _EPMoEKernel(torch.autograd.Function):
         d_down = ex.dispatch(d_ret, 1, ex.buf.scratch_recv[par], None)
         x_recv = bufs["recv"].view(0, cap * C, BF16).view(cap, C)
         wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
-        pre = G.grouped_gemm(x_recv, wu, ex.tile_group, out=torch.empty(cap, 2 * H, dtype=BF16, device=dev))
+        up_bias, down_bias = ctx.biases
+        ub = up_bias.detach().float().reshape(El, 2 * H) if up_bias is not None else None
+        pre = G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, out=torch.empty(cap, 2 * H, dtype=BF16, device=dev))
         act = ew.swiglu_fwd(pre, beta, limit, rows_dev=ex.total)
         gd = cuda_ops.GRAD_DTYPE
         if w_down.requires_grad:
@@ -263,7 +291,19 @@ class _EPMoEKernel(torch.autograd.Function):
                 w_up.grad = G.grouped_wgrad(x_recv, d_pre, ex.offsets, El).view(w_up.shape).to(gd)
             else:
                 G.grouped_wgrad(x_recv, d_pre, ex.offsets, El, out=w_up.grad.view(El, C, 2 * H), accumulate=True)
-        dx_recv = G.grouped_gemm(d_pre, wu, ex.tile_group, w_kmajor=True, out=torch.empty(cap, C, dtype=BF16, device=dev))
-        dx_a = ex.collect(dx_recv, bufs["meta"], ex.buf.scratch_ret[par])
+        if FUSED_RETURN:
+            G.grouped_gemm(d_pre, wu, ex.tile_group, w_kmajor=True, row_dest=ex.row_dest, peer_out=ex.buf.scratch_ret[par].peer_ptrs)
+            dx_a = ex.returned(ex.buf.scratch_ret[par])
+        else:
+            dx_recv = G.grouped_gemm(d_pre, wu, ex.tile_group, w_kmajor=True, out=torch.empty(cap, C, dtype=BF16, device=dev))
+            dx_a = ex.collect(dx_recv, bufs["meta"], ex.buf.scratch_ret[par])
         dxn = ew.gather_sum_rows(dx_a, ident, F_, K)
-        return dxn, dscores, None, None, None, None, None
+        if up_bias is not None or down_bias is not None:   # per-expert column sums over the rows of each local expert (no host sync)
+            gid = ex.tile_group.long().repeat_interleave(128)
+            dead = (gid < 0)[:, None]                       # rows of unused tiles hold uninitialised memory: mask, do not multiply
+            gid = gid.clamp(min=0)
+            if up_bias is not None and up_bias.requires_grad:
+                cuda_ops._add_grad(up_bias, torch.zeros(El, 2 * H, dtype=torch.float32, device=dev).index_add_(0, gid, d_pre.float().masked_fill(dead, 0.0)))
+            if down_bias is not None and down_bias.requires_grad:
+                cuda_ops._add_grad(down_bias, torch.zeros(El, C, dtype=torch.float32, device=dev).index_add_(0, gid, d_down.float().masked_fill(dead, 0.0)))
+        return dxn, dscores, None, None, None, None, None, None, None

@@ -219,6 +219,13 @@ class Runtime:
                 self._comm.weight_view(name).view(shape).copy_(self._master_of(name).detach())
         self._comm.gather_weights()
 
+    def finish_weight_pulls(self) -> None:
+        """Completes every compute copy now (pulls that would otherwise ride inside the first forward GEMM of each leaf);
+        for inference, where not every leaf's first use is a fused-pull GEMM."""
+        if self._comm is not None and getattr(self._comm, "p2p", False):
+            self._comm.finish_pending()
+            self._comm.barrier()
+
     # ------------------------------------------------------------------ hooks used by the model / stepper
     def begin_layer(self, idx: int) -> None:
         self._layer = idx
