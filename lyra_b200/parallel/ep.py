@@ -139,9 +139,11 @@ class _Exchange:
         self.rt, self.nat, self.lib = rt, native, native.kernels()
         F_, K = indices.shape
         key = (F_, K, C)
-        if rt._ep_state.get("key") != key:
-            rt._ep_state = {"key": key, "buf": EPBuffers(rt, F_, K, C)}
-        self.buf: EPBuffers = rt._ep_state["buf"]
+        sets = rt._ep_state.setdefault("sets", {})               # one buffer set per problem size (prefill and decode alternate)
+        if key not in sets:
+            sets[key] = EPBuffers(rt, F_, K, C)
+        rt._ep_state["key"], rt._ep_state["buf"] = key, sets[key]
+        self.buf: EPBuffers = sets[key]
         self.F, self.K, self.C = F_, K, C
         self.W, self.E, self.El, self.rank = rt.world, rt.mcfg.n_experts, rt.e_local, rt.rank
         comm = rt._comm
@@ -235,7 +237,9 @@ class _EPMoEKernel(torch.autograd.Function):
         ub = up_bias.detach().float().reshape(El, 2 * H) if up_bias is not None else None      # local experts' biases (GPT-OSS)
         db = down_bias.detach().float().reshape(El, C) if down_bias is not None else None
         ex = _Exchange(rt, indices, C)
-        bufs = ex.buf.for_layer(rt._layer)
+        # training keeps every layer's receive buffer for its backward pass; without gradients one set serves all layers
+        # (a layer's exchange completes, on every rank, before the next layer's dispatch can be signalled)
+        bufs = ex.buf.for_layer(rt._layer if any(ctx.needs_input_grad) else -1)
         x_recv = ex.dispatch(xn, K, bufs["recv"], bufs["meta"])
         wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
         cap = ex.buf.cap
