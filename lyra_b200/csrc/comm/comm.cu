@@ -114,6 +114,44 @@ __global__ void wait_kernel(const int* __restrict__ flags, int world, int value,
   if (r < world && !wait_flag(flags + r, value, limit_ns)) atomicExch(status, STATUS_PEER_TIMEOUT);
 }
 
+// Device-resident epochs. The host-valued versions above bake the epoch into the launch, which a replayed CUDA graph cannot
+// change; here the epoch lives in a counter in this GPU's memory: the signalling kernel increments it and raises the new
+// value on every peer, the waiting kernel reads it. Every rank runs the same sequence, so the counters agree.
+__global__ void signal_ctr_kernel(PeerPtrs flag_arrays, int world, int my_rank, int* ctr) {
+  __shared__ int v;
+  if (threadIdx.x == 0) {
+    v = *ctr + 1;
+    *ctr = v;
+  }
+  __syncthreads();
+  const int r = threadIdx.x;
+  if (r < world) {
+    __threadfence_system();
+    st_release_sys(reinterpret_cast<int*>(flag_arrays.p[r]) + my_rank, v);
+  }
+}
+__global__ void wait_ctr_kernel(const int* __restrict__ flags, int world, const int* __restrict__ ctr, int* status, long long limit_ns) {
+  const int r = threadIdx.x;
+  const int value = *ctr;
+  if (r < world && !wait_flag(flags + r, value, limit_ns)) atomicExch(status, STATUS_PEER_TIMEOUT);
+}
+// One block: this rank's per-expert counts into row [my_rank] of every rank's counts matrix, then its flag (epoch = ++*ctr).
+__global__ void ep_counts_push_ctr_kernel(const int* __restrict__ my_counts, PeerPtrs counts_mats, PeerPtrs flag_arrays, int world, int my_rank,
+                                          int n_experts, int* ctr) {
+  __shared__ int v;
+  if (threadIdx.x == 0) {
+    v = *ctr + 1;
+    *ctr = v;
+  }
+  for (int r = 0; r < world; ++r) {
+    int* dst = reinterpret_cast<int*>(counts_mats.p[r]) + (long long)my_rank * n_experts;
+    for (int e = threadIdx.x; e < n_experts; e += blockDim.x) dst[e] = my_counts[e];
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < world) st_release_sys(reinterpret_cast<int*>(flag_arrays.p[threadIdx.x]) + my_rank, v);
+}
+
 // ------------------------------------------------------------------------------------------------ expert-parallel exchange
 // Writes this rank's per-expert counts into row [my_rank] of every rank's counts matrix, then raises its flag there.
 __global__ void ep_counts_push_kernel(const int* __restrict__ my_counts, PeerPtrs counts_mats, PeerPtrs flag_arrays, int world, int my_rank,
@@ -288,6 +326,26 @@ extern "C" int lyra_signal(const long long* flag_arrays, int world, int my_rank,
 
 extern "C" int lyra_wait(const int* flags, int world, int value, int* status, void* stream) {
   wait_kernel<<<1, 32, 0, ST(stream)>>>(flags, world, value, status, PEER_WAIT_NS);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_signal_ctr(const long long* flag_arrays, int world, int my_rank, int* ctr, void* stream) {
+  signal_ctr_kernel<<<1, 32, 0, ST(stream)>>>(make_ptrs(flag_arrays, world), world, my_rank, ctr);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_wait_ctr(const int* flags, int world, const int* ctr, int* status, void* stream) {
+  wait_ctr_kernel<<<1, 32, 0, ST(stream)>>>(flags, world, ctr, status, PEER_WAIT_NS);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_counts_push_ctr(const int* my_counts, const long long* counts_mats, const long long* flag_arrays, int world, int my_rank,
+                                       int n_experts, int* ctr, void* stream) {
+  ep_counts_push_ctr_kernel<<<1, 128, 0, ST(stream)>>>(my_counts, make_ptrs(counts_mats, world), make_ptrs(flag_arrays, world), world, my_rank,
+                                                       n_experts, ctr);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

@@ -151,7 +151,7 @@ class BatchedGenerator:
 
     @torch.no_grad()
     def decode(self, first: torch.Tensor, n: int) -> torch.Tensor:
-        if self.use_cuda_graph and self.rt is None and self.decode_cfg.sample_temperature <= 0:
+        if self.use_cuda_graph and self.decode_cfg.sample_temperature <= 0 and (self.rt is None or getattr(self.rt, "implementation", "") == "b200"):
             return self._decode_graph(first, n)
         out = [first]
         tok = first
@@ -163,7 +163,7 @@ class BatchedGenerator:
     def _graph_step(self) -> None:
         """One greedy token from ``_static_tok`` at the device-resident position; advances both in place."""
         hidden, _, cache = model_apply(self._static_tok.reshape(self.batch, 1), self.model, self.cache, self.decode_cfg,
-                                       return_hidden_states=True, rt=None)
+                                       return_hidden_states=True, rt=self.rt)
         nxt = self._next_from_hidden(hidden[:, -1])
         self._static_tok.copy_(nxt)
         self.cache.pos_dev.add_(1)
@@ -172,7 +172,8 @@ class BatchedGenerator:
     def _decode_graph(self, first: torch.Tensor, n: int) -> torch.Tensor:
         """Greedy decode with the per-token launch sequence captured once in a CUDA graph and replayed: the position
         lives in device memory (cache writes, RoPE row, attention bounds read it there), so every replay is identical
-        on the host side and costs one launch instead of a few hundred."""
+        on the host side and costs one launch instead of a few hundred. With an expert-parallel runtime the exchange kernels
+        are part of the graph (their epochs are device counters), and every rank replays the same number of times."""
         start = self.cache.pos
         if start + n - 1 > self.capacity:
             raise ValueError(f"cache capacity {self.capacity} too small for {start} + {n - 1} positions")

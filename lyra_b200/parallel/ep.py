@@ -107,11 +107,26 @@ class EPBuffers:
         self.A = F_ * K
         dev = rt.device
         self.counts = [SymmetricSlab(W * E * 4, dev, name) for _ in range(2)]
-        self.scratch_recv = [SymmetricSlab(self.cap * C * 2, dev, name) for _ in range(2)]   # backward receive (parity)
-        self.scratch_ret = [SymmetricSlab(self.A * C * 2, dev, name) for _ in range(2)]      # backward return (parity)
+        self._scratch: dict[str, list] = {}                      # backward-pass buffers, created by the first backward
         self.layer: dict[int, dict] = {}
         self.calls = 0
         self.C, self.name = C, name
+
+    def _lazy(self, kind: str, nbytes: int) -> list:
+        from lyra_b200.parallel.comm import SymmetricSlab
+
+        if kind not in self._scratch:                            # same call order on every rank (symmetric allocation is collective)
+            self._scratch[kind] = [SymmetricSlab(nbytes, self.rt.device, self.name) for _ in range(2)]
+        return self._scratch[kind]
+
+    @property
+    def scratch_recv(self) -> list:
+        """Backward receive buffers (two, by call parity); inference never allocates them."""
+        return self._lazy("recv", self.cap * self.C * 2)
+
+    @property
+    def scratch_ret(self) -> list:
+        return self._lazy("ret", self.A * self.C * 2)
 
     def for_layer(self, idx: int) -> dict:
         from lyra_b200.parallel.comm import SymmetricSlab
@@ -162,11 +177,15 @@ class _Exchange:
         par = self.buf.calls & 1
         self.counts_slab = self.buf.counts[par]
         stream = native.stream_ptr()
-        rt._ep_epoch = getattr(rt, "_ep_epoch", 0) + 1
-        ep = rt._ep_epoch
-        native.check(self.lib.lyra_ep_counts_push(native.ptr(counts), _arr(self.counts_slab.peer_ptrs), _arr(self.flags.peers_at(64)), self.W,
-                                                  self.rank, self.E, ep, stream), "ep_counts_push")
-        native.check(self.lib.lyra_wait(ctypes.c_void_p(self.flags.buffer.data_ptr() + 64), self.W, ep, native.ptr(native.status_word()), stream), "wait")
+        # epochs live in device counters (index 0: counts exchange, 1: dispatch phase, 2: return phase), so the launch
+        # sequence is the same every time and can be replayed from a CUDA graph
+        if getattr(rt, "_ep_ctr", None) is None:
+            rt._ep_ctr = torch.zeros(4, dtype=torch.int32, device=dev)
+        self.ctr = rt._ep_ctr
+        native.check(self.lib.lyra_ep_counts_push_ctr(native.ptr(counts), _arr(self.counts_slab.peer_ptrs), _arr(self.flags.peers_at(64)), self.W,
+                                                      self.rank, self.E, ctypes.c_void_p(self.ctr.data_ptr()), stream), "ep_counts_push")
+        native.check(self.lib.lyra_wait_ctr(ctypes.c_void_p(self.flags.buffer.data_ptr() + 64), self.W, ctypes.c_void_p(self.ctr.data_ptr()),
+                                            native.ptr(native.status_word()), stream), "wait")
         self.counts_mat = self.counts_slab.view(0, self.W * self.E, torch.int32).clone()   # private copy: the slab is reused by later calls
         self.send_base = torch.empty(self.E, dtype=torch.int32, device=dev)
         self.offsets = torch.empty(self.El + 1, dtype=torch.int32, device=dev)
@@ -180,12 +199,10 @@ class _Exchange:
     def _phase(self, flag_offset: int) -> None:
         """Raises this rank's flag on all peers and waits for everyone's: all stores of the phase have landed."""
         nat = self.nat
-        self.rt._ep_phase = getattr(self.rt, "_ep_phase", {})
-        v = self.rt._ep_phase.get(flag_offset, 0) + 1
-        self.rt._ep_phase[flag_offset] = v
+        ctr = ctypes.c_void_p(self.ctr.data_ptr() + 4 * (1 if flag_offset == 128 else 2))
         stream = nat.stream_ptr()
-        nat.check(self.lib.lyra_signal(_arr(self.flags.peers_at(flag_offset)), self.W, self.rank, v, stream), "signal")
-        nat.check(self.lib.lyra_wait(ctypes.c_void_p(self.flags.buffer.data_ptr() + flag_offset), self.W, v, nat.ptr(nat.status_word()), stream), "wait")
+        nat.check(self.lib.lyra_signal_ctr(_arr(self.flags.peers_at(flag_offset)), self.W, self.rank, ctr, stream), "signal")
+        nat.check(self.lib.lyra_wait_ctr(ctypes.c_void_p(self.flags.buffer.data_ptr() + flag_offset), self.W, ctr, nat.ptr(nat.status_word()), stream), "wait")
         nat.count_launch(2)
 
     def dispatch(self, src: torch.Tensor, src_div: int, recv_slab, meta_slab) -> torch.Tensor:
