@@ -29,6 +29,7 @@ struct DGParams {
   const uint8_t* w;         // [G, K, N] bf16 or e4m3
   const float* wscale;      // [G, K / bk, N / bn]
   const int* offsets;       // [G + 1] row offsets, or null: one group holding all R rows
+  const int* counts;        // optional [G]: rows of group g are offsets[g] .. offsets[g] + counts[g] - 1 (padded layouts)
   float* part;              // [splits, R, N]
   int R, K, N, G, splits, k_per_split, bk, bn, zblocks;
 };
@@ -80,7 +81,8 @@ __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int n0 = blockIdx.x * TN, g = blockIdx.y;
   const int split = blockIdx.z % p.splits, zb = blockIdx.z / p.splits;
-  const int gbeg = p.offsets ? p.offsets[g] : 0, gend = p.offsets ? p.offsets[g + 1] : p.R;
+  const int gbeg = p.offsets ? p.offsets[g] : 0;
+  const int gend = p.offsets ? (p.counts ? gbeg + p.counts[g] : p.offsets[g + 1]) : p.R;
   const int r0 = gbeg + zb * MROWS;
   if (r0 >= gend) return;                                        // group without rows (or fewer than this block covers)
   const int cnt = min(MROWS, gend - r0);
@@ -241,10 +243,11 @@ int launch_tn(const DGParams& p, int tn, cudaStream_t stream) {
 }  // namespace
 
 // x [R, K] bf16 (rows sorted by group); w [G, K, N] bf16 (quant = 0) or e4m3 with wscale [G, K/bk, N/bn] (quant = 1);
-// offsets [G+1] int32 on the device (null: a single group); part: fp32 scratch [splits, R, N]; out bf16 [R, N] or, with
+// offsets [G+1] int32 on the device (null: a single group), counts [G] optional real row counts when the offsets are padded; part: fp32 scratch [splits, R, N]; out bf16 [R, N] or, with
 // swiglu, [R, N/2]. bias fp32 [G, N] or null. K and N must be multiples of 64, K / splits a multiple of 64.
 // `panel` = columns per CTA: 64, 128 or 192, a divisor of N (0: 128 if it divides N, else 64).
-extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscale, int quant, int bk, int bn, const int* offsets, const float* bias,
+extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscale, int quant, int bk, int bn, const int* offsets, const int* counts,
+                                const float* bias,
                                 float* part, void* out, int R, int K, int N, int G, int splits, int swiglu, float swiglu_beta, float swiglu_limit,
                                 int panel, cudaStream_t stream) {
   if (R <= 0) return 0;
@@ -258,6 +261,7 @@ extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscal
   p.w = static_cast<const uint8_t*>(w);
   p.wscale = wscale;
   p.offsets = offsets;
+  p.counts = offsets ? counts : nullptr;
   p.part = part;
   p.R = R;
   p.K = K;

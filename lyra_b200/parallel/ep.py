@@ -22,7 +22,10 @@ from lyra_b200.config import ModelConfig
 from lyra_b200.ops import api as ops
 from lyra_b200.ops import reference as ref
 
+from lyra_b200.nn.quant import QArray
+
 BF16 = torch.bfloat16
+EP_DECODE_MAX_ROWS = 512   # assignments per rank up to which an inference exchange uses the weight-streaming small-M products
 FUSED_RETURN = os.environ.get("LYRA_EP_FUSED_RETURN", "1") != "0"   # expert outputs leave through the GEMM epilogue (peer stores), no return kernel
 CAPACITY = float(os.environ.get("LYRA_EP_CAPACITY", "4.0"))  # receive-buffer rows as a multiple of the balanced load (never above the world size)
 
@@ -30,7 +33,10 @@ CAPACITY = float(os.environ.get("LYRA_EP_CAPACITY", "4.0"))  # receive-buffer ro
 def ep_moe_forward(rt, xn, scores, indices, w, c: ModelConfig):
     Kr = c.n_active_routed_experts
     r_scores, r_idx = scores[:, :Kr].contiguous(), indices[:, :Kr].contiguous()
-    if rt.implementation == "b200" and xn.is_cuda:
+    quantised = isinstance(w.mlp_up, QArray) or isinstance(w.mlp_down, QArray)
+    if rt.implementation == "b200" and xn.is_cuda and (quantised or (r_idx.numel() <= EP_DECODE_MAX_ROWS and not torch.is_grad_enabled())):
+        out = _ep_moe_decode(rt, xn.contiguous(), r_scores.float(), r_idx, w, c)
+    elif rt.implementation == "b200" and xn.is_cuda:
         out = _EPMoEKernel.apply(xn.contiguous(), r_scores.float(), r_idx, w.mlp_up, w.mlp_down, w.mlp_up_bias, w.mlp_down_bias, rt, c)
     else:
         out = _ep_moe_collectives(rt, xn, r_scores, r_idx, w, c)
@@ -41,6 +47,44 @@ def ep_moe_forward(rt, xn, scores, indices, w, c: ModelConfig):
         o = ops.linear(h, down, None, impl)
         out = out + o * scores[:, Kr + j, None].to(o.dtype)
     return out
+
+
+@torch.no_grad()
+def _ep_moe_decode(rt, xn, scores, indices, w, c: ModelConfig):
+    """Inference-only exchange for a handful of rows per expert: dispatch into the owners' receive buffers, the two expert
+    products with the small-M weight-streaming kernel (bf16 or block-scaled e4m3 weights, empty experts skipped), return,
+    weighted combine. Large row counts with quantised weights dequantise the local experts and use the tile GEMM."""
+    from lyra_b200.nn.quant import dequantize
+    from lyra_b200.ops import cuda_ops, decode as dec, elementwise as ew, gemm as G
+
+    F_, K = indices.shape
+    C = xn.shape[1]
+    up, down = w.mlp_up, w.mlp_down
+    El = (up.qval if isinstance(up, QArray) else up).shape[0]
+    wu = up if isinstance(up, QArray) else cuda_ops.bf16_weight(up).view(El, C, -1)
+    wd = down if isinstance(down, QArray) else cuda_ops.bf16_weight(down)
+    n_up = (wu.qval if isinstance(wu, QArray) else wu).shape[-1]
+    H = n_up // 2
+    ub = w.mlp_up_bias.detach().float().reshape(El, n_up) if w.mlp_up_bias is not None else None
+    db = w.mlp_down_bias.detach().float().reshape(El, C) if w.mlp_down_bias is not None else None
+    ex = _Exchange(rt, indices, C)
+    bufs = ex.buf.for_layer(-1)
+    x_recv = ex.dispatch(xn.to(BF16), K, bufs["recv"], bufs["meta"])
+    small = F_ * K <= EP_DECODE_MAX_ROWS and dec.decode_gemm_supported(C, n_up, wu) and dec.decode_gemm_supported(H, C, wd)
+    if small:
+        valid = ex.counts_mat.view(ex.W, ex.E)[:, ex.rank * El:(ex.rank + 1) * El].sum(0).to(torch.int32)
+        act = dec.decode_gemm(x_recv, wu, offsets=ex.offsets, counts=valid, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta,
+                              swiglu_limit=c.swiglu_limit, active_groups=El)
+        rows = dec.decode_gemm(act, wd, offsets=ex.offsets, counts=valid, bias=db, active_groups=El)
+    else:
+        wu_t = dequantize(wu, BF16) if isinstance(wu, QArray) else wu
+        wd_t = dequantize(wd, BF16) if isinstance(wd, QArray) else wd
+        cap = ex.buf.cap
+        act = G.grouped_gemm(x_recv, wu_t, ex.tile_group, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
+                             out=torch.empty(cap, H, dtype=BF16, device=xn.device))
+        rows = G.grouped_gemm(act, wd_t, ex.tile_group, bias=db, out=torch.empty(cap, C, dtype=BF16, device=xn.device))
+    ret = ex.collect(rows, bufs["meta"], bufs["ret"])
+    return ew.combine_rows(ret, torch.arange(F_ * K, device=xn.device), scores, F_, K)
 
 
 # ============================================================================================ baseline: collectives
