@@ -245,11 +245,12 @@ int launch_tn(const DGParams& p, int tn, cudaStream_t stream) {
 // x [R, K] bf16 (rows sorted by group); w [G, K, N] bf16 (quant = 0) or e4m3 with wscale [G, K/bk, N/bn] (quant = 1);
 // offsets [G+1] int32 on the device (null: a single group), counts [G] optional real row counts when the offsets are padded; part: fp32 scratch [splits, R, N]; out bf16 [R, N] or, with
 // swiglu, [R, N/2]. bias fp32 [G, N] or null. K and N must be multiples of 64, K / splits a multiple of 64.
+// `max_group_rows` = upper bound of the rows of one group (sizes grid.z; R when unknown).
 // `panel` = columns per CTA: 64, 128 or 192, a divisor of N (0: 128 if it divides N, else 64).
 extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscale, int quant, int bk, int bn, const int* offsets, const int* counts,
                                 const float* bias,
                                 float* part, void* out, int R, int K, int N, int G, int splits, int swiglu, float swiglu_beta, float swiglu_limit,
-                                int panel, cudaStream_t stream) {
+                                int panel, int max_group_rows, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (panel == 0) panel = N % 128 == 0 ? 128 : 64;
   if ((panel != 64 && panel != 128 && panel != 192) || N % panel) return -90;
@@ -271,7 +272,8 @@ extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscal
   p.k_per_split = K / splits;
   p.bk = bk;
   p.bn = bn;
-  p.zblocks = (R + MROWS - 1) / MROWS;
+  if (max_group_rows <= 0 || max_group_rows > R) max_group_rows = R;
+  p.zblocks = (max_group_rows + MROWS - 1) / MROWS;   // 64-row blocks that the largest possible group needs
   const int rc = quant ? launch_tn<true>(p, panel, stream) : launch_tn<false>(p, panel, stream);
   if (rc) return rc;
   decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,

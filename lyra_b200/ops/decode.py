@@ -99,11 +99,13 @@ def _gemm_splits(n_cols: int, panel: int, groups_with_rows: int, k_chunks: int) 
 
 def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, counts: torch.Tensor | None = None, bias: torch.Tensor | None = None,
                 swiglu: bool = False,
-                swiglu_beta: float = 1.702, swiglu_limit: float = 7.0, active_groups: int | None = None) -> torch.Tensor:
+                swiglu_beta: float = 1.702, swiglu_limit: float = 7.0, active_groups: int | None = None,
+                max_group_rows: int | None = None) -> torch.Tensor:
     """``x [R, K]`` (rows sorted by group) times ``w [G, K, N]`` (bf16 tensor, or QArray of e4m3 values with 2-D block
     scales) -> bf16 ``[R, N]`` (``[R, N/2]`` with SwiGLU). ``offsets [G+1]`` int32 row offsets on the device; ``None``
     means one group (a dense layer, ``w [K, N]`` or ``[1, K, N]``). ``counts [G]`` int32 gives the real rows per group when
-    ``offsets`` describe a padded layout (the expert-parallel receive buffer). Rows per group beyond 64 cost another pass over that
+    ``offsets`` describe a padded layout (the expert-parallel receive buffer); ``max_group_rows`` bounds the rows any group
+    can hold (default: all ``R``), which sizes the launch. Rows per group beyond 64 cost another pass over that
     group's weights, so this is the path for a few rows per expert."""
     lib = native.kernels()
     quant = isinstance(w, QArray)
@@ -127,7 +129,7 @@ def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, coun
     lib.lyra_decode_gemm.restype = c_int
     rc = lib.lyra_decode_gemm(ptr(x), ptr(wq), ptr(scale), c_int(int(quant)), c_int(bk), c_int(bn), ptr(offsets), ptr(counts), ptr(b), ptr(part), ptr(out),
                               c_int(R), c_int(K), c_int(N), c_int(G), c_int(splits), c_int(int(swiglu)), c_float(swiglu_beta),
-                              c_float(swiglu_limit), c_int(panel), native.stream_ptr())
+                              c_float(swiglu_limit), c_int(panel), c_int(min(R, max_group_rows) if max_group_rows else R), native.stream_ptr())
     native.check(rc, "lyra_decode_gemm")
     native.count_launch(2)
     return out

@@ -34,7 +34,7 @@ def ep_moe_forward(rt, xn, scores, indices, w, c: ModelConfig):
     Kr = c.n_active_routed_experts
     r_scores, r_idx = scores[:, :Kr].contiguous(), indices[:, :Kr].contiguous()
     quantised = isinstance(w.mlp_up, QArray) or isinstance(w.mlp_down, QArray)
-    if rt.implementation == "b200" and xn.is_cuda and (quantised or (r_idx.numel() <= EP_DECODE_MAX_ROWS and not torch.is_grad_enabled())):
+    if rt.implementation == "b200" and xn.is_cuda and quantised:   # bf16 experts: the tile GEMM path below is the faster one (measured, EP2)
         out = _ep_moe_decode(rt, xn.contiguous(), r_scores.float(), r_idx, w, c)
     elif rt.implementation == "b200" and xn.is_cuda:
         out = _EPMoEKernel.apply(xn.contiguous(), r_scores.float(), r_idx, w.mlp_up, w.mlp_down, w.mlp_up_bias, w.mlp_down_bias, rt, c)
@@ -73,9 +73,10 @@ def _ep_moe_decode(rt, xn, scores, indices, w, c: ModelConfig):
     small = F_ * K <= EP_DECODE_MAX_ROWS and dec.decode_gemm_supported(C, n_up, wu) and dec.decode_gemm_supported(H, C, wd)
     if small:
         valid = ex.counts_mat.view(ex.W, ex.E)[:, ex.rank * El:(ex.rank + 1) * El].sum(0).to(torch.int32)
+        most = ex.W * F_ * K                                     # an expert can receive at most every assignment of every rank
         act = dec.decode_gemm(x_recv, wu, offsets=ex.offsets, counts=valid, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta,
-                              swiglu_limit=c.swiglu_limit, active_groups=El)
-        rows = dec.decode_gemm(act, wd, offsets=ex.offsets, counts=valid, bias=db, active_groups=El)
+                              swiglu_limit=c.swiglu_limit, active_groups=El, max_group_rows=most)
+        rows = dec.decode_gemm(act, wd, offsets=ex.offsets, counts=valid, bias=db, active_groups=El, max_group_rows=most)
     else:
         wu_t = dequantize(wu, BF16) if isinstance(wu, QArray) else wu
         wd_t = dequantize(wd, BF16) if isinstance(wd, QArray) else wd
