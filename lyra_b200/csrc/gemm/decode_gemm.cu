@@ -189,8 +189,10 @@ __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) 
 }
 
 // out[r, c] = act(sum over splits of part[s, r, c] + bias[group(r), c]); with SwiGLU the N = 2H columns are gate | linear.
+// Without SwiGLU an optional residual is added after scaling: out = residual + alpha * (sum + bias).
 __global__ void decode_gemm_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias, const int* __restrict__ offsets,
-                                          __nv_bfloat16* __restrict__ out, int R, int N, int G, int splits, int swiglu, float beta, float limit) {
+                                          __nv_bfloat16* __restrict__ out, int R, int N, int G, int splits, int swiglu, float beta, float limit,
+                                          const __nv_bfloat16* __restrict__ residual, float alpha) {
   const int r = blockIdx.x;
   int g = 0;
   if (offsets && bias) {
@@ -213,6 +215,9 @@ __global__ void decode_gemm_finish_kernel(const float* __restrict__ part, const 
     if (swiglu) {
       const float gc = fminf(a, limit), lc = fminf(fmaxf(l, -limit), limit);
       a = (lc + 1.f) * gc / (1.f + __expf(-beta * gc));
+    } else {
+      a *= alpha;
+      if (residual) a += __bfloat162float(residual[static_cast<size_t>(r) * N + c]);
     }
     out[static_cast<size_t>(r) * H + c] = __float2bfloat16(a);
   }
@@ -244,13 +249,13 @@ int launch_tn(const DGParams& p, int tn, cudaStream_t stream) {
 
 // x [R, K] bf16 (rows sorted by group); w [G, K, N] bf16 (quant = 0) or e4m3 with wscale [G, K/bk, N/bn] (quant = 1);
 // offsets [G+1] int32 on the device (null: a single group), counts [G] optional real row counts when the offsets are padded; part: fp32 scratch [splits, R, N]; out bf16 [R, N] or, with
-// swiglu, [R, N/2]. bias fp32 [G, N] or null. K and N must be multiples of 64, K / splits a multiple of 64.
+// swiglu, [R, N/2]. bias fp32 [G, N] or null. Without swiglu: out = residual (bf16 [R, N], optional) + alpha * (x @ w + bias). K and N must be multiples of 64, K / splits a multiple of 64.
 // `max_group_rows` = upper bound of the rows of one group (sizes grid.z; R when unknown).
 // `panel` = columns per CTA: 64, 128 or 192, a divisor of N (0: 128 if it divides N, else 64).
 extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscale, int quant, int bk, int bn, const int* offsets, const int* counts,
                                 const float* bias,
                                 float* part, void* out, int R, int K, int N, int G, int splits, int swiglu, float swiglu_beta, float swiglu_limit,
-                                int panel, int max_group_rows, cudaStream_t stream) {
+                                int panel, int max_group_rows, const void* residual, float alpha, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (panel == 0) panel = N % 128 == 0 ? 128 : 64;
   if ((panel != 64 && panel != 128 && panel != 192) || N % panel) return -90;
@@ -276,7 +281,8 @@ extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscal
   p.zblocks = (max_group_rows + MROWS - 1) / MROWS;   // 64-row blocks that the largest possible group needs
   const int rc = quant ? launch_tn<true>(p, panel, stream) : launch_tn<false>(p, panel, stream);
   if (rc) return rc;
+  if (swiglu && (residual || alpha != 1.f)) return -90;
   decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,
-                                                   swiglu_limit);
+                                                   swiglu_limit, static_cast<const __nv_bfloat16*>(residual), alpha);
   return cudaGetLastError() == cudaSuccess ? 0 : -93;
 }

@@ -154,12 +154,15 @@ SMALL_M_ROWS = 64   # at most this many rows (and no autograd): the weight-strea
 def linear(x, w, bias=None, *, residual=None, alpha: float = 1.0, out_dtype=None):
     N = w.shape[1]
     rows = x.numel() // x.shape[-1]
-    if (rows <= SMALL_M_ROWS and residual is None and alpha == 1.0 and N % 64 == 0 and w.shape[0] % 64 == 0 and w.ndim == 2
-            and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad)) and (AG_HOOK is None or AG_HOOK(w) is None)):
+    if (rows <= SMALL_M_ROWS and N % 64 == 0 and w.shape[0] % 64 == 0 and w.ndim == 2
+            and not (torch.is_grad_enabled() and (x.requires_grad or w.requires_grad or (residual is not None and residual.requires_grad)))
+            and (AG_HOOK is None or AG_HOOK(w) is None)):
         from lyra_b200.ops import decode as dec
 
         x2 = x.reshape(rows, x.shape[-1]).to(BF16).contiguous()
-        y = dec.decode_gemm(x2, bf16_weight(w), bias=bias.reshape(1, N) if bias is not None else None).reshape(*x.shape[:-1], N)
+        res2 = residual.reshape(rows, N).to(BF16).contiguous() if residual is not None else None
+        y = dec.decode_gemm(x2, bf16_weight(w), bias=bias.reshape(1, N) if bias is not None else None, residual=res2,
+                            alpha=alpha).reshape(*x.shape[:-1], N)
     elif N % 8 or w.shape[0] % 8:
         y = ref_linear(x, w, bias, residual, alpha)
     else:

@@ -100,7 +100,7 @@ def _gemm_splits(n_cols: int, panel: int, groups_with_rows: int, k_chunks: int) 
 def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, counts: torch.Tensor | None = None, bias: torch.Tensor | None = None,
                 swiglu: bool = False,
                 swiglu_beta: float = 1.702, swiglu_limit: float = 7.0, active_groups: int | None = None,
-                max_group_rows: int | None = None) -> torch.Tensor:
+                max_group_rows: int | None = None, residual: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:
     """``x [R, K]`` (rows sorted by group) times ``w [G, K, N]`` (bf16 tensor, or QArray of e4m3 values with 2-D block
     scales) -> bf16 ``[R, N]`` (``[R, N/2]`` with SwiGLU). ``offsets [G+1]`` int32 row offsets on the device; ``None``
     means one group (a dense layer, ``w [K, N]`` or ``[1, K, N]``). ``counts [G]`` int32 gives the real rows per group when
@@ -126,10 +126,12 @@ def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, coun
     part = torch.empty(splits, R, N, dtype=torch.float32, device=x.device)
     out = torch.empty(R, N // 2 if swiglu else N, dtype=BF16, device=x.device)
     b = bias.detach().float().contiguous() if bias is not None else None
+    if residual is not None:
+        assert not swiglu and residual.dtype == BF16 and residual.shape == (R, N) and residual.is_contiguous()
     lib.lyra_decode_gemm.restype = c_int
     rc = lib.lyra_decode_gemm(ptr(x), ptr(wq), ptr(scale), c_int(int(quant)), c_int(bk), c_int(bn), ptr(offsets), ptr(counts), ptr(b), ptr(part), ptr(out),
                               c_int(R), c_int(K), c_int(N), c_int(G), c_int(splits), c_int(int(swiglu)), c_float(swiglu_beta),
-                              c_float(swiglu_limit), c_int(panel), c_int(min(R, max_group_rows) if max_group_rows else R), native.stream_ptr())
+                              c_float(swiglu_limit), c_int(panel), c_int(min(R, max_group_rows) if max_group_rows else R), ptr(residual), c_float(alpha), native.stream_ptr())
     native.check(rc, "lyra_decode_gemm")
     native.count_launch(2)
     return out

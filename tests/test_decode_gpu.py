@@ -151,6 +151,13 @@ def test_decode_gemm_dense_split_k():
     with torch.no_grad():
         y2 = cuda_ops.linear(x, w)               # small-M inference calls take the same kernel
     assert torch.equal(y, y2)
+    # residual and scale ride in the finishing pass: out = residual + alpha * (x @ w + bias)
+    res = torch.randn(5, 1024, device="cuda").bfloat16()
+    bias = torch.randn(1024, device="cuda")
+    with torch.no_grad():
+        y3 = cuda_ops.linear(x, w, bias, residual=res, alpha=0.25)
+    ref3 = res.float() + 0.25 * (ref + bias)
+    assert (y3.float() - ref3).abs().max().item() < 3e-2
 
 
 def test_decode_moe_matches_grouped_path():
