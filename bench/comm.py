@@ -3,7 +3,8 @@
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 bench/comm.py
 
 Each line: device time (CUDA events, max over ranks, median of 10 after 3 warm-ups, L2 flushed between runs) and the
-achieved fraction of  max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s)  for the fused kernels.
+achieved fraction of  max(FLOPs / measured bf16 peak, bytes over NVLink / 770 GB/s)  for the fused kernels: the all-gather
+(peer pull) fused GEMM and the expert-parallel return fused into the grouped GEMM epilogue (peer stores).
 """
 
 from __future__ import annotations
@@ -89,6 +90,59 @@ def main():
                               "peer_copy_gbs": round(nbytes / t_copy / 1e6, 1), "roofline_ms": round(roof_ms, 4),
                               "frac_of_roofline": round(roof_ms / t_fused, 3)}), flush=True)
         del slab
+    # ---- expert-parallel return leg fused into the grouped GEMM epilogue ------------------------------------------------
+    # Every rank holds R expert-sorted rows [R, H] (El local experts, R / El rows each) that came from all ranks in equal
+    # parts; the down-projection's result rows go back to slot `a` of their source rank's return buffer.
+    import ctypes
+
+    def arr(ptrs):
+        return (ctypes.c_longlong * len(ptrs))(*ptrs)
+
+    for (R, H, C, El) in [(32768, 2048, 4096, 4), (8192, 2048, 4096, 4), (32768, 2880, 2880, 16)]:
+        E = El * world
+        per_e = R // El
+        act = (torch.randn(R, H, device=dev) / 8).bfloat16()
+        w = (torch.randn(El, H, C, device=dev) / H ** 0.5).bfloat16()
+        tile_group = (torch.arange(R // 128, device=dev) // (per_e // 128)).to(torch.int32)
+        offsets = (torch.arange(El + 1, device=dev) * per_e).to(torch.int32)
+        counts = torch.full((world, E), per_e // world, dtype=torch.int32, device=dev)
+        # row r of expert j came from source rank (r_in_expert // (per_e / world)); slots are dense per source
+        r_in = torch.arange(R, device=dev) % per_e
+        src = (r_in // (per_e // world)).to(torch.int64)
+        slot = (torch.arange(R, device=dev) // per_e) * (per_e // world) + r_in % (per_e // world) + rank * (R // world)
+        meta = ((src << 24) | slot).to(torch.int32)
+        ret = SymmetricSlab(R * C * 2, dev, dist.group.WORLD.group_name)
+        row_dest = meta.clone()
+        out_local = torch.empty(R, C, dtype=torch.bfloat16, device=dev)
+
+        def fused():
+            G.grouped_gemm(act, w, tile_group, row_dest=row_dest, peer_out=ret.peer_ptrs)
+
+        def unfused():
+            G.grouped_gemm(act, w, tile_group, out=out_local)
+            native.check(lib.lyra_ep_return(native.ptr(out_local), native.ptr(meta), native.ptr(offsets), native.ptr(counts), world, rank, E, El,
+                                            arr(ret.peer_ptrs), R, C, native.stream_ptr()), "ep_return")
+
+        t_gemm = timed(lambda: G.grouped_gemm(act, w, tile_group, out=out_local))
+        t_unfused = timed(unfused)
+        t_fused = timed(fused)
+        torch.cuda.synchronize()
+        dist.barrier()
+        # correctness of the fused path against the unfused one (same buffer, same slots)
+        fused(); torch.cuda.synchronize(); dist.barrier()
+        a = ret.view(0, R * C, torch.bfloat16).clone()
+        dist.barrier()
+        unfused(); torch.cuda.synchronize(); dist.barrier()
+        same = bool(torch.equal(a, ret.view(0, R * C, torch.bfloat16)))
+        flops = 2.0 * R * H * C
+        nbytes = R * C * 2.0 * (world - 1) / world
+        roof_ms = max(flops / (peak * 1e12), nbytes / (NVLINK_GBS * 1e9)) * 1e3
+        if rank == 0:
+            print(json.dumps({"kernel": f"EP return fused into grouped GEMM R{R} H{H} C{C} experts/rank {El}", "world": world,
+                              "fused_ms": round(t_fused, 4), "gemm_only_ms": round(t_gemm, 4), "gemm_then_return_kernel_ms": round(t_unfused, 4),
+                              "roofline_ms": round(roof_ms, 4), "frac_of_roofline": round(roof_ms / t_fused, 3), "equals_unfused": same}), flush=True)
+        del ret
+    native.check_status()
     dist.destroy_process_group()
 
 

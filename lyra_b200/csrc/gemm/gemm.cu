@@ -27,6 +27,8 @@ constexpr int BK = 64;
 constexpr int GEMM_THREADS = 192;
 constexpr int MIRROR_LD = 136;           // row length (elements) of the 32 x 128 staging tile used to mirror symmetric results
 constexpr int MIRROR_BYTES = 32 * MIRROR_LD * 2;
+constexpr int SCATTER_LD = 72;           // row length (elements) of the 128 x 64 staging tile of the scattered (peer) store
+constexpr int EPI_STAGE_BYTES = 128 * SCATTER_LD * 2 + 128 * 4 + 512;   // staging tile + one destination per row (>= MIRROR_BYTES)
 constexpr int GEMM_THREADS_AG = 320;   // + four warps that pull the B operand from peer GPUs (all-gather fused GEMM)
 constexpr int AG_MAX_RANKS = 16;
 
@@ -369,7 +371,57 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       const int rdest = (p.row_dest && row < p.M) ? p.row_dest[row] : -1;   // scattered-output mode only
       const float* bias = p.bias ? p.bias + (long long)(p.group_mode == GROUP_M ? t.gb : t.gc) * p.bias_group_stride : nullptr;
 
-      if (EPI == EPI_STORE) {
+      if (EPI == EPI_STORE && p.row_dest) {
+        // Scattered store to other GPUs' buffers: 16-byte stores from one row per thread would cross NVLink as 32 separate
+        // small writes per instruction, so two 32-column chunks are staged in shared memory and written out as 128 contiguous
+        // bytes per row (eight lanes per row, four rows per store instruction).
+        __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * STAGE_BYTES);
+        int* sdest = reinterpret_cast<int*>(smem + STAGES * STAGE_BYTES + 128 * SCATTER_LD * 2);
+        sdest[row_in_tile] = rdest;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          if (have_acc) {
+            tmem_ld32(taddr + c * 32, r);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = 0u;
+          }
+          const int col = t.n0 + c * 32;
+          float v[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+          if (bias) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if (col + i < p.N) v[i] += bias[col + i];
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            o.x = pack_bf16(v[q * 8 + 0], v[q * 8 + 1]);
+            o.y = pack_bf16(v[q * 8 + 2], v[q * 8 + 3]);
+            o.z = pack_bf16(v[q * 8 + 4], v[q * 8 + 5]);
+            o.w = pack_bf16(v[q * 8 + 6], v[q * 8 + 7]);
+            *reinterpret_cast<uint4*>(stg + row_in_tile * SCATTER_LD + (c & 1) * 32 + q * 8) = o;
+          }
+          if (c & 1) {
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int col0 = t.n0 + (c - 1) * 32;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              const int piece = row_in_tile + 128 * k, rr = piece >> 3, part = piece & 7;
+              const int d = sdest[rr];
+              const int colp = col0 + part * 8;
+              if (d >= 0 && colp < p.N)
+                *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.peer_out[d >> 24]) + (long long)(d & 0xFFFFFF) * p.ldc + colp) =
+                    *reinterpret_cast<const uint4*>(stg + rr * SCATTER_LD + part * 8);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+          }
+        }
+      } else if (EPI == EPI_STORE) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -407,12 +459,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
               }
             } else {
               __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.C) + c_off + col;
-              if (p.row_dest)
-                dst = rdest >= 0 ? reinterpret_cast<__nv_bfloat16*>(p.peer_out[rdest >> 24]) + (long long)(rdest & 0xFFFFFF) * p.ldc + col : nullptr;
               const __nv_bfloat16* src = p.Cin ? reinterpret_cast<const __nv_bfloat16*>(p.Cin) + c_off + col : nullptr;
 #pragma unroll
               for (int q = 0; q < 4; ++q) {
-                if (col + q * 8 < p.N && dst) {
+                if (col + q * 8 < p.N) {
                   if (src) {
                     const uint4 s4 = *reinterpret_cast<const uint4*>(src + q * 8);
                     const __nv_bfloat162* sp = reinterpret_cast<const __nv_bfloat162*>(&s4);
@@ -582,7 +632,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 
 template <int BN>
 constexpr int gemm_smem_bytes() {
-  return ((BN == 256) ? 4 : 6) * (BM * BK * 2 + BN * BK * 2) + 1024 + MIRROR_BYTES;
+  return ((BN == 256) ? 4 : 6) * (BM * BK * 2 + BN * BK * 2) + 1024 + EPI_STAGE_BYTES;
 }
 
 template <int BN, bool A_MN, bool B_MN, int EPI>
