@@ -272,7 +272,16 @@ def _one_decode():
     return lambda: decode.decode_attention(q, k, v, sinks, D ** -0.5, 0, S - 1)
 
 
-ONE = {"gemm": _one_gemm, "flash_fwd": lambda: _one_attention(False), "flash_bwd": lambda: _one_attention(True),
+def _one_decode_gemm():
+    from lyra_b200.ops import decode
+    G_, K, N, rows = 32, 2880, 5760, 8
+    x = torch.randn(G_ * rows, K, device="cuda").bfloat16()
+    w = (torch.randn(G_, K, N, device="cuda") / K ** 0.5).bfloat16()
+    offsets = torch.arange(G_ + 1, device="cuda", dtype=torch.int32) * rows
+    return lambda: decode.decode_gemm(x, w, offsets=offsets)
+
+
+ONE = {"decode_gemm": _one_decode_gemm, "gemm": _one_gemm, "flash_fwd": lambda: _one_attention(False), "flash_bwd": lambda: _one_attention(True),
        "flash_fwd_window": lambda: _one_attention(False, 128), "ce": _one_ce, "rmsnorm": _one_rmsnorm, "moe_up": _one_moe, "decode": lambda: _one_decode()}
 
 
