@@ -146,7 +146,9 @@ def decode_gemm_supported(K: int, N: int, w) -> bool:
     return True
 
 
-DECODE_GEMM_MAX_ROWS = 512   # assignments (tokens x experts per token); above this the 128-row-tile tcgen05 grouped GEMM takes over
+import os as _os
+
+DECODE_GEMM_MAX_ROWS = int(_os.environ.get("LYRA_DECODE_GEMM_MAX_ROWS", "512"))   # assignments (tokens x experts per token); above this the 128-row-tile tcgen05 grouped GEMM takes over
 
 
 def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit):
