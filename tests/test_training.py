@@ -156,3 +156,40 @@ def test_interrupted_run_resumes_bit_exactly(tmp_path):
     assert (tmp_path / "run2" / "metrics.png").exists() and (tmp_path / "run2" / "config.json").exists()
     numerics = [json.loads(l) for l in (tmp_path / "run2" / "numerics.jsonl").read_text().splitlines()]
     assert any("load_max_ratio" in s for s in numerics[0]["records"].values())
+
+
+def test_tiny_moe_twenty_steps_checkpoint_at_twenty_and_resume(tmp_path):
+    """The plumbing configuration: the `tiny` variant (d_model 256, one sliding + one global layer, 4 query / 2 kv heads of
+    64, gated attention with sinks, 4 routed top-2 + 1 shared expert, hidden 512, full 201,088-token vocabulary), sequence
+    256, batch 2, iid-uniform tokens from torch seed 0, fp32 weights with bf16 compute, Muon + Adam; 20 steps, the
+    checkpoint of step 20, and a resumed run that continues from it."""
+    from lyra_b200.variants import model_variant
+
+    c = model_variant("tiny")
+    assert (c.n_embd, c.n_layers, c.n_attn_heads, c.n_kv_heads, c.head_dim, c.vocab_size) == (256, 2, 4, 2, 64, 201088)
+    assert c.param_dtype == torch.float32 and c.compute_dtype == torch.bfloat16
+    g = torch.Generator().manual_seed(0)
+    tokens = torch.randint(0, c.vocab_size, (64 * (c.seq_len + 1),), generator=g, dtype=torch.int32).numpy()
+    np.save(tmp_path / "tok.npy", tokens)
+    tcfg = TrainingConfig(steps=22, batch_size=2, accumulation_steps=1, data_path=tmp_path / "tok.npy", eval_data_path=tmp_path / "tok.npy",
+                          eval_every=None, checkpoint_every=20, checkpoint_path=tmp_path / "run", log_every=5,
+                          data_loader=DataLoaderConfig(worker_count=1))
+
+    class StopAfterTwenty(TrainHooks):
+        def before_step(self, step, *a):
+            if step == 21:
+                raise RuntimeError("stopped after the step-20 checkpoint")
+
+    with pytest.raises(RuntimeError, match="step-20 checkpoint"):
+        train(ModelWeights.init(0, c), c, tcfg, device="cpu", hooks=StopAfterTwenty())
+    assert [p.name for p in checkpoint_steps(tmp_path / "run")] == ["step_00000020"]
+    rows = [json.loads(l) for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
+    assert rows[-1]["step"] == 20 and all(np.isfinite(r["loss"]) for r in rows)
+    assert rows[-1]["loss"] < rows[0]["loss"]                     # 64 sequences seen many times: the loss moves down
+    at_twenty = load_train_state(tmp_path / "run", c, tcfg)
+    assert at_twenty.step == 20
+    resumed = train(None, c, replace(tcfg, resume_from=tmp_path / "run"), device="cpu")
+    a, b = tree_dict(at_twenty.state.params), tree_dict(resumed.params)
+    assert any(not torch.equal(a[k], b[k]) for k in a)            # two more optimizer steps were taken
+    rows = [json.loads(l) for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
+    assert [r["step"] for r in rows][-1] == 22 and np.isfinite(rows[-1]["loss"])
