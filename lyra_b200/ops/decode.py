@@ -166,11 +166,11 @@ def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limi
     wd = w_down if down_q else cuda_ops.bf16_weight(w_down)
     N_up = (wu.qval if up_q else wu).shape[-1]
     H = N_up // 2
-    # Measured on gpt-oss-20b shapes (batch 64): replayed from a CUDA graph, the tile GEMM on 128-row padded groups is the
-    # faster path for bf16 experts (15.9 vs 17.0 ms per step); launched eagerly the small-M kernel wins (fewer launches).
-    # Quantised experts always take the small-M kernel (it dequantises in flight).
-    capturing = xn.is_cuda and torch.cuda.is_current_stream_capturing()
-    small = F_ * K <= DECODE_GEMM_MAX_ROWS and (up_q or down_q or not capturing)
+    # Measured on gpt-oss-20b shapes (batch 64, CUDA-graph replay): for bf16 experts the tcgen05 tile GEMM on 128-row padded
+    # groups is faster than the small-M kernel (15.9 vs 17.0 ms per step), so bf16 experts take the tile path below;
+    # quantised experts take the small-M kernel, which dequantises in flight. LYRA_DECODE_MOE_SMALL_M=1 forces it for bf16 too.
+    force = _os.environ.get("LYRA_DECODE_MOE_SMALL_M", "0") == "1"
+    small = F_ * K <= DECODE_GEMM_MAX_ROWS and (up_q or down_q or force)
     if small and decode_gemm_supported(C, N_up, wu) and decode_gemm_supported(H, C, wd):
         flat = indices.reshape(-1)
         counts = ref.count_ids(flat, E)

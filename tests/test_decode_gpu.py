@@ -160,7 +160,7 @@ def test_decode_gemm_dense_split_k():
     assert (y3.float() - ref3).abs().max().item() < 3e-2
 
 
-def test_decode_moe_matches_grouped_path():
+def test_decode_moe_matches_grouped_path(monkeypatch):
     from lyra_b200.ops import cuda_ops, decode
 
     F_, K, E, C, H = 16, 4, 32, 256, 128
@@ -172,6 +172,7 @@ def test_decode_moe_matches_grouped_path():
     w_down = (torch.randn(E, H, C, device="cuda") / H ** 0.5).bfloat16()
     ub = torch.randn(E, 2, H, device="cuda") * 0.1
     db = torch.randn(E, C, device="cuda") * 0.1
+    monkeypatch.setenv("LYRA_DECODE_MOE_SMALL_M", "1")          # bf16 experts default to the tile GEMM; this test is about the small-M path
     with torch.no_grad():
         a = decode.decode_moe(xn, scores, indices, w_up, ub, w_down, db, 1.702, 7.0)
         b = cuda_ops.moe_experts(xn, scores, indices, w_up, ub, w_down, db, 1.702, 7.0)
@@ -200,3 +201,24 @@ def test_cuda_graph_decode_equals_eager(fp8_cache):
     assert torch.equal(want.long(), got)
     got2 = graph.decode(graph.prefill(prompts), N)     # second round replays the same graph from a fresh prefill
     assert torch.equal(got, got2)
+
+
+def test_decode_moe_quantised_experts_match_dequantised_weights():
+    """e4m3 experts go through the small-M kernel (dequantised in flight); same result as dequantise-then-grouped-GEMM."""
+    from lyra_b200.nn.quant import dequantize, quantize
+    from lyra_b200.ops import cuda_ops, decode
+
+    F_, K, E, C, H = 16, 4, 32, 256, 128
+    torch.manual_seed(12)
+    xn = torch.randn(F_, C, device="cuda").bfloat16()
+    scores = torch.rand(F_, K, device="cuda")
+    indices = torch.stack([torch.randperm(E, device="cuda")[:K] for _ in range(F_)])
+    w_up = torch.randn(E, C, 2 * H, device="cuda") / C ** 0.5
+    w_down = torch.randn(E, H, C, device="cuda") / H ** 0.5
+    up_q = quantize(w_up, torch.float8_e4m3fn, block=(64, 64))
+    down_q = quantize(w_down, torch.float8_e4m3fn, block=(64, 64))
+    with torch.no_grad():
+        a = decode.decode_moe(xn, scores, indices, up_q, None, down_q, None, 1.702, 7.0)
+        b = cuda_ops.moe_experts(xn, scores, indices, dequantize(up_q, torch.bfloat16).view(E, C, 2, H), None,
+                                 dequantize(down_q, torch.bfloat16), None, 1.702, 7.0)
+    assert (a.float() - b.float()).abs().max().item() < 3e-2
