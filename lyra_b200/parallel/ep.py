@@ -307,8 +307,15 @@ class _EPMoEKernel(torch.autograd.Function):
         cap = ex.buf.cap
         # The receive buffer is sized for the worst case; only the 128-row tiles that belong to an expert are computed,
         # and only those rows are read afterwards, so the outputs need no zero fill.
-        act = G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
-                             out=torch.empty(cap, H, dtype=BF16, device=xn.device))
+        pre = None
+        if cuda_ops.SAVE_PREACT and any(ctx.needs_input_grad):
+            # memory to spare (several ranks): keep the pre-activations so that backward skips the up-projection recompute,
+            # the largest GEMM of the layer on the rank with the most rows
+            pre = G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, out=torch.empty(cap, 2 * H, dtype=BF16, device=xn.device))
+            act = ew.swiglu_fwd(pre, c.swiglu_beta, c.swiglu_limit, rows_dev=ex.total)
+        else:
+            act = G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta, swiglu_limit=c.swiglu_limit,
+                                 out=torch.empty(cap, H, dtype=BF16, device=xn.device))
         if FUSED_RETURN:   # down-projection whose epilogue stores each row straight into its source rank's return buffer
             ex.build_row_dest(bufs["meta"])
             G.grouped_gemm(act, wd, ex.tile_group, bias=db, row_dest=ex.row_dest, peer_out=bufs["ret"].peer_ptrs)
@@ -321,6 +328,7 @@ class _EPMoEKernel(torch.autograd.Function):
         ctx.save_for_backward(scores, w_up, w_down, ident)
         ctx.ex, ctx.bufs, ctx.cfg, ctx.rt = ex, bufs, (c.swiglu_beta, c.swiglu_limit), rt
         ctx.biases = (up_bias, down_bias)
+        ctx.pre = pre
         return out
 
     @staticmethod
@@ -340,7 +348,8 @@ class _EPMoEKernel(torch.autograd.Function):
         wu, wd = cuda_ops.bf16_weight(w_up).view(El, C, 2 * H), cuda_ops.bf16_weight(w_down)
         up_bias, down_bias = ctx.biases
         ub = up_bias.detach().float().reshape(El, 2 * H) if up_bias is not None else None
-        pre = G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, out=torch.empty(cap, 2 * H, dtype=BF16, device=dev))
+        pre = ctx.pre if ctx.pre is not None else G.grouped_gemm(x_recv, wu, ex.tile_group, bias=ub, out=torch.empty(cap, 2 * H, dtype=BF16, device=dev))
+        ctx.pre = None
         act = ew.swiglu_fwd(pre, beta, limit, rows_dev=ex.total)
         gd = cuda_ops.GRAD_DTYPE
         if w_down.requires_grad:
