@@ -374,12 +374,19 @@ class _MoEExperts(torch.autograd.Function):
         wd = bf16_weight(w_down)
         ub = up_bias.detach().float().reshape(E, 2 * H) if up_bias is not None else None
         db = down_bias.detach().float().reshape(E, C) if down_bias is not None else None
-        act = G.grouped_gemm(x_perm, wu, tile_group, bias=ub, swiglu=True, swiglu_beta=beta, swiglu_limit=limit,
-                             out=torch.zeros(R, H, dtype=BF16, device=xn.device))
+        pre = None
+        if SAVE_PREACT and (xn.requires_grad or w_up.requires_grad):
+            # memory to spare: keep the pre-activations (and the permuted rows) so that backward skips the up-projection recompute
+            pre = G.grouped_gemm(x_perm, wu, tile_group, bias=ub, out=torch.zeros(R, 2 * H, dtype=BF16, device=xn.device))
+            act = ew.swiglu_fwd(pre, beta, limit)
+        else:
+            act = G.grouped_gemm(x_perm, wu, tile_group, bias=ub, swiglu=True, swiglu_beta=beta, swiglu_limit=limit,
+                                 out=torch.zeros(R, H, dtype=BF16, device=xn.device))
         down = G.grouped_gemm(act, wd, tile_group, bias=db, out=torch.zeros(R, C, dtype=BF16, device=xn.device))
         out = ew.combine_rows(down, dest, scores, F_, K)
         ctx.save_for_backward(xn, scores, dest, tile_group, offsets, w_up, w_down, down)
         ctx.cfg = (beta, limit, R, up_bias, down_bias)
+        ctx.kept = (x_perm, pre) if pre is not None else None
         return out
 
     @staticmethod
@@ -395,8 +402,12 @@ class _MoEExperts(torch.autograd.Function):
         # d(down rows) = score * dout[token]; dscore = <down row, dout[token]>
         d_down, dscores = ew.combine_rows_bwd(down, dout, dest, scores, R)
         del down
-        x_perm = ew.scatter_rows(xn, dest, K, R)
-        pre = G.grouped_gemm(x_perm, wu, tile_group, bias=ub, out=torch.zeros(R, 2 * H, dtype=BF16, device=xn.device))
+        if ctx.kept is not None:
+            x_perm, pre = ctx.kept
+            ctx.kept = None
+        else:
+            x_perm = ew.scatter_rows(xn, dest, K, R)
+            pre = G.grouped_gemm(x_perm, wu, tile_group, bias=ub, out=torch.zeros(R, 2 * H, dtype=BF16, device=xn.device))
         act = ew.swiglu_fwd(pre, beta, limit)
         if w_down.requires_grad:
             if w_down.grad is None:
