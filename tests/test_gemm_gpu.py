@@ -152,3 +152,31 @@ def test_newton_schulz_gemm_matches_torch():
         ref = _ns_unnormalised(X.float())
         got = newtonschulz_gemm(X.clone()).float()      # the iteration ping-pongs between its input buffer and a scratch one
         assert (got - ref).abs().max().item() < 0.05, (got - ref).abs().max().item()
+
+
+@pytest.mark.parametrize("N", [512, 2880])
+def test_grouped_gemm_scattered_epilogue(N):
+    """The epilogue that stores result rows to per-row destinations (the expert-parallel return leg) on one GPU: the
+    "peer" buffer is a local tensor, the row map a permutation with some rows dropped."""
+    from lyra_b200.ops import gemm as G, native
+
+    torch.manual_seed(3)
+    R, K, E = 1024, 256, 4
+    x = torch.randn(R, K, device="cuda").bfloat16()
+    w = (torch.randn(E, K, N, device="cuda") / K ** 0.5).bfloat16()
+    bias = torch.randn(E, N, device="cuda")
+    tile_group = torch.tensor([0, 0, 1, 2, 2, 2, 3, -1], dtype=torch.int32, device="cuda")
+    ref = G.grouped_gemm(x, w, tile_group, bias=bias, out=torch.zeros(R, N, dtype=torch.bfloat16, device="cuda"))
+    perm = torch.randperm(R, device="cuda")
+    row_dest = perm.to(torch.int32).clone()                 # rank 0 << 24 | slot
+    dropped = torch.arange(R, device="cuda") % 7 == 3
+    row_dest[dropped] = -1
+    out = torch.full((R, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    G.grouped_gemm(x, w, tile_group, bias=bias, row_dest=row_dest, peer_out=[out.data_ptr()])
+    torch.cuda.synchronize()
+    native.check_status()
+    live = (~dropped) & (torch.arange(R, device="cuda") < 7 * 128)       # the last tile belongs to no expert: nothing is stored
+    assert torch.equal(out[perm[live]], ref[live])
+    untouched = torch.ones(R, dtype=torch.bool, device="cuda")
+    untouched[perm[live]] = False
+    assert (out[untouched] == 7.0).all()
