@@ -78,6 +78,44 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_fwd_kernel(const __nv_bflo
   }
 }
 
+// One warp per row for C = NV * 256 (NV 16-byte vectors per lane): no block-wide barrier, NV independent 16-byte loads in
+// flight per lane. The block-per-row kernel above pays two __syncthreads per row and holds one vector per thread at C = 2048.
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_fwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                                                               __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int rows, float eps) {
+  constexpr int C = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, nwarps = (gridDim.x * blockDim.x) >> 5;
+  for (int row = warp; row < rows; row += nwarps) {
+    const BF8* xr = reinterpret_cast<const BF8*>(x + (long long)row * C);
+    BF8 raw[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) raw[j] = xr[lane + 32 * j];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float v[8];
+      unpack8(raw[j], v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+    const float rstd = rsqrtf(ss / C + eps);
+    if (lane == 0 && rstd_out) rstd_out[row] = rstd;
+    BF8* yr = reinterpret_cast<BF8*>(y + (long long)row * C);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float v[8], o[8];
+      unpack8(raw[j], v);
+      const float4 s0 = reinterpret_cast<const float4*>(scale)[(lane + 32 * j) * 2], s1 = reinterpret_cast<const float4*>(scale)[(lane + 32 * j) * 2 + 1];
+      o[0] = v[0] * rstd * s0.x; o[1] = v[1] * rstd * s0.y; o[2] = v[2] * rstd * s0.z; o[3] = v[3] * rstd * s0.w;
+      o[4] = v[4] * rstd * s1.x; o[5] = v[5] * rstd * s1.y; o[6] = v[6] * rstd * s1.z; o[7] = v[7] * rstd * s1.w;
+      yr[lane + 32 * j] = pack8(o);
+    }
+  }
+}
+
 // dx = (g - xhat * mean(g * xhat)) * rstd with g = dy * scale; dscale partial per block = sum_rows dy * xhat
 __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
                                                                  const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
@@ -131,6 +169,68 @@ __global__ void __launch_bounds__(RN_THREADS) rmsnorm_bwd_kernel(const __nv_bflo
 #pragma unroll
       for (int i = 0; i < 8; ++i) partial[(long long)blockIdx.x * C + c * 8 + i] = ds[j][i];
     }
+  }
+}
+
+// Warp-per-row backward for C = NV * 256 <= 2048: x and dy stay packed in registers between the two passes, every warp keeps
+// its own dscale partial (row `warp` of `partial`, which therefore has one row per warp of the launch).
+template <int NV>
+__global__ void __launch_bounds__(256) rmsnorm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale,
+                                                               const float* __restrict__ rstd_in, const __nv_bfloat16* __restrict__ dy,
+                                                               __nv_bfloat16* __restrict__ dx, float* __restrict__ partial, int rows, int nwarps) {
+  constexpr int C = NV * 256;
+  const int lane = threadIdx.x & 31;
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (warp >= nwarps) return;
+  float ds[NV][8];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int i = 0; i < 8; ++i) ds[j][i] = 0.f;
+  for (int row = warp; row < rows; row += nwarps) {
+    const BF8* xr = reinterpret_cast<const BF8*>(x + (long long)row * C);
+    const BF8* gr = reinterpret_cast<const BF8*>(dy + (long long)row * C);
+    BF8 xraw[NV], graw[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      xraw[j] = xr[lane + 32 * j];
+      graw[j] = gr[lane + 32 * j];
+    }
+    const float rstd = rstd_in[row];
+    float dot = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float xv[8], dv[8];
+      unpack8(xraw[j], xv);
+      unpack8(graw[j], dv);
+      const float* sc = scale + (lane + 32 * j) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float xh = xv[i] * rstd;
+        ds[j][i] += dv[i] * xh;
+        dot += dv[i] * sc[i] * xh;
+      }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+    const float mean = dot / C;
+    BF8* dr = reinterpret_cast<BF8*>(dx + (long long)row * C);
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      float xv[8], dv[8], o[8];
+      unpack8(xraw[j], xv);
+      unpack8(graw[j], dv);
+      const float* sc = scale + (lane + 32 * j) * 8;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] = (dv[i] * sc[i] - xv[i] * rstd * mean) * rstd;
+      dr[lane + 32 * j] = pack8(o);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    float* out = partial + (long long)warp * C + (lane + 32 * j) * 8;
+    reinterpret_cast<float4*>(out)[0] = make_float4(ds[j][0], ds[j][1], ds[j][2], ds[j][3]);
+    reinterpret_cast<float4*>(out)[1] = make_float4(ds[j][4], ds[j][5], ds[j][6], ds[j][7]);
   }
 }
 
@@ -324,6 +424,20 @@ using namespace lyra;
 extern "C" int lyra_rmsnorm_fwd(const void* x, const float* scale, void* y, float* rstd, int rows, int C, float eps, void* stream) {
   if (rows <= 0) return 0;
   if (C % 8 || C > 8 * RN_THREADS * RN_MAXV) return -40;
+  if (C % 256 == 0 && C <= 4096 && (reinterpret_cast<uintptr_t>(scale) & 15) == 0) {   // warp-per-row kernels
+    const int blocks = (rows + 7) / 8 < sm_count() * 8 ? (rows + 7) / 8 : sm_count() * 8;
+    switch (C / 256) {
+      case 1: rmsnorm_fwd_warp_kernel<1><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, eps); break;
+      case 2: rmsnorm_fwd_warp_kernel<2><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, eps); break;
+      case 4: rmsnorm_fwd_warp_kernel<4><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, eps); break;
+      case 8: rmsnorm_fwd_warp_kernel<8><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, eps); break;
+      case 16: rmsnorm_fwd_warp_kernel<16><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, eps); break;
+      default: goto block_kernel;
+    }
+    LYRA_CHECK_LAUNCH();
+    return 0;
+  }
+block_kernel:
   const int grid = rows < sm_count() * 8 ? rows : sm_count() * 8;
   rmsnorm_fwd_kernel<<<grid, RN_THREADS, 0, S_(stream)>>>(CBFP(x), scale, BFP(y), rstd, rows, C, eps);
   LYRA_CHECK_LAUNCH();
@@ -334,6 +448,19 @@ extern "C" int lyra_rmsnorm_bwd(const void* x, const float* scale, const float* 
                                 int nblk, void* stream) {
   if (rows <= 0) return 0;
   if (C % 8 || C > 8 * RN_THREADS * RN_MAXV) return -40;
+  if (C % 256 == 0 && C <= 2048) {   // warp-per-row kernel: `nblk` rows of `partial` = `nblk` warps
+    const int blocks = (nblk + 7) / 8;
+    switch (C / 256) {
+      case 1: rmsnorm_bwd_warp_kernel<1><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, rstd, CBFP(dy), BFP(dx), partial, rows, nblk); break;
+      case 2: rmsnorm_bwd_warp_kernel<2><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, rstd, CBFP(dy), BFP(dx), partial, rows, nblk); break;
+      case 4: rmsnorm_bwd_warp_kernel<4><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, rstd, CBFP(dy), BFP(dx), partial, rows, nblk); break;
+      case 8: rmsnorm_bwd_warp_kernel<8><<<blocks, 256, 0, S_(stream)>>>(CBFP(x), scale, rstd, CBFP(dy), BFP(dx), partial, rows, nblk); break;
+      default: goto block_kernel;
+    }
+    LYRA_CHECK_LAUNCH();
+    return 0;
+  }
+block_kernel:
   rmsnorm_bwd_kernel<<<nblk, RN_THREADS, 0, S_(stream)>>>(CBFP(x), scale, rstd, CBFP(dy), BFP(dx), partial, rows, C);
   LYRA_CHECK_LAUNCH();
   return 0;

@@ -52,7 +52,9 @@ class RMSNorm(torch.autograd.Function):
             dy2 = dy2.contiguous()
             dx = torch.empty_like(x2)
             rows = x2.shape[0]
-            nblk = min(1024, max(1, (rows + 31) // 32))
+            # rows of the partial-sum buffer: one per block of the block-per-row kernel, one per warp of the warp-per-row
+            # kernel that serves C % 256 == 0, C <= 2048 (148 SMs x 8 warps)
+            nblk = min(1184, max(1, rows // 4)) if (C % 256 == 0 and C <= 2048) else min(1024, max(1, (rows + 31) // 32))
             partial = torch.empty(nblk, C, dtype=torch.float32, device=x2.device)
             sc = scale.detach().float().contiguous()
             native.check(_lib().lyra_rmsnorm_bwd(ptr(x2), ptr(sc), ptr(rstd), ptr(dy2), ptr(dx), ptr(partial), c_int(rows), c_int(C),
