@@ -15,7 +15,7 @@
 
 namespace lyra {
 
-constexpr int FA_THREADS = 192;
+constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, two groups of four softmax warps (64 of a tile's 128 key columns each)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -48,6 +48,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   uint8_t* sV = sK + 2 * TILE;       // 2 stages
   uint8_t* sP = sV + 2 * TILE;
   __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full;
+  __shared__ uint64_t x_full[2], l_full;          // row-maximum / row-sum exchange between the two softmax groups
+  __shared__ float xmax[2][2][BQ], xl[2][BQ];
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -71,9 +73,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       mbar_init(smem_u32(&v_full[s]), 1);
       mbar_init(smem_u32(&v_empty[s]), 1);
       mbar_init(smem_u32(&s_full[s]), 1);
-      mbar_init(smem_u32(&s_empty[s]), 128);
+      mbar_init(smem_u32(&s_empty[s]), 256);
+      mbar_init(smem_u32(&x_full[s]), 256);
     }
-    mbar_init(smem_u32(&p_full), 128);
+    mbar_init(smem_u32(&l_full), 256);
+    mbar_init(smem_u32(&p_full), 256);
     mbar_init(smem_u32(&p_empty), 1);
     mbar_init(smem_u32(&o_full), 1);
     abort_flag = 0;
@@ -165,8 +169,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     const int qpos = p.q_start + q0 + row;                // absolute position of this query
     const bool row_valid = (q0 + row) < p.T;
+    const int wg = (warp - 2) >> 2;                       // group 0: key columns 0..63 of every tile, group 1: 64..127
     const float sink2 = p.sinks[head] * LOG2E;
-    float m = sink2, l = 1.0f;
+    float m = sink2, l = wg == 0 ? 1.0f : 0.0f;           // the sink's unit weight is counted once; the groups' sums are added at the end
     bool failed = false;
 
     for (int j = 0; j < n_tiles; ++j) {
@@ -183,7 +188,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // pass 1: row maximum
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = wg * (BKV / 64); c < (wg + 1) * (BKV / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(s_addr + c * 32, r);
         tmem_ld_wait();
@@ -199,6 +204,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         }
       }
       mx *= p.scale_log2;
+      // the row maximum over all 128 columns: exchange the two halves (bounded wait, like every other wait here)
+      xmax[s][wg][row] = mx;
+      mbar_arrive(smem_u32(&x_full[s]));
+      if (!mbar_wait(smem_u32(&x_full[s]), ph, abortp)) { failed = true; break; }
+      mx = fmaxf(mx, xmax[s][wg ^ 1][row]);
       // lazy rescale: keep the old reference max unless the new one exceeds it by more than 2^8
       float factor = 1.0f;
       if (mx > m + 8.0f) {
@@ -212,7 +222,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
         tc_fence_after();
         if (__any_sync(0xffffffffu, factor != 1.0f)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
+          for (int c = wg; c < D / 32; c += 2) {           // each group rescales half of the accumulator's columns
             uint32_t r[32];
             tmem_ld32(tmem + lane_addr + O_COL + c * 32, r);
             tmem_ld_wait();
@@ -226,7 +236,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // pass 2: probabilities -> shared memory (bf16, K-major 128B swizzle), row sum
       float sum = 0.0f;
 #pragma unroll 1
-      for (int c = 0; c < BKV / 32; ++c) {
+      for (int c = wg * (BKV / 64); c < (wg + 1) * (BKV / 64); ++c) {
         uint32_t r[32];
         tmem_ld32(s_addr + c * 32, r);
         tmem_ld_wait();
@@ -272,10 +282,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       abort_flag = 1;
     } else {
       tc_fence_after();
+      xl[wg][row] = l;                                      // add the two groups' partial row sums
+      mbar_arrive(smem_u32(&l_full));
+      if (!mbar_wait(smem_u32(&l_full), 0, abortp)) {
+        if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+        abort_flag = 1;
+      }
+      l = xl[0][row] + xl[1][row];
       const float inv = 1.0f / l;
       __nv_bfloat16* orow = p.out + (((long long)b * p.T + (q0 + row)) * p.Nq + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = wg; c < D / 32; c += 2) {
         uint32_t r[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem + lane_addr + O_COL + c * 32, r);
@@ -296,7 +313,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           }
         }
       }
-      if (row_valid) p.lse[((long long)b * p.Nq + head) * p.T + q0 + row] = (m + log2f(l)) * LN2;
+      if (row_valid && wg == 0) p.lse[((long long)b * p.Nq + head) * p.T + q0 + row] = (m + log2f(l)) * LN2;
     }
   }
 #undef FA_FAIL
