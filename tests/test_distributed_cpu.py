@@ -101,3 +101,41 @@ def test_two_rank_step_matches_single_process(tmp_path):
     assert torch.allclose(load_leaf(ck, some_expert, ShardInfo()), ref[some_expert], atol=1.5e-3)
     some_dense = next(iter(sorted(owner)))
     assert torch.allclose(load_leaf(ck, some_dense, ShardInfo()), ref[some_dense], atol=1.5e-3)
+
+
+def _serve_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lyra_b200.generate import BatchedGenerator
+        from lyra_b200.model import ModelWeights
+        from lyra_b200.parallel.runtime import Runtime
+
+        c = replace(_cfg(), sample_temperature=0.0)
+        rt = Runtime.create(world_size=world, rank=rank, device="cpu", implementation="nccl", mcfg=c)
+        w = ModelWeights.init(0, c, shard_fn=rt.shard_info)
+        rt.register(w)
+        prompts = torch.from_numpy(np.load(tmp + "/prompts.npy"))[rank * 2:(rank + 1) * 2]      # this rank's rows of the batch
+        gen = BatchedGenerator(w, c, batch=2, capacity=16, device="cpu", rt=rt)
+        toks = gen.decode(gen.prefill(prompts), 6)
+        torch.save(toks, f"{tmp}/serve{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_serving_matches_single_process(tmp_path):
+    """Prefill + greedy decode with the experts sharded over two ranks (each rank serves its own rows, weights pulled from
+    their owners) produces the tokens of the single-process generator."""
+    from lyra_b200.generate import BatchedGenerator
+    from lyra_b200.model import ModelWeights
+
+    c = replace(_cfg(), sample_temperature=0.0)
+    prompts = np.random.default_rng(1).integers(0, c.vocab_size, size=(4, 8)).astype(np.int64)
+    np.save(tmp_path / "prompts.npy", prompts)
+    port = 29900 + os.getpid() % 90
+    mp.spawn(_serve_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    w = ModelWeights.init(0, c)
+    gen = BatchedGenerator(w, c, batch=4, capacity=16, device="cpu")
+    want = gen.decode(gen.prefill(torch.from_numpy(prompts)), 6)
+    got = torch.cat([torch.load(tmp_path / f"serve{r}.pt") for r in range(2)])
+    assert torch.equal(want, got)
