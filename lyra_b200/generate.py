@@ -118,7 +118,7 @@ class BatchedGenerator:
         self.model, self.rt, self.device = model, rt, torch.device(device)
         self.prefill_cfg = replace(mcfg, mode=Mode.PREFILL)
         self.decode_cfg = replace(mcfg, mode=Mode.DECODE)
-        self.cache = init_cache(mcfg, capacity, device, batch)
+        self.cache = init_cache(mcfg, capacity, device, batch, getattr(rt, "n_kv_local", None))   # tensor parallel: this rank's kv heads only
         self.batch, self.capacity = batch, capacity
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
         self._graph = None

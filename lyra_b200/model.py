@@ -368,10 +368,14 @@ def moe_apply(x, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE,
         xn = xn.reshape(B * T, C)
         with scope("route_tokens"):
             scores, indices, aux = route_tokens(xn, w, c, probe=probe, rt=rt)
+        tp = rt.tp_size if rt is not None else 1
+        # tensor parallel: every rank holds a slice of each expert's hidden units; the partial outputs are summed below, so the
+        # (replicated) down-projection bias enters as bias / tp on every rank (lyra/model.py:549)
+        down_bias = w.mlp_down_bias / tp if (tp > 1 and w.mlp_down_bias is not None) else w.mlp_down_bias
         if rt is not None and rt.ep_size > 1:
             t = rt.ep_moe(xn, scores, indices, w, c)
         elif c.mode == Mode.DECODE and ops.use_kernels(xn, impl) and not xn.requires_grad:
-            t = ops._cuda().decode_moe(xn, scores, indices, w.mlp_up, w.mlp_up_bias, w.mlp_down, w.mlp_down_bias,
+            t = ops._cuda().decode_moe(xn, scores, indices, w.mlp_up, w.mlp_up_bias, w.mlp_down, down_bias,
                                        c.swiglu_beta, c.swiglu_limit)
         else:
             up, down = w.mlp_up, w.mlp_down
@@ -380,8 +384,10 @@ def moe_apply(x, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE,
             if isinstance(down, QArray):
                 down = dequantize(down, xn.dtype)
             with scope("experts"):
-                t = ops.moe_experts(xn, scores, indices, up, w.mlp_up_bias, down, w.mlp_down_bias,
+                t = ops.moe_experts(xn, scores, indices, up, w.mlp_up_bias, down, down_bias,
                                     c.swiglu_beta, c.swiglu_limit, impl)
+        if tp > 1:
+            t = rt.tp_all_reduce(t)
         t = t.reshape(B, T, C).to(x.dtype)
         probe.tensor("combined", t)
         t = t * c.residual_scale

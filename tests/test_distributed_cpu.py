@@ -139,3 +139,90 @@ def test_expert_parallel_serving_matches_single_process(tmp_path):
     want = gen.decode(gen.prefill(torch.from_numpy(prompts)), 6)
     got = torch.cat([torch.load(tmp_path / f"serve{r}.pt") for r in range(2)])
     assert torch.equal(want, got)
+
+
+def _tp_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lyra_b200.generate import BatchedGenerator
+        from lyra_b200.model import ModelWeights, model_apply
+        from lyra_b200.parallel.tp import TensorParallel
+
+        c = replace(_cfg(), sample_temperature=0.0, use_qkv_bias=True, use_attn_out_bias=True, use_mlp_bias=True, use_sdpa_output_gate=True,
+                    use_learned_xsa=True)
+        tp = TensorParallel(c, rank, world)
+        w = ModelWeights.init(3, c, shard_fn=tp.shard_info)
+        _randomise_zero_init(w)
+        prompts = torch.from_numpy(np.load(tmp + "/prompts.npy"))
+        with torch.no_grad():
+            logits, _, _ = model_apply(prompts, w, None, c, rt=tp)
+        gen = BatchedGenerator(w, c, batch=prompts.shape[0], capacity=16, device="cpu", rt=tp)
+        toks = gen.decode(gen.prefill(prompts), 5)
+        torch.save({"logits": logits, "tokens": toks, "q_shape": tuple(w.layers[0].attn.q.shape),
+                    "kv_cache": tuple(gen.cache.layers[0].k.shape)}, f"{tmp}/tp{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def _randomise_zero_init(w):
+    """Biases, sinks, gates and XSA strengths start at zero; give them values so that their sharding is exercised. Every rank
+    derives the same full tensor from the leaf's path and takes its own slice, like the initialiser does."""
+    import zlib
+
+    from lyra_b200.nn.params import tree_dict
+
+    for path, t in tree_dict(w).items():
+        name = path.split("/")[-1]
+        if name.endswith("_bias") or name in ("sinks", "xsa_alpha", "sdpa_gate"):
+            t.data = t.data + _full_noise(path, name, t)
+
+
+def _full_noise(path, name, t):
+    import zlib
+
+    g = torch.Generator().manual_seed(zlib.crc32(path.encode()))
+    full_shape = list(t.shape)
+    rank, world = (dist.get_rank(), dist.get_world_size()) if dist.is_initialized() else (0, 1)
+    from lyra_b200.parallel.tp import _COLUMNS, _ROWS, _VECTORS
+
+    dim = None
+    if name in _COLUMNS:
+        dim = 1
+    elif name in _ROWS or name in _VECTORS:
+        dim = 0
+    elif name == "mlp_up_bias":
+        dim = t.ndim - 1
+    if dim is not None and world > 1:
+        full_shape[dim] *= world
+    full = torch.randn(full_shape, generator=g) * 0.1
+    if dim is not None and world > 1:
+        n = full.shape[dim] // world
+        full = full.narrow(dim, rank * n, n)
+    return full.to(t.dtype)
+
+
+def test_tensor_parallel_inference_matches_single_process(tmp_path):
+    """Heads and hidden units split over two ranks (Megatron layout), one all-reduce per block: same logits and greedy tokens."""
+    from lyra_b200.generate import BatchedGenerator
+    from lyra_b200.model import ModelWeights, model_apply
+
+    c = replace(_cfg(), sample_temperature=0.0, use_qkv_bias=True, use_attn_out_bias=True, use_mlp_bias=True, use_sdpa_output_gate=True,
+                use_learned_xsa=True)
+    prompts = np.random.default_rng(2).integers(0, c.vocab_size, size=(3, 8)).astype(np.int64)
+    np.save(tmp_path / "prompts.npy", prompts)
+    port = 29800 + os.getpid() % 90
+    mp.spawn(_tp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    w = ModelWeights.init(3, c)
+    _randomise_zero_init(w)
+    with torch.no_grad():
+        want, _, _ = model_apply(torch.from_numpy(prompts), w, None, c)
+    gen = BatchedGenerator(w, c, batch=3, capacity=16, device="cpu")
+    tokens = gen.decode(gen.prefill(torch.from_numpy(prompts)), 5)
+    for r in range(2):
+        got = torch.load(tmp_path / f"tp{r}.pt")
+        assert got["q_shape"][1] * 2 == w.layers[0].attn.q.shape[1]          # half of the query heads per rank
+        assert got["kv_cache"][1] * 2 == c.n_kv_heads                          # and half of the kv heads in its cache
+        live = want[..., : c.vocab_size]
+        assert torch.allclose(got["logits"][..., : c.vocab_size], live, atol=2e-4, rtol=1e-4), (got["logits"][..., : c.vocab_size] - live).abs().max()
+        assert torch.equal(got["tokens"], tokens)
