@@ -16,6 +16,14 @@ sys.path.insert(0, str(ROOT))
 pytestmark = pytest.mark.gpu
 
 
+def _free_port() -> int:
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]
+
+
 def _cfg():
     from lyra_b200.config import ModelConfig
 
@@ -67,7 +75,7 @@ def _worker(rank, world, port, tmp):
 def test_peer_memory_runtime_matches_collective_runtime(tmp_path):
     import torch.multiprocessing as mp
 
-    port = 29900 + os.getpid() % 90
+    port = _free_port()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     init = None
     for r in range(2):
@@ -132,7 +140,7 @@ def _ag_worker(rank, world, port, tmp):
 def test_allgather_fused_gemm(tmp_path):
     import torch.multiprocessing as mp
 
-    port = 29800 + os.getpid() % 90
+    port = _free_port()
     mp.spawn(_ag_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         res = torch.load(tmp_path / f"ag{r}.pt", weights_only=False)
