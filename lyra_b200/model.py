@@ -332,6 +332,9 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
     vals, idx = torch.topk(logits, k, dim=-1)  # ties -> lower index first, like lax.top_k
     scores = torch.softmax(vals, dim=-1)
     aux = calculate_aux_loss(logits, idx, c, probe=probe)
+    meter = getattr(rt, "load_meter", None)
+    if meter is not None and torch.is_grad_enabled():            # training forwards only: the load that sets the step time
+        meter.add(rt._layer, idx)
     if probe.enabled:
         probe.routing("routing", router_logits=logits, expert_scores=scores,
                       group_sizes=ref_ops.count_ids(idx, c.n_routed_experts),

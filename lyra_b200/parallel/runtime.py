@@ -111,6 +111,7 @@ class Runtime:
         self._comm = None
         self._ep_state: dict = {}
         self._layer = 0
+        self.load_meter = None                                   # ExpertLoadMeter once expert re-placement is switched on
 
     @classmethod
     def create(cls, *, world_size: int, rank: int, device, implementation: str = "b200", mcfg: ModelConfig | None = None) -> "Runtime":
@@ -299,6 +300,24 @@ class Runtime:
         return path not in self.plan.replicated or self.rank == 0
 
     # ------------------------------------------------------------------ expert parallel MoE
+    def meter_expert_load(self) -> bool:
+        """Starts counting the tokens every routed expert slot receives (input of ``rebalance_experts``). Returns whether
+        there is anything to re-place (experts sharded over more than one rank)."""
+        if self.ep_size <= 1:
+            return False
+        if self.load_meter is None:
+            from lyra_b200.parallel.placement import ExpertLoadMeter
+
+            moe_layers = [i for i, kind in enumerate(self.mcfg.mlp_map) if kind == "moe"]
+            self.load_meter = ExpertLoadMeter(moe_layers, self.mcfg.n_routed_experts, self.device)
+        return True
+
+    def rebalance_experts(self, params: dict[str, torch.Tensor], optimizer_state, *, min_gain: float = 0.05) -> dict:
+        """Collective, between steps: moves experts (masters and moments) so that the ranks draw equal numbers of tokens."""
+        from lyra_b200.parallel.placement import rebalance_experts
+
+        return rebalance_experts(self, params, optimizer_state, min_gain=min_gain)
+
     def ep_moe(self, xn, scores, indices, w, c: ModelConfig):
         from lyra_b200.parallel.ep import ep_moe_forward
 

@@ -81,6 +81,12 @@ class TrainingConfig:
     peer_timeout_seconds: float = 600.0
     """Multi-rank runs: how long a rank waits at a step boundary for the others' heartbeat before it gives up (an addition; the reference has no failure detection)."""
 
+    rebalance_experts_every: int | None = None
+    """Expert-parallel runs: every this many steps the experts of each MoE layer are re-placed on the ranks by the token counts
+    measured since the last time (an addition; None = static placement as in the reference)."""
+    rebalance_min_gain: float = 0.05
+    """A layer is re-placed only if its heaviest rank gets at least this much lighter."""
+
     sample_prompts: tuple[str, ...] = DEFAULT_SAMPLE_PROMPTS
     sample_tokens: int = 128
     checkpoint_path: Path = CHECKPOINT_DIR / "model"
@@ -252,6 +258,8 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
 
         heartbeat = Heartbeat(_get_default_store(), rt.rank, rt.world)
 
+    rebalancing = tcfg.rebalance_experts_every is not None and rt is not None and rt.meter_expert_load()
+
     run_start = time.perf_counter()
     try:
         for step in range(start_step + 1, tcfg.steps + 1):
@@ -275,6 +283,11 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
                     torch.cuda.synchronize()
             metrics.record(aux)
             hooks.after_step(step, state, aux, time.perf_counter() - step_start if timed else None)
+            if rebalancing and step % tcfg.rebalance_experts_every == 0 and step < tcfg.steps:
+                moved = rt.rebalance_experts(stepper.params, state.optimizer, min_gain=tcfg.rebalance_min_gain)
+                if primary and moved["layers_moved"]:
+                    print(f"\n[experts] step {step:,}: re-placed {moved['layers_moved']} layers; heaviest rank's share of the tokens "
+                          f"{moved['max_share_before']:.3f} -> {moved['max_share_after']:.3f} (balanced: {1 / rt.world:.3f})")
 
             checkpoint = due(tcfg.checkpoint_every, step)
             evaluating = eval_loader is not None and due(tcfg.eval_every, step)

@@ -69,6 +69,8 @@ class Args:
     """Peak Muon learning rate."""
     grad_clip: float | None = None
     """Per-matrix Muon gradient RMS limit."""
+    rebalance_experts_every: int | None = None
+    """Multi-GPU runs: re-place the experts on the ranks by measured token counts every this many steps."""
 
 
 FIELDS = {
@@ -77,6 +79,7 @@ FIELDS = {
     "numerics_every": "numerics_every", "chkpt_every": "checkpoint_every", "chkpt_keep": "checkpoint_keep",
     "decay_type": "decay_type", "warmup_fraction": "warmup_fraction", "stable_fraction": "stable_fraction",
     "adam_lr": "adam_max_lr", "muon_lr": "muon_max_lr", "grad_clip": "muon_grad_clip",
+    "rebalance_experts_every": "rebalance_experts_every",
 }
 PATH_FIELDS = {"data": "data_path", "eval_data": "eval_data_path", "out": "checkpoint_path", "resume": "resume_from"}
 
