@@ -17,3 +17,12 @@ def small_config(**kw):
 def token_file(path, n=6000, vocab=500, seed=0):
     np.save(path, np.random.default_rng(seed).integers(0, vocab, size=n).astype("<i4"))
     return path
+
+
+def free_port() -> int:
+    """A port the OS hands out as free right now (fixed ports can collide with a socket of an earlier test in TIME_WAIT)."""
+    import socket
+
+    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]

@@ -14,16 +14,9 @@ import torch.multiprocessing as mp
 
 ROOT = Path(__file__).resolve().parents[1]
 sys.path.insert(0, str(ROOT))
+
+from tests.helpers import free_port  # noqa: E402
 os.environ["LYRA_SMALL_LEAF"] = "2048"  # shard the small test model's matrices too (inherited by the spawned ranks)
-
-
-def _free_port() -> int:
-    """A port the OS hands out as free right now (fixed ports can collide with a socket of an earlier test in TIME_WAIT)."""
-    import socket
-
-    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
-        sock.bind(("127.0.0.1", 0))
-        return sock.getsockname()[1]
 
 
 def _cfg():
@@ -80,7 +73,7 @@ def test_two_rank_step_matches_single_process(tmp_path):
     rng = np.random.default_rng(0)
     data = rng.integers(0, c.vocab_size, size=(2, 4, c.seq_len)).astype(np.int32)
     np.save(tmp_path / "batch.npy", data)
-    port = _free_port()
+    port = free_port()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
 
     tcfg = TrainingConfig(steps=4, batch_size=4, accumulation_steps=2)
@@ -141,7 +134,7 @@ def test_expert_parallel_serving_matches_single_process(tmp_path):
     c = replace(_cfg(), sample_temperature=0.0)
     prompts = np.random.default_rng(1).integers(0, c.vocab_size, size=(4, 8)).astype(np.int64)
     np.save(tmp_path / "prompts.npy", prompts)
-    port = _free_port()
+    port = free_port()
     mp.spawn(_serve_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     w = ModelWeights.init(0, c)
     gen = BatchedGenerator(w, c, batch=4, capacity=16, device="cpu")
@@ -220,7 +213,7 @@ def test_tensor_parallel_inference_matches_single_process(tmp_path):
                 use_learned_xsa=True)
     prompts = np.random.default_rng(2).integers(0, c.vocab_size, size=(3, 8)).astype(np.int64)
     np.save(tmp_path / "prompts.npy", prompts)
-    port = _free_port()
+    port = free_port()
     mp.spawn(_tp_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     w = ModelWeights.init(3, c)
     _randomise_zero_init(w)

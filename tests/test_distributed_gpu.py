@@ -13,15 +13,9 @@ import torch
 ROOT = Path(__file__).resolve().parents[1]
 sys.path.insert(0, str(ROOT))
 
+from tests.helpers import free_port  # noqa: E402
+
 pytestmark = pytest.mark.gpu
-
-
-def _free_port() -> int:
-    import socket
-
-    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
-        sock.bind(("127.0.0.1", 0))
-        return sock.getsockname()[1]
 
 
 def _cfg():
@@ -75,7 +69,7 @@ def _worker(rank, world, port, tmp):
 def test_peer_memory_runtime_matches_collective_runtime(tmp_path):
     import torch.multiprocessing as mp
 
-    port = _free_port()
+    port = free_port()
     mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     init = None
     for r in range(2):
@@ -140,7 +134,7 @@ def _ag_worker(rank, world, port, tmp):
 def test_allgather_fused_gemm(tmp_path):
     import torch.multiprocessing as mp
 
-    port = _free_port()
+    port = free_port()
     mp.spawn(_ag_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
         res = torch.load(tmp_path / f"ag{r}.pt", weights_only=False)

@@ -16,6 +16,7 @@ sys.path.insert(0, str(ROOT))
 os.environ["LYRA_SMALL_LEAF"] = "2048"
 
 from lyra_b200.parallel.placement import ExpertLoadMeter, apply_slot_permutation, plan_slots, rank_loads  # noqa: E402
+from tests.helpers import free_port  # noqa: E402
 
 
 def test_planner_balances_within_capacities_and_moves_little():
@@ -81,14 +82,6 @@ def _cfg():
                         vocab_size=2000, padded_vocab_size=2048, compute_dtype=torch.float32, seq_len=16, load_balance_weight=0.0)
 
 
-def _free_port() -> int:
-    import socket
-
-    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
-        sock.bind(("127.0.0.1", 0))
-        return sock.getsockname()[1]
-
-
 def _worker(rank, world, port, tmp):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -131,7 +124,7 @@ def test_two_ranks_move_experts_mid_run_and_keep_the_trajectory(tmp_path):
     c = _cfg()
     data = np.random.default_rng(0).integers(0, c.vocab_size, size=(2, 4, c.seq_len)).astype(np.int32)
     np.save(tmp_path / "batch.npy", data)
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
     got = torch.load(tmp_path / "placement.pt", weights_only=False)
 
     tcfg = TrainingConfig(steps=8, batch_size=4, accumulation_steps=2)
@@ -177,7 +170,7 @@ def test_training_loop_with_periodic_re_placement_matches_the_static_run(tmp_pat
 
     c = _cfg()
     token_file(tmp_path / "tok.npy", n=4 * 8 * (c.seq_len + 1) * 4, vocab=c.vocab_size)
-    mp.spawn(_loop_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_loop_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
     train(ModelWeights.init(0, c), c, _loop_tcfg(tmp_path, "static"), device="cpu")
 
     def losses(run):
