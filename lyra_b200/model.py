@@ -199,6 +199,8 @@ def attention_apply(x, w: AttentionWeights, idx: int, pos: int, freq_cis, cache:
     with scope("attention"):
         h = ops.rms_norm(x, W(w.norm_scale), c.norm_eps, impl)
         probe.tensor("norm_out", h)
+        if rt is not None and rt.tp_size > 1:
+            h = rt.tp_copy(h)                                # q / k / v and the gate are column-sharded: their input gradients are partial
         with scope("qkv_projection"):
             q = ops.linear(h, _dq(W(w.q), h.dtype), W(w.q_bias), impl).reshape(B, T, -1, c.head_dim)
             k = ops.linear(h, _dq(W(w.k), h.dtype), W(w.k_bias), impl).reshape(B, T, -1, c.head_dim)
@@ -375,6 +377,8 @@ def moe_apply(x, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE,
         # tensor parallel: every rank holds a slice of each expert's hidden units; the partial outputs are summed below, so the
         # (replicated) down-projection bias enters as bias / tp on every rank (lyra/model.py:549)
         down_bias = w.mlp_down_bias / tp if (tp > 1 and w.mlp_down_bias is not None) else w.mlp_down_bias
+        if tp > 1:                                           # the experts' hidden units are split: gradients of their inputs are partial
+            xn, scores = rt.tp_copy(xn), rt.tp_copy(scores)
         if rt is not None and rt.ep_size > 1:
             t = rt.ep_moe(xn, scores, indices, w, c)
         elif c.mode == Mode.DECODE and ops.use_kernels(xn, impl) and not xn.requires_grad:
@@ -439,6 +443,8 @@ def dense_mlp_apply(x, w: DenseMLPWeights, config: ModelConfig, *, probe: Probe 
     with scope("dense_mlp"):
         t = ops.rms_norm(x, W(w.norm_scale), c.norm_eps, impl)
         probe.tensor("norm_out", t)
+        if rt is not None and rt.tp_size > 1:
+            t = rt.tp_copy(t)
         up = _dq(W(w.mlp_up), t.dtype)
         if probe.detailed:
             C, _, H = up.shape

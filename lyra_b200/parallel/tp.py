@@ -12,9 +12,21 @@ dense down-projection; biases of row-sharded layers are divided by the axis size
   partial results are summed with one all-reduce per block (``tp_all_reduce``; the expert down-projection bias enters as
   ``bias / tp`` on every rank so that the sum restores it).
 
-This runtime is forward-only: there is no gradient or optimizer sharding for the model axis (training runs shard by leaf
-ownership and by expert, see ``parallel/runtime.py``). It works on any ``torch.distributed`` backend; every rank must be
-given the same input rows."""
+Training on the model axis (every rank sees the same rows; the axis is not combined with data or expert parallelism here):
+
+* the all-reduce after a row-sharded layer is the identity in backward, and ``tp_copy`` - the identity in forward, applied
+  where a replicated activation (the normalised layer input, the routing scores) enters sharded layers - sums the partial
+  gradients over the axis in backward, so replicated parameters upstream see whole gradients (Megatron's ``g`` / ``f`` pair);
+* replicated parameters that sit inside a sharded region receive partial gradients and are summed in ``reduce_grads``: the
+  per-head-dim q / k norm scales (every rank normalises its own heads) and the expert down-projection bias (``bias / tp``);
+* parameters, gradients and moments of a sharded leaf stay sharded; Muon's per-matrix RMS and Newton-Schulz need whole
+  matrices, so ``optimizer_step`` gathers the gradient and the update direction over the axis (``gather_leaf``) and keeps
+  its own slice of the result (``slice_leaf``). Adam is element-wise and stays local;
+* checkpoints hold global arrays: every rank writes its slice (``shard_of`` / ``checkpoint_leaves``), rank 0 the replicated
+  leaves.
+
+The step runs the PyTorch optimizer (``owns_optimizer``) and library collectives on any ``torch.distributed`` backend; the
+fused peer-memory paths of ``parallel/runtime.py`` do not apply to this axis."""
 
 from __future__ import annotations
 
@@ -24,18 +36,53 @@ import torch
 import torch.distributed as dist
 
 from lyra_b200.config import ModelConfig
-from lyra_b200.nn.params import ShardInfo
+from lyra_b200.nn.params import ShardInfo, tree_dict
 
 _COLUMNS = {"q", "k", "v", "sdpa_gate"}                 # [C, heads * ...]: shard dim 1
 _ROWS = {"out"}                                         # [heads * hd, C]: shard dim 0
 _VECTORS = {"q_bias", "k_bias", "v_bias", "sinks", "xsa_alpha"}   # [heads (* hd)]: shard dim 0
 
 
+_PARTIAL_GRADS = {"qnorm_scale", "knorm_scale"}         # replicated, but each rank sees only its own heads
+
+
+class _SumForward(torch.autograd.Function):
+    """Sum over the axis in forward, identity in backward (after a row-sharded layer)."""
+
+    @staticmethod
+    def forward(ctx, t, group):
+        t = t.contiguous().clone()
+        dist.all_reduce(t, group=group)
+        return t
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class _SumBackward(torch.autograd.Function):
+    """Identity in forward, sum over the axis in backward (in front of column-sharded layers)."""
+
+    @staticmethod
+    def forward(ctx, t, group):
+        ctx.group = group
+        return t.view_as(t)
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.contiguous().clone()
+        dist.all_reduce(g, group=ctx.group)
+        return g, None
+
+
 class TensorParallel:
-    """Runtime object accepted by ``model_apply(..., rt=...)`` and ``BatchedGenerator(..., rt=...)``."""
+    """Runtime object accepted by ``model_apply(..., rt=...)``, ``BatchedGenerator(..., rt=...)`` and ``Stepper(..., rt=...)``."""
 
     implementation = "nccl"
     ep_size = 1
+    data_size, data_rank = 1, 0                          # every rank of the axis works on the same rows
+    owns_optimizer = True                                # the step uses the PyTorch optimizer with the gather hooks below
+    load_meter = None
 
     def __init__(self, mcfg: ModelConfig, rank: int, size: int, group=None):
         if mcfg.n_attn_heads % size or mcfg.n_kv_heads % size:
@@ -69,6 +116,102 @@ class TensorParallel:
 
     def tp_all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.tp_size > 1:
+            if torch.is_grad_enabled() and t.requires_grad:
+                return _SumForward.apply(t, self.group)
             t = t.contiguous()
             dist.all_reduce(t, group=self.group)
         return t
+
+    def tp_copy(self, t: torch.Tensor) -> torch.Tensor:
+        """Marks the point where a replicated activation enters sharded layers."""
+        if self.tp_size > 1 and torch.is_grad_enabled() and t.requires_grad:
+            return _SumBackward.apply(t, self.group)
+        return t
+
+    # ------------------------------------------------------------------ training hooks (the stepper's contract)
+    def _specs(self) -> dict:
+        if not hasattr(self, "_spec_cache"):
+            from lyra_b200.model import ModelWeights
+
+            self._spec_cache = tree_dict(ModelWeights.spec(self.mcfg))
+        return self._spec_cache
+
+    def _info(self, path: str) -> ShardInfo:
+        spec = self._specs().get(path)
+        return self.shard_info(path, spec) if spec is not None else ShardInfo()
+
+    def register(self, params: Any) -> None:
+        pass
+
+    def meter_expert_load(self) -> bool:
+        return False                                      # every rank holds a slice of every expert: nothing to re-place
+
+    def begin_microbatch(self, index: int, total: int) -> None:
+        pass
+
+    def after_optimizer(self, params: dict[str, torch.Tensor]) -> None:
+        pass
+
+    def barrier(self) -> None:
+        dist.barrier(group=self.group)
+
+    def sum_scalars(self, t: torch.Tensor) -> torch.Tensor:
+        return t                                          # same rows on every rank: the loss is already the job's loss
+
+    def sum_over_ranks(self, *ts: torch.Tensor):
+        stacked = torch.stack([t.float() for t in ts])
+        dist.all_reduce(stacked, group=self.group)
+        return tuple(stacked.unbind(0))
+
+    def max_over_ranks(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.clone()
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        return t
+
+    def counts_once(self, path: str) -> bool:
+        """Whether this rank counts ``path`` in global norms: its own slice of a sharded leaf, replicated leaves on rank 0."""
+        return bool(self._info(path).slices) or self.rank == 0
+
+    @torch.no_grad()
+    def reduce_grads(self, grads: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        specs = self._specs()
+        for path, g in grads.items():
+            name = path.split("/")[-1]
+            if name in _PARTIAL_GRADS or (name == "mlp_down_bias" and specs[path].kind.startswith("moe_")):
+                dist.all_reduce(g, group=self.group)
+        return grads
+
+    def gather_leaf(self, path: str, t: torch.Tensor) -> torch.Tensor:
+        info = self._info(path)
+        if not info.slices:
+            return t
+        (dim, _, parts), = info.slices
+        pieces = [torch.empty_like(t) for _ in range(parts)]
+        dist.all_gather(pieces, t.contiguous(), group=self.group)
+        return torch.cat(pieces, dim=dim)
+
+    def slice_leaf(self, path: str, full: torch.Tensor) -> torch.Tensor:
+        return self._info(path).narrow(full)
+
+    # ------------------------------------------------------------------ checkpoints (global arrays, one slice per rank)
+    def shard_of(self, path: str, t: torch.Tensor):
+        spec = self._specs().get(path)
+        if spec is None:
+            return tuple(t.shape), ShardInfo()
+        return tuple(spec.shape), self.shard_info(path, spec)
+
+    def writes_leaf(self, path: str) -> bool:
+        return bool(self._info(path).slices) or self.rank == 0
+
+    def checkpoint_leaves(self, name: str, tree: Any):
+        present = tree_dict(tree)
+        specs = self._specs()
+        if not present or not all(p in specs for p in present):
+            return None
+        out = {}
+        for p, t in present.items():
+            parts = [1] * len(specs[p].shape)
+            for dim, _, n in self._info(p).slices:
+                parts[dim] = n
+            out[p] = (tuple(specs[p].shape), t.dtype, tuple(parts))
+        return out

@@ -123,17 +123,22 @@ def optimizer_step(params: dict[str, torch.Tensor], grads: dict[str, torch.Tenso
     finite = torch.isfinite(grad_norm)
     enabled = finite.float()
 
+    # Under tensor parallelism a rank holds a column or row slice of each matrix: the per-matrix RMS and Newton-Schulz need
+    # the whole matrix, so the runtime gathers it (``gather_leaf``) and hands back this rank's slice (``slice_leaf``).
+    gather = getattr(rt, "gather_leaf", None)
+    take = getattr(rt, "slice_leaf", None)
     all_rms = []
     clipped: dict[str, torch.Tensor] = {}
     for p in muon_paths:
         g = grads[p]
-        m, swapped = as_matrices(p, g.float())
+        local, swapped = as_matrices(p, g.float())
+        m = as_matrices(p, gather(p, g).float())[0] if gather is not None else local
         msq = (m * m).sum(dim=(-2, -1), keepdim=True)
         numel = m.shape[-2] * m.shape[-1]
         r = (msq / numel).sqrt()
         all_rms.append(r.reshape(-1))
         scale = torch.where(torch.isfinite(r), torch.clamp(tcfg.muon_grad_clip / (r + 1e-8), max=1.0), torch.ones_like(r))
-        c = m * scale
+        c = local * scale
         clipped[p] = (c.transpose(-3, -2) if swapped else c).to(g.dtype)
     all_rms_t = torch.cat(all_rms) if all_rms else torch.zeros(1, device=dev)
     metrics = {
@@ -155,11 +160,13 @@ def optimizer_step(params: dict[str, torch.Tensor], grads: dict[str, torch.Tenso
         m_new = (momentum * state.muon_moment[p].float() + g).to(tcfg.muon_moment_dtype)
         state.muon_moment[p].copy_(m_new)
         d = (g + tcfg.muon_momentum * m_new.float()) if tcfg.muon_nesterov else m_new.float()
-        dm, swapped = as_matrices(p, d)
-        ns = newtonschulz(dm)  # every matrix is whole on the rank that updates it
+        dm, swapped = as_matrices(p, gather(p, d) if gather is not None else d)
+        ns = newtonschulz(dm)  # every matrix is whole here: owned as a whole leaf, or gathered over the model axis
         rows, cols = dm.shape[-2], dm.shape[-1]
         stepv = lr_m * ns.float() * (math.sqrt(max(rows, cols)) * tcfg.muon_update_rms)
         stepv = stepv.transpose(-3, -2) if swapped else stepv
+        if take is not None:
+            stepv = take(p, stepv)
         w = params[p]
         w.copy_((w.float() - (stepv + lr_m * tcfg.muon_wd * w.float())).to(w.dtype))
 

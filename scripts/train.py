@@ -69,6 +69,8 @@ class Args:
     """Peak Muon learning rate."""
     grad_clip: float | None = None
     """Per-matrix Muon gradient RMS limit."""
+    tensor_parallel: bool = False
+    """Multi-rank runs: split heads and hidden units over the ranks (every rank sees all rows) instead of leaf ownership + expert parallelism."""
     rebalance_experts_every: int | None = None
     """Multi-GPU runs: re-place the experts on the ranks by measured token counts every this many steps."""
 
@@ -132,6 +134,11 @@ def main(argv: list[str] | None = None) -> int:
         from lyra_b200.parallel.runtime import Runtime
 
         dist.init_process_group("nccl" if use_gpu else "gloo")
+    if world > 1 and args.tensor_parallel:
+        from lyra_b200.parallel.tp import TensorParallel
+
+        rt = TensorParallel(mcfg, dist.get_rank(), world)
+    elif world > 1:
         rt = Runtime.create(world_size=world, rank=dist.get_rank(), device=device,
                             implementation="nccl" if (args.implementation in ("torch", "nccl") or not use_gpu) else "b200", mcfg=mcfg)
     if rt is None or rt.rank == 0:

@@ -228,3 +228,115 @@ def test_tensor_parallel_inference_matches_single_process(tmp_path):
         live = want[..., : c.vocab_size]
         assert torch.allclose(got["logits"][..., : c.vocab_size], live, atol=2e-4, rtol=1e-4), (got["logits"][..., : c.vocab_size] - live).abs().max()
         assert torch.equal(got["tokens"], tokens)
+
+
+def _tp_train_cfg():
+    # the balance term is kept: every rank of the model axis routes the same rows, so it is the single-process term
+    return replace(_cfg(), use_qkv_bias=True, use_attn_out_bias=True, use_mlp_bias=True, use_sdpa_output_gate=True, use_learned_xsa=True,
+                   load_balance_weight=1e-2)
+
+
+def _exact_newton_schulz():
+    """Replaces the bf16 Newton-Schulz by a float64 one for a comparison: in bf16 a last-bit difference of a gradient (summation
+    order across ranks) moves the result by percents, which would hide a real error of the sharding logic."""
+    import lyra_b200.training.optimizer as O
+
+    def ns(X, eps=1e-7):
+        tall = X.shape[-2] > X.shape[-1]
+        X = X.double()
+        X = X / (1.01 * torch.linalg.matrix_norm(X, dim=(-2, -1), keepdim=True) + eps)
+        X = X.transpose(-1, -2) if tall else X
+        for a, b, c in O.POLAR_EXPRESS_COEFFS:
+            A = X @ X.transpose(-1, -2)
+            X = a * X + (b * A + c * (A @ A)) @ X
+        return (X.transpose(-1, -2) if tall else X).float()
+
+    O.newtonschulz = ns
+
+
+def _tp_tcfg():
+    from lyra_b200.training.train import TrainingConfig
+
+    return TrainingConfig(steps=4, batch_size=2, accumulation_steps=2, muon_moment_dtype=torch.float32, adam_mu_dtype=torch.float32)
+
+
+def _tp_train_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _exact_newton_schulz()
+    try:
+        from lyra_b200.model import ModelWeights
+        from lyra_b200.nn.params import tree_dict
+        from lyra_b200.parallel.tp import TensorParallel
+        from lyra_b200.training.state import init_train_state, load_train_state, save_checkpoint
+        from lyra_b200.training.steps import Stepper
+        from lyra_b200.training.train import TrainingConfig
+
+        c = _tp_train_cfg()
+        tcfg = _tp_tcfg()
+        tp = TensorParallel(c, rank, world)
+        w = ModelWeights.init(3, c, shard_fn=tp.shard_info)
+        _randomise_zero_init(w)
+        state = init_train_state(w, c, tcfg)
+        st = Stepper(state, c, tcfg, device="cpu", rt=tp)
+        data = np.load(tmp + "/batch.npy")                      # every rank of the model axis sees all rows
+        out = None
+        for step in range(3):
+            out = st.train_step(data, np.roll(data, -1, axis=-1), step)
+        torch.save({"loss": float(out["loss"]), "grad_norm": float(out["grad_norm"]), "rms_max": float(out["muon_grad_rms_max"]),
+                    "params": {p: t.detach().clone() for p, t in tree_dict(w).items()}}, f"{tmp}/tptrain{rank}.pt")
+        save_checkpoint(Path(tmp) / "tpckpt", 3, state, b'{"position": 0}', {"resume_signature": {}}, keep=1, rt=tp)
+        restored = load_train_state(Path(tmp) / "tpckpt", c, tcfg, rt=tp)
+        a, b = tree_dict(state.params), tree_dict(restored.state.params)
+        assert all(torch.equal(a[k], b[k]) for k in a)
+        assert all(torch.equal(state.optimizer.muon_moment[k], restored.state.optimizer.muon_moment[k]) for k in state.optimizer.muon_moment)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_training_matches_single_process(tmp_path):
+    """Three optimizer steps with heads and hidden units split over two ranks: the same loss, gradient norm and parameters as
+    one process (partial gradients summed where a replicated tensor enters sharded layers, Muon on gathered matrices), and a
+    checkpoint that holds the global arrays."""
+    from lyra_b200.model import ModelWeights
+    from lyra_b200.nn.checkpoints import load_leaf
+    from lyra_b200.nn.params import ShardInfo, tree_dict
+    from lyra_b200.parallel.tp import TensorParallel
+    from lyra_b200.training.state import init_train_state
+    from lyra_b200.training.steps import Stepper
+    from lyra_b200.training.train import TrainingConfig
+
+    c = _tp_train_cfg()
+    data = np.random.default_rng(5).integers(0, c.vocab_size, size=(2, 2, c.seq_len)).astype(np.int32)
+    np.save(tmp_path / "batch.npy", data)
+    mp.spawn(_tp_train_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+
+    import lyra_b200.training.optimizer as O
+
+    tcfg = _tp_tcfg()
+    w = ModelWeights.init(3, c)
+    _randomise_zero_init(w)
+    st = Stepper(init_train_state(w, c, tcfg), c, tcfg, device="cpu")
+    bf16_ns = O.newtonschulz
+    _exact_newton_schulz()
+    try:
+        for step in range(3):
+            out = st.train_step(data, np.roll(data, -1, axis=-1), step)
+    finally:
+        O.newtonschulz = bf16_ns
+    ref = tree_dict(w)
+    ranks = [torch.load(tmp_path / f"tptrain{r}.pt", weights_only=False) for r in range(2)]
+    for r in range(2):
+        assert abs(ranks[r]["loss"] - float(out["loss"])) < 1e-4
+        assert abs(ranks[r]["grad_norm"] - float(out["grad_norm"])) < 1e-3 * float(out["grad_norm"])
+        assert abs(ranks[r]["rms_max"] - float(out["muon_grad_rms_max"])) < 1e-3 * float(out["muon_grad_rms_max"])
+    sharded = 0
+    for p, full in ref.items():
+        for r in range(2):
+            info = TensorParallel(c, r, 2)._info(p)
+            sharded += bool(info.slices)
+            assert torch.allclose(ranks[r]["params"][p], info.narrow(full), atol=3e-5), (p, (ranks[r]["params"][p] - info.narrow(full)).abs().max())
+    assert sharded > 20
+    ck = tmp_path / "tpckpt" / "step_00000003" / "params"
+    for p in ("layers/1/attn/q", "layers/1/mlp/mlp_up", "layers/0/mlp/mlp_down", "layers/1/attn/qnorm_scale", "layers/1/attn/sinks"):
+        assert torch.allclose(load_leaf(ck, p, ShardInfo()), ref[p], atol=3e-5), p
