@@ -43,9 +43,9 @@ def apply_inference_overrides(mcfg: ModelConfig, icfg: InferenceConfig) -> Model
     return mcfg
 
 
-def load_model(mcfg: ModelConfig, icfg: InferenceConfig, device="cpu") -> ModelWeights:
+def load_model(mcfg: ModelConfig, icfg: InferenceConfig, device="cpu", rt=None) -> ModelWeights:
     mcfg = apply_inference_overrides(mcfg, icfg)
-    return ModelWeights.quantize(ModelWeights.load(icfg.weights, mcfg, device=device), mcfg)
+    return ModelWeights.quantize(ModelWeights.load(icfg.weights, mcfg, device=device, rt=rt), mcfg)
 
 
 def _key(seed: int, *folds: int) -> torch.Generator:
@@ -77,7 +77,12 @@ def sample_token(logits: torch.Tensor, key: torch.Generator | None, mcfg: ModelC
 def generate(ctx: torch.Tensor, model: ModelWeights, cache: ModelCache, key, mcfg: ModelConfig, sample_pos: int, rt=None):
     """One model call + one sampled token for a single sequence ``ctx [1, T]`` (lyra/generate.py:56-61)."""
     logits, _, updated = model_apply(ctx, model, cache, mcfg, rt=rt)
-    return sample_token(logits[0, sample_pos], key, mcfg), updated
+    token = sample_token(logits[0, sample_pos], key, mcfg)
+    if getattr(rt, "tp_size", 1) > 1:      # the ranks of a model axis must feed back the same token: rank 0's draw is the one that counts
+        import torch.distributed as dist
+
+        dist.broadcast(token, src=dist.get_global_rank(rt.group, 0) if rt.group is not None else 0, group=rt.group)
+    return token, updated
 
 
 def init_cache(mcfg: ModelConfig, length: int, device="cpu", batch: int = 1, n_kv_local: int | None = None) -> ModelCache:
@@ -90,7 +95,7 @@ def sample_tokens(model: ModelWeights, seed_key: tuple[int, ...], mcfg: ModelCon
     """Prefill + token-by-token decode on the device; returns ``max_new_tokens`` ids (lyra/generate.py:64-85)."""
     prefill, decode = replace(mcfg, mode=Mode.PREFILL), replace(mcfg, mode=Mode.DECODE)
     n = len(prompt)
-    cache = init_cache(mcfg, n + max_new_tokens, device)
+    cache = init_cache(mcfg, n + max_new_tokens, device, n_kv_local=getattr(rt, "n_kv_local", None))
     ctx = torch.tensor([prompt], dtype=torch.long, device=device)
     token, cache = generate(ctx, model, cache, _key(*seed_key, 0), prefill, n - 1, rt)
     cache.pos = n
@@ -261,7 +266,7 @@ def serve_model(model: ModelWeights, mcfg: ModelConfig, icfg: InferenceConfig, *
                 continue
             output_fn("\n[context window full; starting a new conversation]\n")
 
-        cache = init_cache(mcfg, capacity, device)
+        cache = init_cache(mcfg, capacity, device, n_kv_local=getattr(rt, "n_kv_local", None))
         ctx = torch.tensor([context], dtype=torch.long, device=device)
         token, cache = generate(ctx, model, cache, _key(mcfg.seed, turn, -1), prefill_cfg, len(context) - 1, rt)
         cache.pos = len(context)

@@ -64,9 +64,10 @@ def _interleave_glu(x: torch.Tensor) -> torch.Tensor:
     return torch.stack((x[..., 0, :], x[..., 1, :]), dim=-1).reshape(*x.shape[:-2], -1)
 
 
-def load_gpt_oss_model(source, config: ModelConfig, device="cpu", expert_slice: tuple[int, int] | None = None):
+def load_gpt_oss_model(source, config: ModelConfig, device="cpu", expert_slice: tuple[int, int] | None = None, shard_fn=None):
     """Reads a GPT-OSS checkpoint into a ``ModelWeights`` tree (then applies ``ModelWeights.quantize``).
-    ``expert_slice = (lo, hi)`` keeps only experts ``lo:hi`` (an expert-parallel rank's share)."""
+    ``expert_slice = (lo, hi)`` keeps only experts ``lo:hi`` (an expert-parallel rank's share); ``shard_fn(path, spec)``
+    (a runtime's ``shard_info``) keeps this rank's slice of every leaf (a tensor-parallel rank's heads and hidden units)."""
     from safetensors import safe_open
 
     from lyra_b200.model import ModelWeights
@@ -83,8 +84,10 @@ def load_gpt_oss_model(source, config: ModelConfig, device="cpu", expert_slice: 
         with safe_open(files[name], framework="pt") as f:
             return f.get_tensor(name)
 
-    def place(value, spec, dtype=None):
+    def place(value, spec, dtype=None, path=None):
         assert tuple(value.shape) == tuple(spec.shape) or expert_slice is not None, (value.shape, spec.shape)
+        if shard_fn is not None:
+            value = shard_fn(path, spec).narrow(value)
         return value.to(dtype or spec.dtype).to(device).contiguous()
 
     def padded_vocab(name: str):
@@ -94,27 +97,33 @@ def load_gpt_oss_model(source, config: ModelConfig, device="cpu", expert_slice: 
     ex = (lambda t: t[expert_slice[0]:expert_slice[1]]) if expert_slice else (lambda t: t)
     spec = ModelWeights.spec(config)
     q_dim, kv_dim = config.n_attn_heads * config.head_dim, config.n_kv_heads * config.head_dim
-    tok = replace(spec.tok, emb=place(padded_vocab("embedding.weight"), spec.tok.emb),
-                  unemb=place(padded_vocab("unembedding.weight"), spec.tok.unemb), norm_scale=place(get("norm.scale"), spec.tok.norm_scale))
+    tok = replace(spec.tok, emb=place(padded_vocab("embedding.weight"), spec.tok.emb, path="tok/emb"),
+                  unemb=place(padded_vocab("unembedding.weight"), spec.tok.unemb, path="tok/unemb"),
+                  norm_scale=place(get("norm.scale"), spec.tok.norm_scale, path="tok/norm_scale"))
     layers = []
     for index, layer in enumerate(spec.layers):
         block, attn, mlp = f"block.{index}", layer.attn, layer.mlp  # GPT-OSS is MoE in every layer
+        at, ml = f"layers/{index}/attn/", f"layers/{index}/mlp/"
         q, k, v = torch.split(get(f"{block}.attn.qkv.weight"), [q_dim, kv_dim, kv_dim])
         qb, kb, vb = torch.split(get(f"{block}.attn.qkv.bias"), [q_dim, kv_dim, kv_dim])
         attn = replace(
-            attn, q=place(q.T, attn.q), k=place(k.T, attn.k), v=place(v.T, attn.v), q_bias=place(qb, attn.q_bias),
-            k_bias=place(kb, attn.k_bias), v_bias=place(vb, attn.v_bias), sinks=place(get(f"{block}.attn.sinks"), attn.sinks),
-            out=place(get(f"{block}.attn.out.weight").T, attn.out), out_bias=place(get(f"{block}.attn.out.bias"), attn.out_bias),
-            norm_scale=place(get(f"{block}.attn.norm.scale"), attn.norm_scale),
+            attn, q=place(q.T, attn.q, path=at + "q"), k=place(k.T, attn.k, path=at + "k"), v=place(v.T, attn.v, path=at + "v"),
+            q_bias=place(qb, attn.q_bias, path=at + "q_bias"), k_bias=place(kb, attn.k_bias, path=at + "k_bias"),
+            v_bias=place(vb, attn.v_bias, path=at + "v_bias"), sinks=place(get(f"{block}.attn.sinks"), attn.sinks, path=at + "sinks"),
+            out=place(get(f"{block}.attn.out.weight").T, attn.out, path=at + "out"),
+            out_bias=place(get(f"{block}.attn.out.bias"), attn.out_bias, path=at + "out_bias"),
+            norm_scale=place(get(f"{block}.attn.norm.scale"), attn.norm_scale, path=at + "norm_scale"),
         )
         up = dequantize_mxfp4(ex(get(f"{block}.mlp.mlp1_weight.blocks")).to(device), ex(get(f"{block}.mlp.mlp1_weight.scales")).to(device)).transpose(1, 2)
         down = dequantize_mxfp4(ex(get(f"{block}.mlp.mlp2_weight.blocks")).to(device), ex(get(f"{block}.mlp.mlp2_weight.scales")).to(device)).transpose(1, 2)
         mlp = replace(
-            mlp, router=place(get(f"{block}.mlp.gate.weight").T, mlp.router), router_bias=place(get(f"{block}.mlp.gate.bias"), mlp.router_bias),
-            mlp_up=place(_deinterleave_glu(up), mlp.mlp_up, torch.bfloat16),
-            mlp_up_bias=place(_deinterleave_glu(ex(get(f"{block}.mlp.mlp1_bias"))), mlp.mlp_up_bias),
-            mlp_down=place(down, mlp.mlp_down, torch.bfloat16), mlp_down_bias=place(ex(get(f"{block}.mlp.mlp2_bias")), mlp.mlp_down_bias),
-            norm_scale=place(get(f"{block}.mlp.norm.scale"), mlp.norm_scale),
+            mlp, router=place(get(f"{block}.mlp.gate.weight").T, mlp.router, path=ml + "router"),
+            router_bias=place(get(f"{block}.mlp.gate.bias"), mlp.router_bias, path=ml + "router_bias"),
+            mlp_up=place(_deinterleave_glu(up), mlp.mlp_up, torch.bfloat16, path=ml + "mlp_up"),
+            mlp_up_bias=place(_deinterleave_glu(ex(get(f"{block}.mlp.mlp1_bias"))), mlp.mlp_up_bias, path=ml + "mlp_up_bias"),
+            mlp_down=place(down, mlp.mlp_down, torch.bfloat16, path=ml + "mlp_down"),
+            mlp_down_bias=place(ex(get(f"{block}.mlp.mlp2_bias")), mlp.mlp_down_bias, path=ml + "mlp_down_bias"),
+            norm_scale=place(get(f"{block}.mlp.norm.scale"), mlp.norm_scale, path=ml + "norm_scale"),
         )
         layers.append(replace(layer, attn=attn, mlp=mlp))
     return ModelWeights.quantize(ModelWeights(tok=tok, layers=layers), config)

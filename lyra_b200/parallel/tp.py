@@ -215,3 +215,26 @@ class TensorParallel:
                 parts[dim] = n
             out[p] = (tuple(specs[p].shape), t.dtype, tuple(parts))
         return out
+
+
+def shared_terminal(rt: TensorParallel, input_fn=input, output_fn=print) -> dict:
+    """``input_fn`` / ``output_fn`` for an interactive loop that runs on every rank of the axis: rank 0 talks to the user,
+    the others receive what it read (an ``EOFError`` included) and print nothing."""
+
+    def read(prompt: str) -> str:
+        box = [None]
+        if rt.rank == 0:
+            try:
+                box[0] = input_fn(prompt)
+            except EOFError:
+                box[0] = EOFError
+        dist.broadcast_object_list(box, src=dist.get_global_rank(rt.group, 0) if rt.group is not None else 0, group=rt.group)
+        if box[0] is EOFError:
+            raise EOFError
+        return box[0]
+
+    def write(*args, **kwargs) -> None:
+        if rt.rank == 0:
+            output_fn(*args, **kwargs)
+
+    return {"input_fn": read, "output_fn": write}

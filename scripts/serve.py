@@ -1,7 +1,12 @@
-"""Chat with a checkpoint (own Orbax-layout checkpoints or GPT-OSS ``original/`` checkpoints)."""
+"""Chat with a checkpoint (own Orbax-layout checkpoints or GPT-OSS ``original/`` checkpoints).
+
+Under ``python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 scripts/serve.py ...`` the model is split
+over the N ranks tensor-parallel (heads and hidden units; a model that does not fit one GPU): rank 0 owns the terminal, reads
+the prompt and prints the reply, the others receive the prompt and take part in every model call."""
 
 from __future__ import annotations
 
+import os
 import sys
 from dataclasses import dataclass
 from pathlib import Path
@@ -43,12 +48,28 @@ def main(argv: list[str] | None = None) -> int:
     from lyra_b200.gpt_oss import load_gpt_oss_model
     from lyra_b200.variants import model_variant
 
-    device = "cuda" if (args.device == "gpu" or (args.device == "auto" and torch.cuda.is_available())) else "cpu"
+    use_gpu = args.device == "gpu" or (args.device == "auto" and torch.cuda.is_available())
+    world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    if use_gpu:
+        torch.cuda.set_device(local)
+    device = f"cuda:{local}" if use_gpu else "cpu"
     icfg = InferenceConfig(weights=args.weights or str(ROOT / "chkpt" / args.variant), max_new_tokens=args.max_new_tokens,
                            max_cache_length=args.max_cache_length, temperature=args.temperature, top_k=args.top_k, fp8=args.fp8)
     mcfg = apply_inference_overrides(model_variant(args.variant), icfg)
-    model = load_gpt_oss_model(icfg.weights, mcfg, device=device) if args.format == "gpt-oss" else load_model(mcfg, icfg, device=device)
-    serve_model(model, mcfg, icfg, harmony=args.format == "gpt-oss", device=device)
+    rt, io = None, {}
+    if world > 1:
+        import torch.distributed as dist
+
+        from lyra_b200.parallel.tp import TensorParallel, shared_terminal
+
+        dist.init_process_group("nccl" if use_gpu else "gloo")
+        rt = TensorParallel(mcfg, dist.get_rank(), world)
+        io = shared_terminal(rt)
+    if args.format == "gpt-oss":
+        model = load_gpt_oss_model(icfg.weights, mcfg, device=device, shard_fn=rt.shard_info if rt is not None else None)
+    else:
+        model = load_model(mcfg, icfg, device=device, rt=rt)
+    serve_model(model, mcfg, icfg, harmony=args.format == "gpt-oss", device=device, rt=rt, **io)
     return 0
 
 

@@ -340,3 +340,60 @@ def test_tensor_parallel_training_matches_single_process(tmp_path):
     ck = tmp_path / "tpckpt" / "step_00000003" / "params"
     for p in ("layers/1/attn/q", "layers/1/mlp/mlp_up", "layers/0/mlp/mlp_down", "layers/1/attn/qnorm_scale", "layers/1/attn/sinks"):
         assert torch.allclose(load_leaf(ck, p, ShardInfo()), ref[p], atol=3e-5), p
+
+
+def _gpt_oss_cfg(**kw):
+    from lyra_b200.config import ModelConfig
+
+    return ModelConfig(name="Tiny GPT-OSS", seq_len=32, n_embd=64, n_layers=2, mlp_map=("moe", "moe"), vocab_size=201088, padded_vocab_size=201088,
+                       head_dim=16, n_attn_heads=4, n_kv_heads=2, sliding_window=8, n_routed_experts=4, n_shared_experts=0, n_active_experts=2,
+                       expert_mlp_widening=2.0, rope_scale=32.0, tie_embeddings=False, use_qk_norm=False, use_qkv_bias=True,
+                       use_attn_out_bias=True, use_mlp_bias=True, use_router_bias=True, param_dtype=torch.bfloat16, compute_dtype=torch.float32,
+                       implementation="torch", **kw)
+
+
+def _chat(model, c, rt=None, **io):
+    from lyra_b200.generate import InferenceConfig, serve_model
+
+    prompts = iter(["hello there", "and again", "exit"])
+    printed = []
+    terminal = dict(input_fn=lambda _: next(prompts), output_fn=lambda *a, **k: printed.append("".join(map(str, a))))
+    if rt is not None:
+        from lyra_b200.parallel.tp import shared_terminal
+
+        terminal = shared_terminal(rt, **terminal)
+    serve_model(model, c, InferenceConfig(weights="x", max_new_tokens=6, max_cache_length=32), device="cpu", rt=rt, **terminal)
+    return printed
+
+
+def _tp_chat_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lyra_b200.gpt_oss import load_gpt_oss_model
+        from lyra_b200.parallel.tp import TensorParallel
+
+        out = {}
+        for name, c in (("greedy", _gpt_oss_cfg(sample_temperature=0.0)), ("sampled", _gpt_oss_cfg(sample_temperature=1.0, sample_topk=8))):
+            tp = TensorParallel(c, rank, world)
+            model = load_gpt_oss_model(tmp + "/ckpt", c, shard_fn=tp.shard_info)
+            assert model.layers[0].attn.q.shape[1] == c.n_attn_heads * c.head_dim // world
+            out[name] = _chat(model, c, tp)
+        torch.save(out, f"{tmp}/chat{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tensor_parallel_chat_from_a_gpt_oss_checkpoint(tmp_path):
+    """The serving loop on two ranks of a model axis: each rank reads its heads and hidden units from the GPT-OSS files, rank 0
+    owns the terminal, and the greedy reply is the single-process reply."""
+    from lyra_b200.gpt_oss import load_gpt_oss_model, write_random_gpt_oss_checkpoint
+
+    c = _gpt_oss_cfg(sample_temperature=0.0)
+    write_random_gpt_oss_checkpoint(tmp_path / "ckpt", c, seed=4)
+    want = _chat(load_gpt_oss_model(tmp_path / "ckpt", c), c)
+    mp.spawn(_tp_chat_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    rank0, rank1 = (torch.load(tmp_path / f"chat{r}.pt", weights_only=False) for r in range(2))
+    assert rank0["greedy"] == want and len("".join(want)) > len("Type a prompt")
+    assert rank1["greedy"] == [] and rank1["sampled"] == []            # the other rank prints nothing
+    assert len(rank0["sampled"]) == len(want)                          # both turns ran with rank 0's sampled tokens fed to both ranks
