@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import os
 import sys
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -44,21 +45,37 @@ def main(argv: list[str] | None = None) -> int:
     from lyra_b200.model import ModelWeights
     from lyra_b200.variants import model_variant
 
-    device = "cuda" if (args.device == "gpu" or (args.device == "auto" and torch.cuda.is_available())) else "cpu"
+    use_gpu = args.device == "gpu" or (args.device == "auto" and torch.cuda.is_available())
+    world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    if use_gpu:
+        torch.cuda.set_device(local)
+    device = f"cuda:{local}" if use_gpu else "cpu"
     config = model_variant(args.variant)
     weights = args.weights or str(ROOT / "chkpt" / args.variant)
-    model = load_gpt_oss_model(weights, config, device=device) if args.format == "gpt-oss" else ModelWeights.load(weights, config, device=device)
-    scorer = Scorer(model, config, batch_size=args.batch_size, harmony=args.format == "gpt-oss", device=device)
+    rt = None
+    if world > 1:   # under torch.distributed.run the model is split tensor-parallel; every rank scores the same documents
+        import torch.distributed as dist
+
+        from lyra_b200.parallel.tp import TensorParallel
+
+        dist.init_process_group("nccl" if use_gpu else "gloo")
+        rt = TensorParallel(config, dist.get_rank(), world)
+    say = print if rt is None or rt.rank == 0 else (lambda *a, **k: None)
+    if args.format == "gpt-oss":
+        model = load_gpt_oss_model(weights, config, device=device, shard_fn=rt.shard_info if rt is not None else None)
+    else:
+        model = ModelWeights.load(weights, config, device=device, rt=rt)
+    scorer = Scorer(model, config, batch_size=args.batch_size, harmony=args.format == "gpt-oss", device=device, rt=rt)
     results = []
     for task in args.tasks:
         shots = args.fewshot.get(task, 0)
         docs = TASKS[task](limit=args.limit, num_fewshot=shots, fewshot_seed=args.fewshot_seed)
-        print(f"Running {task} ({shots}-shot) on {len(docs)} documents...", flush=True)
+        say(f"Running {task} ({shots}-shot) on {len(docs)} documents...", flush=True)
         results.append(evaluate(task, docs, scorer))
-        print(results[-1], flush=True)
-    print("\nResults")
+        say(results[-1], flush=True)
+    say("\nResults")
     for result in results:
-        print(result)
+        say(result)
     return 0
 
 
