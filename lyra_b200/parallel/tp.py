@@ -12,7 +12,8 @@ dense down-projection; biases of row-sharded layers are divided by the axis size
   partial results are summed with one all-reduce per block (``tp_all_reduce``; the expert down-projection bias enters as
   ``bias / tp`` on every rank so that the sum restores it).
 
-Training on the model axis (every rank sees the same rows; the axis is not combined with data or expert parallelism here):
+Training on the model axis (every rank of an axis sees the same rows; ``TensorParallel.mesh`` adds a data axis of replicas
+around it, with gradients summed over the replicas; expert parallelism is the other runtime's business):
 
 * the all-reduce after a row-sharded layer is the identity in backward, and ``tp_copy`` - the identity in forward, applied
   where a replicated activation (the normalised layer input, the routing scores) enters sharded layers - sums the partial
@@ -85,11 +86,34 @@ class TensorParallel:
     load_meter = None
 
     def __init__(self, mcfg: ModelConfig, rank: int, size: int, group=None):
+        """One model axis of ``size`` ranks (``group``, or all ranks); ``rank`` is the index on it. See ``mesh`` for data x model."""
         if mcfg.n_attn_heads % size or mcfg.n_kv_heads % size:
             raise ValueError(f"{mcfg.n_attn_heads} query / {mcfg.n_kv_heads} kv heads do not split over {size} ranks")
-        self.mcfg, self.rank, self.tp_size, self.group = mcfg, rank, size, group
-        self.world = size
+        self.mcfg, self.rank, self.tp_rank, self.tp_size, self.group = mcfg, rank, rank, size, group
+        self.world, self.world_group, self.data_group = size, group, None
         self.n_kv_local = mcfg.n_kv_heads // size
+
+    @classmethod
+    def mesh(cls, mcfg: ModelConfig, rank: int, world: int, model_axis: int) -> "TensorParallel":
+        """``world = data x model`` ranks of the default process group, the model axis fastest (ranks ``d * model .. d * model +
+        model - 1`` hold one replica; the reference's ``tensor_parallel(data_axis, model_axis)`` layout, lyra/nn/params.py:168-265).
+        Rows are split over the data axis; gradients are summed over it after the partial gradients of the model axis."""
+        if world % model_axis:
+            raise ValueError(f"{world} ranks do not split into model axes of {model_axis}")
+        data = world // model_axis
+        self = cls(mcfg, rank % model_axis, model_axis)
+        self.rank, self.world, self.world_group = rank, world, None
+        self.data_size, self.data_rank = data, rank // model_axis
+        # every rank creates every group, in the same order
+        for d in range(data):
+            g = dist.new_group(list(range(d * model_axis, (d + 1) * model_axis)))
+            if d == self.data_rank:
+                self.group = g
+        for m in range(model_axis):
+            g = dist.new_group(list(range(m, world, model_axis)))
+            if m == self.tp_rank:
+                self.data_group = g
+        return self
 
     # ------------------------------------------------------------------ placement
     def shard_info(self, path: str, spec: Any) -> ShardInfo:
@@ -98,13 +122,13 @@ class TensorParallel:
         if self.tp_size == 1:
             return ShardInfo()
         if name in _COLUMNS:
-            return ShardInfo(((1, self.rank, self.tp_size),))
+            return ShardInfo(((1, self.tp_rank, self.tp_size),))
         if name in _ROWS or name in _VECTORS:
-            return ShardInfo(((0, self.rank, self.tp_size),))
+            return ShardInfo(((0, self.tp_rank, self.tp_size),))
         if name in ("mlp_up", "mlp_up_bias"):
-            return ShardInfo(((nd - 1, self.rank, self.tp_size),))
+            return ShardInfo(((nd - 1, self.tp_rank, self.tp_size),))
         if name == "mlp_down":
-            return ShardInfo(((nd - 2, self.rank, self.tp_size),))
+            return ShardInfo(((nd - 2, self.tp_rank, self.tp_size),))
         return ShardInfo()
 
     # ------------------------------------------------------------------ hooks of the model code
@@ -153,24 +177,27 @@ class TensorParallel:
         pass
 
     def barrier(self) -> None:
-        dist.barrier(group=self.group)
+        dist.barrier(group=self.world_group)
 
     def sum_scalars(self, t: torch.Tensor) -> torch.Tensor:
-        return t                                          # same rows on every rank: the loss is already the job's loss
+        if self.data_size > 1:                            # the ranks of a model axis see the same rows; the data axis splits them
+            dist.all_reduce(t, group=self.data_group)
+        return t
 
     def sum_over_ranks(self, *ts: torch.Tensor):
         stacked = torch.stack([t.float() for t in ts])
-        dist.all_reduce(stacked, group=self.group)
+        dist.all_reduce(stacked, group=self.world_group)
         return tuple(stacked.unbind(0))
 
     def max_over_ranks(self, t: torch.Tensor) -> torch.Tensor:
         t = t.clone()
-        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.world_group)
         return t
 
     def counts_once(self, path: str) -> bool:
-        """Whether this rank counts ``path`` in global norms: its own slice of a sharded leaf, replicated leaves on rank 0."""
-        return bool(self._info(path).slices) or self.rank == 0
+        """Whether this rank counts ``path`` in global norms: on the first replica, every rank its own slice of a sharded leaf
+        and the first rank the replicated leaves."""
+        return self.data_rank == 0 and (bool(self._info(path).slices) or self.tp_rank == 0)
 
     @torch.no_grad()
     def reduce_grads(self, grads: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
@@ -179,6 +206,8 @@ class TensorParallel:
             name = path.split("/")[-1]
             if name in _PARTIAL_GRADS or (name == "mlp_down_bias" and specs[path].kind.startswith("moe_")):
                 dist.all_reduce(g, group=self.group)
+            if self.data_size > 1:                        # the loss terms carry 1 / data_size: a sum over the replicas
+                dist.all_reduce(g, group=self.data_group)
         return grads
 
     def gather_leaf(self, path: str, t: torch.Tensor) -> torch.Tensor:
@@ -201,7 +230,7 @@ class TensorParallel:
         return tuple(spec.shape), self.shard_info(path, spec)
 
     def writes_leaf(self, path: str) -> bool:
-        return bool(self._info(path).slices) or self.rank == 0
+        return self.data_rank == 0 and (bool(self._info(path).slices) or self.tp_rank == 0)
 
     def checkpoint_leaves(self, name: str, tree: Any):
         present = tree_dict(tree)
@@ -228,7 +257,7 @@ def shared_terminal(rt: TensorParallel, input_fn=input, output_fn=print) -> dict
                 box[0] = input_fn(prompt)
             except EOFError:
                 box[0] = EOFError
-        dist.broadcast_object_list(box, src=dist.get_global_rank(rt.group, 0) if rt.group is not None else 0, group=rt.group)
+        dist.broadcast_object_list(box, src=dist.get_global_rank(rt.world_group, 0) if rt.world_group is not None else 0, group=rt.world_group)
         if box[0] is EOFError:
             raise EOFError
         return box[0]

@@ -70,7 +70,9 @@ class Args:
     grad_clip: float | None = None
     """Per-matrix Muon gradient RMS limit."""
     tensor_parallel: bool = False
-    """Multi-rank runs: split heads and hidden units over the ranks (every rank sees all rows) instead of leaf ownership + expert parallelism."""
+    """Multi-rank runs: split heads and hidden units over the ranks of a model axis instead of leaf ownership + expert parallelism."""
+    model_axis: int | None = None
+    """With --tensor-parallel: ranks per model axis (default: all of them); the remaining factor of the ranks is data parallel."""
     rebalance_experts_every: int | None = None
     """Multi-GPU runs: re-place the experts on the ranks by measured token counts every this many steps."""
 
@@ -137,7 +139,7 @@ def main(argv: list[str] | None = None) -> int:
     if world > 1 and args.tensor_parallel:
         from lyra_b200.parallel.tp import TensorParallel
 
-        rt = TensorParallel(mcfg, dist.get_rank(), world)
+        rt = TensorParallel.mesh(mcfg, dist.get_rank(), world, args.model_axis or world)
     elif world > 1:
         rt = Runtime.create(world_size=world, rank=dist.get_rank(), device=device,
                             implementation="nccl" if (args.implementation in ("torch", "nccl") or not use_gpu) else "b200", mcfg=mcfg)

@@ -397,3 +397,92 @@ def test_tensor_parallel_chat_from_a_gpt_oss_checkpoint(tmp_path):
     assert rank0["greedy"] == want and len("".join(want)) > len("Type a prompt")
     assert rank1["greedy"] == [] and rank1["sampled"] == []            # the other rank prints nothing
     assert len(rank0["sampled"]) == len(want)                          # both turns ran with rank 0's sampled tokens fed to both ranks
+
+
+def _mesh_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _exact_newton_schulz()
+    try:
+        from lyra_b200.model import ModelWeights
+        from lyra_b200.nn.params import tree_dict
+        from lyra_b200.parallel.tp import TensorParallel
+        from lyra_b200.training.state import init_train_state, save_checkpoint
+        from lyra_b200.training.steps import Stepper
+
+        c = replace(_tp_train_cfg(), load_balance_weight=0.0)   # a product of per-replica means: not additive over the data axis
+        tcfg = replace(_tp_tcfg(), batch_size=4)
+        tp = TensorParallel.mesh(c, rank, world, model_axis=2)
+        assert (tp.data_size, tp.data_rank, tp.tp_rank) == (2, rank // 2, rank % 2)
+        w = ModelWeights.init(3, c, shard_fn=tp.shard_info)
+        _randomise_zero_init_on(w, tp.tp_rank, 2)
+        state = init_train_state(w, c, tcfg)
+        st = Stepper(state, c, tcfg, device="cpu", rt=tp)
+        data = np.load(tmp + "/batch.npy")[:, tp.data_rank * 2:(tp.data_rank + 1) * 2]   # this replica's rows
+        for step in range(2):
+            out = st.train_step(data, np.roll(data, -1, axis=-1), step)
+        torch.save({"loss": float(out["loss"]), "grad_norm": float(out["grad_norm"]),
+                    "params": {p: t.detach().clone() for p, t in tree_dict(w).items()}}, f"{tmp}/mesh{rank}.pt")
+        save_checkpoint(Path(tmp) / "meshckpt", 2, state, b'{"position": 0}', {"resume_signature": {}}, keep=1, rt=tp)
+    finally:
+        dist.destroy_process_group()
+
+
+def _randomise_zero_init_on(w, tp_rank, tp_size):
+    """``_randomise_zero_init`` for a rank whose index on the model axis differs from its global rank."""
+    import zlib
+
+    from lyra_b200.nn.params import tree_dict
+    from lyra_b200.parallel.tp import _COLUMNS, _ROWS, _VECTORS
+
+    for path, t in tree_dict(w).items():
+        name = path.split("/")[-1]
+        if not (name.endswith("_bias") or name in ("sinks", "xsa_alpha", "sdpa_gate")):
+            continue
+        dim = 1 if name in _COLUMNS else 0 if (name in _ROWS or name in _VECTORS) else t.ndim - 1 if name == "mlp_up_bias" else None
+        shape = list(t.shape)
+        if dim is not None:
+            shape[dim] *= tp_size
+        full = torch.randn(shape, generator=torch.Generator().manual_seed(zlib.crc32(path.encode()))) * 0.1
+        if dim is not None:
+            n = full.shape[dim] // tp_size
+            full = full.narrow(dim, tp_rank * n, n)
+        t.data = t.data + full.to(t.dtype)
+
+
+def test_data_by_model_mesh_training_matches_single_process(tmp_path):
+    """Four ranks as two replicas of a two-rank model axis: rows split over the replicas, heads and hidden units over the axis."""
+    import lyra_b200.training.optimizer as O
+    from lyra_b200.model import ModelWeights
+    from lyra_b200.nn.checkpoints import load_leaf
+    from lyra_b200.nn.params import ShardInfo, tree_dict
+    from lyra_b200.parallel.tp import TensorParallel
+    from lyra_b200.training.state import init_train_state
+    from lyra_b200.training.steps import Stepper
+
+    c = replace(_tp_train_cfg(), load_balance_weight=0.0)
+    data = np.random.default_rng(6).integers(0, c.vocab_size, size=(2, 4, c.seq_len)).astype(np.int32)
+    np.save(tmp_path / "batch.npy", data)
+    mp.spawn(_mesh_worker, args=(4, free_port(), str(tmp_path)), nprocs=4, join=True)
+
+    tcfg = replace(_tp_tcfg(), batch_size=4)
+    w = ModelWeights.init(3, c)
+    _randomise_zero_init_on(w, 0, 1)
+    st = Stepper(init_train_state(w, c, tcfg), c, tcfg, device="cpu")
+    bf16_ns = O.newtonschulz
+    _exact_newton_schulz()
+    try:
+        for step in range(2):
+            out = st.train_step(data, np.roll(data, -1, axis=-1), step)
+    finally:
+        O.newtonschulz = bf16_ns
+    ref = tree_dict(w)
+    for r in range(4):
+        got = torch.load(tmp_path / f"mesh{r}.pt", weights_only=False)
+        assert abs(got["loss"] - float(out["loss"])) < 1e-4 and abs(got["grad_norm"] - float(out["grad_norm"])) < 1e-3 * float(out["grad_norm"])
+        for p, full in ref.items():
+            want = TensorParallel(c, r % 2, 2)._info(p).narrow(full)
+            assert torch.allclose(got["params"][p], want, atol=3e-5), (r, p, (got["params"][p] - want).abs().max())
+    ck = tmp_path / "meshckpt" / "step_00000002" / "params"
+    for p in ("layers/1/attn/q", "layers/1/mlp/mlp_up", "tok/emb"):
+        assert torch.allclose(load_leaf(ck, p, ShardInfo()), ref[p], atol=3e-5), p
