@@ -5,6 +5,7 @@
     python bench/serve.py --layers 4 --new 8 --no-graph    # a small case (e.g. under a profiler)
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 bench/serve.py --variant gpt-oss-120b
                                                            # experts sharded over the ranks, every rank serves its own batch
+    ... bench/serve.py --variant gpt-oss-120b --tensor-parallel     # heads and hidden units split instead, one shared batch
 
 Prints one JSON line: prefill tokens/s, decode tokens/s with the per-token launch sequence replayed from a CUDA graph and
 launched eagerly, and the decode step time against the time to read the active weights and the KV cache once at the
@@ -51,6 +52,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (0 = all)")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights and an e4m3 KV cache")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--tensor-parallel", action="store_true",
+                    help="several ranks: split heads and hidden units over the ranks (one shared batch, library all-reduce per block) instead of expert parallelism")
     args = ap.parse_args()
 
     from lyra_b200.generate import BatchedGenerator
@@ -70,7 +73,16 @@ def main() -> None:
     if args.fp8:
         mcfg = replace(mcfg, quantize_mlp=True, quantize_cache=True, gemm_dtype=torch.float8_e4m3fn, quant_block=(64, 64))
     rt = None
-    if world > 1:   # expert parallel: experts sharded over the ranks, attention replicated, one batch per rank
+    tp = world > 1 and args.tensor_parallel
+    if tp:          # tensor parallel: every rank holds a slice of every layer and all ranks serve the same batch
+        import torch.distributed as dist
+
+        from lyra_b200.parallel.tp import TensorParallel
+
+        dist.init_process_group("nccl", device_id=dev)
+        rt = TensorParallel(mcfg, rank, world)
+        model = ModelWeights.init(0, mcfg, device=dev, shard_fn=rt.shard_info)
+    elif world > 1:   # expert parallel: experts sharded over the ranks, attention replicated, one batch per rank
         import torch.distributed as dist
 
         from lyra_b200.parallel.runtime import Runtime
@@ -85,7 +97,9 @@ def main() -> None:
     if args.fp8:
         model = ModelWeights.quantize(model, mcfg)
     capacity = args.prompt + args.new
-    prompts = torch.randint(0, mcfg.vocab_size, (args.batch, args.prompt), device=dev, generator=torch.Generator(device=dev).manual_seed(1 + rank))
+    prompts = torch.randint(0, mcfg.vocab_size, (args.batch, args.prompt), device=dev,
+                            generator=torch.Generator(device=dev).manual_seed(1 if tp else 1 + rank))   # one shared batch under tensor parallelism
+    served = 1 if tp else world                              # batches served by the job
 
     results = {}
     for mode in (["eager"] if args.no_graph else ["graph", "eager"]):
@@ -117,22 +131,22 @@ def main() -> None:
     frac_active = min(1.0, args.batch * mcfg.n_active_experts / max(1, mcfg.n_experts))
     kv_el = 1 if args.fp8 else 2
     mean_pos = args.prompt + args.new / 2
-    kv = sum(2 * args.batch * mcfg.n_kv_heads * min(mean_pos, mcfg.layer_window(i) or mean_pos) * mcfg.head_dim * kv_el for i in range(mcfg.n_layers))
+    kv = sum(2 * args.batch * (mcfg.n_kv_heads // (world if tp else 1)) * min(mean_pos, mcfg.layer_window(i) or mean_pos) * mcfg.head_dim * kv_el for i in range(mcfg.n_layers))
     step_bytes = total_w - expert_w * (1 - frac_active) + kv
     bw, kind = hbm_gbs()
     step_ms = results[best]["decode_ms"] / steps
     line = {
-        "bench": "batched serve", "n_gpus": world, "parallelism": f"ep{world} + data-parallel attention" if world > 1 else "single", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch": args.batch,
+        "bench": "batched serve", "n_gpus": world, "parallelism": (f"tp{world}" if tp else f"ep{world} + data-parallel attention") if world > 1 else "single", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch": args.batch,
         "prompt_len": args.prompt, "new_tokens": args.new, "dtype": "bf16" + (" + e4m3 experts and KV" if args.fp8 else ""), "data": "synthetic tokens, random-init weights",
-        "prefill_tokens_per_s": round(world * args.batch * args.prompt / results[best]["prefill_ms"] * 1e3, 1),
-        "decode_tokens_per_s": round(world * args.batch * steps / results[best]["decode_ms"] * 1e3, 1),
+        "prefill_tokens_per_s": round(served * args.batch * args.prompt / results[best]["prefill_ms"] * 1e3, 1),
+        "decode_tokens_per_s": round(served * args.batch * steps / results[best]["decode_ms"] * 1e3, 1),
         "decode_ms_per_step": round(step_ms, 3),
         "decode_bytes_per_step_gb": round(step_bytes / 1e9, 3),
         f"decode_frac_of_{kind}_hbm": round(step_bytes / (step_ms * 1e-3) / 1e9 / bw, 3),
         "own_kernel_launches_per_token_eager": round(results["eager"]["launches_per_token"], 1) if "eager" in results else None,
     }
     if not args.no_graph:
-        line["decode_tokens_per_s_eager"] = round(world * args.batch * steps / results["eager"]["decode_ms"] * 1e3, 1)
+        line["decode_tokens_per_s_eager"] = round(served * args.batch * steps / results["eager"]["decode_ms"] * 1e3, 1)
         line["graph_equals_eager"] = same
     if rank == 0:
         print(json.dumps(line), flush=True)

@@ -89,6 +89,11 @@ class MetricsLogger:
             print(f"eval | step {step:,} | loss {record['eval_loss']:.4f} | ce_loss {record['eval_ce_loss']:.4f}")
             self._write(record)
 
+    def log_event(self, kind: str, step: int, fields: dict) -> None:
+        """A row of another kind (e.g. ``experts``: one expert re-placement) for tools that read ``metrics.jsonl``."""
+        if self.enabled:
+            self._write({"kind": kind, "step": step} | {k: float(v) for k, v in fields.items()})
+
     def _write(self, record: dict) -> None:
         self.file.write(json.dumps(record) + "\n")
         self.file.flush()

@@ -285,6 +285,7 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
             hooks.after_step(step, state, aux, time.perf_counter() - step_start if timed else None)
             if rebalancing and step % tcfg.rebalance_experts_every == 0 and step < tcfg.steps:
                 moved = rt.rebalance_experts(stepper.params, state.optimizer, min_gain=tcfg.rebalance_min_gain)
+                metrics.log_event("experts", step, moved)
                 if primary and moved["layers_moved"]:
                     print(f"\n[experts] step {step:,}: re-placed {moved['layers_moved']} layers; heaviest rank's share of the tokens "
                           f"{moved['max_share_before']:.3f} -> {moved['max_share_after']:.3f} (balanced: {1 / rt.world:.3f})")

@@ -177,6 +177,8 @@ def test_training_loop_with_periodic_re_placement_matches_the_static_run(tmp_pat
         rows = [json.loads(l) for l in (tmp_path / run / "metrics.jsonl").read_text().splitlines()]
         return [r["loss"] for r in rows if r["kind"] == "train"]
 
+    events = [json.loads(l) for l in (tmp_path / "moving" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "experts"]
+    assert [e["step"] for e in events] == [2, 4] and events[0]["layers_moved"] >= 1 and events[0]["max_share_after"] <= events[0]["max_share_before"]
     moving, static = losses("moving"), losses("static")
     assert len(moving) == len(static) == 6 and np.allclose(moving, static, atol=3e-4), (moving, static)
     # the checkpoint of the moved model is a relabelled copy of the static one: same multiset of experts per layer
