@@ -52,6 +52,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (0 = all)")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights and an e4m3 KV cache")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--rebalance", action="store_true",
+                    help="expert parallel: one metered warm-up request, then the experts are re-placed on the ranks by its token counts")
     ap.add_argument("--tensor-parallel", action="store_true",
                     help="several ranks: split heads and hidden units over the ranks (one shared batch, library all-reduce per block) instead of expert parallelism")
     args = ap.parse_args()
@@ -101,6 +103,18 @@ def main() -> None:
                             generator=torch.Generator(device=dev).manual_seed(1 if tp else 1 + rank))   # one shared batch under tensor parallelism
     served = 1 if tp else world                              # batches served by the job
 
+    placement = None
+    if args.rebalance and world > 1 and not tp and not args.fp8:
+        from lyra_b200.nn.params import tree_dict
+
+        rt.meter_expert_load(inference=True)
+        gen = BatchedGenerator(model, mcfg, batch=args.batch, capacity=capacity, device=dev, rt=rt, use_cuda_graph=False)
+        gen.decode(gen.prefill(prompts), min(args.new, 8))
+        placement = rt.rebalance_experts(tree_dict(model))
+        rt.load_meter = None                               # the timed runs carry no metering
+        del gen
+        torch.cuda.empty_cache()
+
     results = {}
     for mode in (["eager"] if args.no_graph else ["graph", "eager"]):
         gen = BatchedGenerator(model, mcfg, batch=args.batch, capacity=capacity, device=dev, rt=rt, use_cuda_graph=(mode == "graph"))
@@ -148,6 +162,8 @@ def main() -> None:
     if not args.no_graph:
         line["decode_tokens_per_s_eager"] = round(served * args.batch * steps / results["eager"]["decode_ms"] * 1e3, 1)
         line["graph_equals_eager"] = same
+    if placement is not None:
+        line["expert_placement"] = {k: round(float(v), 4) for k, v in placement.items()}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

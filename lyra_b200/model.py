@@ -335,7 +335,7 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
     scores = torch.softmax(vals, dim=-1)
     aux = calculate_aux_loss(logits, idx, c, probe=probe)
     meter = getattr(rt, "load_meter", None)
-    if meter is not None and torch.is_grad_enabled():            # training forwards only: the load that sets the step time
+    if meter is not None and (meter.always or torch.is_grad_enabled()):   # training forwards (or every call of a serving process)
         meter.add(rt._layer, idx)
     if probe.enabled:
         probe.routing("routing", router_logits=logits, expert_scores=scores,

@@ -9,7 +9,8 @@ the kernels, the expert-to-rank rule or the checkpoint format: slot ``s`` still 
 is which expert sits in which slot.
 
 * ``ExpertLoadMeter`` counts, on the device and without a host synchronisation, the tokens each routed slot of each MoE
-  layer received (``route_tokens`` feeds it when ``Runtime.load_meter`` is set);
+  layer received (``route_tokens`` feeds it when ``Runtime.load_meter`` is set: in training forwards, or in every call when
+  the meter was started for serving);
 * ``plan_slots`` turns one layer's counts into a permutation of its routed slots: longest-processing-time assignment under
   the per-rank slot capacities (shared-expert slots stay where they are), rank labels chosen to keep as many experts as
   possible in place, refused unless the heaviest rank gets lighter by ``min_gain``;
@@ -36,16 +37,14 @@ class ExpertLoadMeter:
         self.layers = list(moe_layers)
         self._row = {layer: i for i, layer in enumerate(self.layers)}
         self.counts = torch.zeros(len(self.layers), n_routed, dtype=torch.int64, device=device)   # exact however long the window
-        self._ones: torch.Tensor | None = None
+        self.always = False                                   # False: training forwards only; True: inference calls too (serving)
 
     def add(self, layer: int, indices: torch.Tensor) -> None:
         row = self._row.get(layer)
         if row is None:
             return
         flat = indices.reshape(-1)
-        if self._ones is None or self._ones.numel() < flat.numel():
-            self._ones = torch.ones(flat.numel(), dtype=torch.int64, device=self.counts.device)
-        self.counts[row].index_add_(0, flat, self._ones[: flat.numel()])
+        self.counts[row].index_add_(0, flat, torch.ones_like(flat, dtype=torch.int64))   # no state of its own: safe inside a CUDA graph
 
     def reset(self) -> None:
         self.counts.zero_()
@@ -126,7 +125,11 @@ def _tensors_of(path: str, params: dict[str, torch.Tensor], opt: Any) -> list[to
     out = []
     for tree in (params, opt.muon_moment, opt.adam_mu, opt.adam_nu):
         t = tree.get(path)
-        if t is not None and t.numel() > 0:
+        if t is None:
+            continue
+        if not isinstance(t, torch.Tensor):
+            raise NotImplementedError(f"{path} is stored quantised: experts are re-placed before ModelWeights.quantize, not after")
+        if t.numel() > 0:
             out.append(t)
     return out
 

@@ -300,9 +300,10 @@ class Runtime:
         return path not in self.plan.replicated or self.rank == 0
 
     # ------------------------------------------------------------------ expert parallel MoE
-    def meter_expert_load(self) -> bool:
-        """Starts counting the tokens every routed expert slot receives (input of ``rebalance_experts``). Returns whether
-        there is anything to re-place (experts sharded over more than one rank)."""
+    def meter_expert_load(self, inference: bool = False) -> bool:
+        """Starts counting the tokens every routed expert slot receives (input of ``rebalance_experts``): in training forwards,
+        or with ``inference`` in every model call (a serving process). Returns whether there is anything to re-place (experts
+        sharded over more than one rank)."""
         if self.ep_size <= 1:
             return False
         if self.load_meter is None:
@@ -310,13 +311,16 @@ class Runtime:
 
             moe_layers = [i for i, kind in enumerate(self.mcfg.mlp_map) if kind == "moe"]
             self.load_meter = ExpertLoadMeter(moe_layers, self.mcfg.n_routed_experts, self.device)
+        self.load_meter.always = inference
         return True
 
-    def rebalance_experts(self, params: dict[str, torch.Tensor], optimizer_state, *, min_gain: float = 0.05) -> dict:
-        """Collective, between steps: moves experts (masters and moments) so that the ranks draw equal numbers of tokens."""
+    def rebalance_experts(self, params: dict[str, torch.Tensor], optimizer_state=None, *, min_gain: float = 0.05) -> dict:
+        """Collective, between steps: moves experts (masters and moments; parameters alone when serving) so that the ranks draw
+        equal numbers of tokens."""
         from lyra_b200.parallel.placement import rebalance_experts
+        from lyra_b200.training.optimizer import OptimizerState
 
-        return rebalance_experts(self, params, optimizer_state, min_gain=min_gain)
+        return rebalance_experts(self, params, optimizer_state if optimizer_state is not None else OptimizerState(), min_gain=min_gain)
 
     def ep_moe(self, xn, scores, indices, w, c: ModelConfig):
         from lyra_b200.parallel.ep import ep_moe_forward

@@ -121,6 +121,15 @@ def _serve_worker(rank, world, port, tmp):
         gen = BatchedGenerator(w, c, batch=2, capacity=16, device="cpu", rt=rt)
         toks = gen.decode(gen.prefill(prompts), 6)
         torch.save(toks, f"{tmp}/serve{rank}.pt")
+        # experts re-placed by the load of that request: the same request gives the same tokens afterwards
+        from lyra_b200.nn.params import tree_dict
+
+        assert rt.meter_expert_load(inference=True)
+        gen.decode(gen.prefill(prompts), 6)
+        report = rt.rebalance_experts(tree_dict(w), min_gain=0.0)
+        assert report["layers_moved"] >= 1 and report["max_share_after"] <= report["max_share_before"]
+        again = BatchedGenerator(w, c, batch=2, capacity=16, device="cpu", rt=rt)
+        assert torch.equal(again.decode(again.prefill(prompts), 6), toks)
     finally:
         dist.destroy_process_group()
 
