@@ -42,7 +42,8 @@ class Args:
     out: str | None = None
     """Checkpoint directory."""
     resume: str | None = None
-    """Checkpoint, or run directory, to resume from."""
+    """Checkpoint, or run directory, to resume from; `auto` continues from the newest checkpoint in --out if there is one and
+    starts a new run otherwise (the same command line then serves every restart of `torch.distributed.run --max-restarts`)."""
     eval_every: int | None = None
     """Validation interval in steps."""
     eval_batches: int | None = None
@@ -97,6 +98,11 @@ def training_config(args: Args):
     config = TRAINING_PRESETS[run]
     overrides = {field: getattr(args, flag) for flag, field in FIELDS.items() if getattr(args, flag) is not None}
     overrides |= {field: Path(getattr(args, flag)).expanduser() for flag, field in PATH_FIELDS.items() if getattr(args, flag) is not None}
+    if args.resume == "auto":
+        from lyra_b200.nn.checkpoints import checkpoint_steps
+
+        out = overrides.get("checkpoint_path", config.checkpoint_path)
+        overrides["resume_from"] = out if (out.is_dir() and checkpoint_steps(out)) else None
     if args.seed is not None:
         overrides["data_loader"] = replace(config.data_loader, seed=args.seed)
     return replace(config, **overrides)

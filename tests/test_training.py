@@ -193,3 +193,31 @@ def test_tiny_moe_twenty_steps_checkpoint_at_twenty_and_resume(tmp_path):
     assert any(not torch.equal(a[k], b[k]) for k in a)            # two more optimizer steps were taken
     rows = [json.loads(l) for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
     assert [r["step"] for r in rows][-1] == 22 and np.isfinite(rows[-1]["loss"])
+
+
+def test_resume_auto_restarts_an_interrupted_run_with_the_same_command_line(tmp_path):
+    """What a supervisor that restarts failed jobs needs (``torch.distributed.run --max-restarts``): the first launch starts a
+    run, a launch after a failure continues from the newest finished checkpoint, both with the same arguments."""
+    from scripts.train import Args, main, training_config
+
+    data = token_file(tmp_path / "tok.npy", n=40000, vocab=256)
+    argv = ["--variant", "dev", "--run", "train-dev", "--device", "cpu", "--implementation", "torch", "--steps", "4", "--batch-size", "2",
+            "--acc-steps", "1", "--data", str(data), "--out", str(tmp_path / "run"), "--chkpt-every", "2", "--resume", "auto"]
+    args = Args(variant="dev", run="train-dev", steps=4, batch_size=2, acc_steps=1, data=str(data), out=str(tmp_path / "run"), chkpt_every=2, resume="auto")
+    first = training_config(args)
+    assert first.resume_from is None                               # nothing there yet: a new run
+
+    class FailAtThree(TrainHooks):
+        def before_step(self, step, *a):
+            if step == 3:
+                raise RuntimeError("lost a peer")
+
+    from lyra_b200.variants import model_variant
+
+    c = replace(model_variant("dev"), implementation="torch")
+    with pytest.raises(RuntimeError, match="lost a peer"):
+        train(ModelWeights.init(c.seed, c), c, first, device="cpu", hooks=FailAtThree())
+    assert training_config(args).resume_from == tmp_path / "run"    # the restart finds the step-2 checkpoint
+    assert main(argv) == 0
+    rows = [json.loads(l) for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
+    assert [p.name for p in checkpoint_steps(tmp_path / "run")][-1] == "step_00000004" and rows[-1]["step"] == 4
