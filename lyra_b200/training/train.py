@@ -306,6 +306,11 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
                 if sampling:
                     sample(step)
     finally:
+        if heartbeat is not None:   # finished or failed: tell the others now, so that none of them waits out its time limit
+            try:
+                heartbeat.leave()
+            except Exception:
+                pass
         metrics.close()
         loader.close()
         if eval_loader is not None:
