@@ -3,6 +3,7 @@ logs, evaluation, sampling, checkpoints, hooks."""
 
 from __future__ import annotations
 
+import itertools
 import json
 import math
 import shutil
@@ -39,6 +40,9 @@ RUN_ARTIFACTS = ("metrics.jsonl", "samples.jsonl", "numerics.jsonl")
 MODEL_FIELDS_IGNORED_ON_RESUME = ("w_init", "b_init", "norm_init", "mode", "sample_topk", "sample_temperature", "quantize_cache",
                                   "implementation", "sharding")
 SCHEDULE_FIELDS = ("steps", "batch_size", "accumulation_steps", "decay_type", "warmup_fraction", "stable_fraction")
+
+
+_RUN_COUNTER = itertools.count()
 
 
 @dataclass(frozen=True, kw_only=True)
@@ -256,7 +260,8 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
 
         from lyra_b200.parallel.health import Heartbeat
 
-        heartbeat = Heartbeat(_get_default_store(), rt.rank, rt.world)
+        # one key space per call of train() in this process group: the farewell of an earlier run must not read as a lost peer
+        heartbeat = Heartbeat(_get_default_store(), rt.rank, rt.world, prefix=f"lyra/hb/{next(_RUN_COUNTER)}")
 
     rebalancing = tcfg.rebalance_experts_every is not None and rt is not None and rt.meter_expert_load()
 
