@@ -179,38 +179,8 @@ def _tp_worker(rank, world, port, tmp):
 def _randomise_zero_init(w):
     """Biases, sinks, gates and XSA strengths start at zero; give them values so that their sharding is exercised. Every rank
     derives the same full tensor from the leaf's path and takes its own slice, like the initialiser does."""
-    import zlib
-
-    from lyra_b200.nn.params import tree_dict
-
-    for path, t in tree_dict(w).items():
-        name = path.split("/")[-1]
-        if name.endswith("_bias") or name in ("sinks", "xsa_alpha", "sdpa_gate"):
-            t.data = t.data + _full_noise(path, name, t)
-
-
-def _full_noise(path, name, t):
-    import zlib
-
-    g = torch.Generator().manual_seed(zlib.crc32(path.encode()))
-    full_shape = list(t.shape)
     rank, world = (dist.get_rank(), dist.get_world_size()) if dist.is_initialized() else (0, 1)
-    from lyra_b200.parallel.tp import _COLUMNS, _ROWS, _VECTORS
-
-    dim = None
-    if name in _COLUMNS:
-        dim = 1
-    elif name in _ROWS or name in _VECTORS:
-        dim = 0
-    elif name == "mlp_up_bias":
-        dim = t.ndim - 1
-    if dim is not None and world > 1:
-        full_shape[dim] *= world
-    full = torch.randn(full_shape, generator=g) * 0.1
-    if dim is not None and world > 1:
-        n = full.shape[dim] // world
-        full = full.narrow(dim, rank * n, n)
-    return full.to(t.dtype)
+    _randomise_zero_init_on(w, rank, world)
 
 
 def test_tensor_parallel_inference_matches_single_process(tmp_path):
@@ -438,7 +408,7 @@ def _mesh_worker(rank, world, port, tmp):
 
 
 def _randomise_zero_init_on(w, tp_rank, tp_size):
-    """``_randomise_zero_init`` for a rank whose index on the model axis differs from its global rank."""
+    """``_randomise_zero_init`` for a given index on a model axis of ``tp_size`` ranks (which may differ from the global rank)."""
     import zlib
 
     from lyra_b200.nn.params import tree_dict
