@@ -465,3 +465,45 @@ def test_data_by_model_mesh_training_matches_single_process(tmp_path):
     ck = tmp_path / "meshckpt" / "step_00000002" / "params"
     for p in ("layers/1/attn/q", "layers/1/mlp/mlp_up", "tok/emb"):
         assert torch.allclose(load_leaf(ck, p, ShardInfo()), ref[p], atol=3e-5), p
+
+
+def _tp_scorer_worker(rank, world, port, tmp):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from lyra_b200.evals import Scorer
+        from lyra_b200.evals.common import Doc
+        from lyra_b200.model import ModelWeights
+        from lyra_b200.parallel.tp import TensorParallel
+
+        c = _scorer_cfg()
+        tp = TensorParallel(c, rank, world)
+        scorer = Scorer(ModelWeights.init(0, c, shard_fn=tp.shard_info), c, batch_size=4, rt=tp)
+        torch.save(scorer.score(_scorer_docs(Doc)), f"{tmp}/scores{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+def _scorer_cfg():
+    from tests.helpers import small_config
+
+    return small_config(vocab_size=201088, padded_vocab_size=204800, n_layers=2, mlp_map=("dense", "moe"), seq_len=64, n_attn_heads=4, n_kv_heads=2,
+                        n_embd=64, head_dim=16, compute_dtype=torch.float32)
+
+
+def _scorer_docs(Doc):
+    return [Doc("Question: 1+1?\nAnswer:", ("2", "3", "4"), 0, True), Doc("Question: sky?\nAnswer:", ("blue", "green"), 0, True)]
+
+
+def test_tensor_parallel_scoring_matches_single_process(tmp_path):
+    """The loglikelihood harness on a model split over two ranks gives the single-process continuation scores on both ranks."""
+    from lyra_b200.evals import Scorer
+    from lyra_b200.evals.common import Doc
+    from lyra_b200.model import ModelWeights
+
+    c = _scorer_cfg()
+    want = Scorer(ModelWeights.init(0, c), c, batch_size=4).score(_scorer_docs(Doc))
+    mp.spawn(_tp_scorer_worker, args=(2, free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        got = torch.load(tmp_path / f"scores{r}.pt", weights_only=False)
+        assert all(np.allclose(a, b, atol=1e-4) for a, b in zip(got, want)), (got, want)
