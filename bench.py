@@ -43,6 +43,8 @@ def parse_args():
     ap.add_argument("--variant", default="lyra-medium")
     ap.add_argument("--micro-batch", type=int, default=2)
     ap.add_argument("--accumulation", type=int, default=None)
+    ap.add_argument("--rebalance-experts", action="store_true",
+                    help="several GPUs: meter the experts' token counts during warm-up, re-place the experts on the ranks once (untimed), keep metering in the timed steps")
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (the result is then labelled invalid)")
     return ap.parse_args()
 
@@ -186,9 +188,15 @@ def main() -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    placement = None
+    metering = args.rebalance_experts and rt is not None and rt.meter_expert_load()
     step_idx = 0
     for _ in range(args.warmup):
         stepper.train_step(dev_x[step_idx % len(dev_x)], dev_y[step_idx % len(dev_y)], step_idx)
+        step_idx += 1
+    if metering:   # what the training loop does every --rebalance-experts-every steps
+        placement = {k: round(float(v), 4) for k, v in rt.rebalance_experts(stepper.params, state.optimizer).items()}
+        stepper.train_step(dev_x[step_idx % len(dev_x)], dev_y[step_idx % len(dev_y)], step_idx)   # one untimed step on the new placement
         step_idx += 1
     barrier()
     native.check_status()
@@ -248,7 +256,7 @@ def main() -> None:
                        "accumulation_steps": acc, "parallelism": ("single" if world == 1 else f"fsdp+ep{world}"),
                        "optimizer": "muon+adam in timed region", "l2": "per-step working set (weights, activations) far exceeds the 126 MB L2",
                        "grad_dtype": str(cuda_ops.GRAD_DTYPE).replace("torch.", ""), "bf16_weight_copies": cuda_ops.KEEP_SHADOWS,
-                       "params": n_params, "valid": valid},
+                       "params": n_params, "valid": valid, **({"expert_placement": placement} if placement is not None else {})},
             "mfu_of_measured_sustained_bf16": round(value * fpt / world / (peak * 1e12), 4),
             "flops_per_token": fpt, "loss": round(loss, 4),
             "clocks": clocks.summary(),
