@@ -331,7 +331,7 @@ def _gpt_oss_cfg(**kw):
                        implementation="torch", **kw)
 
 
-def _chat(model, c, rt=None, **io):
+def _chat(model, c, rt=None, fp8=False):
     from lyra_b200.generate import InferenceConfig, serve_model
 
     prompts = iter(["hello there", "and again", "exit"])
@@ -341,7 +341,7 @@ def _chat(model, c, rt=None, **io):
         from lyra_b200.parallel.tp import shared_terminal
 
         terminal = shared_terminal(rt, **terminal)
-    serve_model(model, c, InferenceConfig(weights="x", max_new_tokens=6, max_cache_length=32), device="cpu", rt=rt, **terminal)
+    serve_model(model, c, InferenceConfig(weights="x", max_new_tokens=6, max_cache_length=32, fp8=fp8), device="cpu", rt=rt, **terminal)
     return printed
 
 
@@ -358,6 +358,12 @@ def _tp_chat_worker(rank, world, port, tmp):
             model = load_gpt_oss_model(tmp + "/ckpt", c, shard_fn=tp.shard_info)
             assert model.layers[0].attn.q.shape[1] == c.n_attn_heads * c.head_dim // world
             out[name] = _chat(model, c, tp)
+        # block-scaled e4m3 expert weights and KV cache on top of the split: every rank quantises its own slice
+        from lyra_b200.generate import InferenceConfig, apply_inference_overrides
+
+        c8 = apply_inference_overrides(_gpt_oss_cfg(sample_temperature=0.0, quant_block=(16, 16)), InferenceConfig(weights="x", fp8=True))
+        tp = TensorParallel(c8, rank, world)
+        out["fp8"] = _chat(load_gpt_oss_model(tmp + "/ckpt", c8, shard_fn=tp.shard_info), c8, tp, fp8=True)
         torch.save(out, f"{tmp}/chat{rank}.pt")
     finally:
         dist.destroy_process_group()
@@ -376,6 +382,7 @@ def test_tensor_parallel_chat_from_a_gpt_oss_checkpoint(tmp_path):
     assert rank0["greedy"] == want and len("".join(want)) > len("Type a prompt")
     assert rank1["greedy"] == [] and rank1["sampled"] == []            # the other rank prints nothing
     assert len(rank0["sampled"]) == len(want)                          # both turns ran with rank 0's sampled tokens fed to both ranks
+    assert len(rank0["fp8"]) >= 4 and rank1["fp8"] == []               # the quantised model answered both turns
 
 
 def _mesh_worker(rank, world, port, tmp):
