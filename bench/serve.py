@@ -104,7 +104,7 @@ def main() -> None:
     served = 1 if tp else world                              # batches served by the job
 
     placement = None
-    if args.rebalance and world > 1 and not tp and not args.fp8:
+    if args.rebalance and world > 1 and not tp:
         from lyra_b200.nn.params import tree_dict
 
         rt.meter_expert_load(inference=True)

@@ -427,6 +427,9 @@ class DenseMLPWeights:
         if not c.quantize_mlp:
             return w
         up, down = w.mlp_up, w.mlp_down
+        if not isinstance(up, QArray) and up.numel() == 0:
+            raise ValueError("this rank holds only a placeholder of a dense MLP leaf (another rank owns it): quantised serving under the "
+                             "leaf-ownership runtime needs a model whose MLPs are all mixtures of experts, or tensor parallelism")
         if not isinstance(up, QArray):
             k, n = c.quant_block
             up = quantize(up, c.gemm_dtype, (math.gcd(up.shape[-3], k), 1, math.gcd(up.shape[-1], n)))

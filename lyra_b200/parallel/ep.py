@@ -22,7 +22,7 @@ from lyra_b200.config import ModelConfig
 from lyra_b200.ops import api as ops
 from lyra_b200.ops import reference as ref
 
-from lyra_b200.nn.quant import QArray
+from lyra_b200.nn.quant import QArray, dequantize
 
 BF16 = torch.bfloat16
 EP_DECODE_MAX_ROWS = 512   # assignments per rank up to which an inference exchange uses the weight-streaming small-M products
@@ -125,10 +125,15 @@ def _ep_moe_collectives(rt, xn, scores, indices, w, c: ModelConfig):
     perm = torch.argsort(exp_id * W + src_id, stable=True)
     grouped = recv[perm]
     groups = recv_counts.sum(0)
-    C, H = w.mlp_up.shape[1], w.mlp_up.shape[3]
-    t = ref.grouped_gemm_autograd(grouped, w.mlp_up.reshape(El, C, 2 * H), groups, None if w.mlp_up_bias is None else w.mlp_up_bias.reshape(El, 2 * H))
+    up, down = w.mlp_up, w.mlp_down
+    if isinstance(up, QArray):                                   # block-scaled e4m3 experts (inference): this mode dequantises them
+        up = dequantize(up, xn.dtype).reshape(El, xn.shape[-1], 2, -1)
+    if isinstance(down, QArray):
+        down = dequantize(down, xn.dtype)
+    C, H = up.shape[1], up.shape[3]
+    t = ref.grouped_gemm_autograd(grouped, up.reshape(El, C, 2 * H), groups, None if w.mlp_up_bias is None else w.mlp_up_bias.reshape(El, 2 * H))
     t = ref.swiglu(t.reshape(-1, 2, H), c.swiglu_beta, c.swiglu_limit).to(xn.dtype)
-    t = ref.grouped_gemm_autograd(t, w.mlp_down, groups, w.mlp_down_bias)
+    t = ref.grouped_gemm_autograd(t, down, groups, w.mlp_down_bias)
     inv = torch.empty_like(perm)
     inv[perm] = torch.arange(perm.numel(), device=perm.device)
     back = _AllToAll.apply(t[inv], recv_splits, send_splits, rt.group)      # rows in `order` order

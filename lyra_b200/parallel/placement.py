@@ -127,9 +127,9 @@ def _tensors_of(path: str, params: dict[str, torch.Tensor], opt: Any) -> list[to
         t = tree.get(path)
         if t is None:
             continue
-        if not isinstance(t, torch.Tensor):
-            raise NotImplementedError(f"{path} is stored quantised: experts are re-placed before ModelWeights.quantize, not after")
-        if t.numel() > 0:
+        if not isinstance(t, torch.Tensor):               # block-quantised stack: values and scales both lead with the expert axis
+            out.extend([t.qval, t.scale])
+        elif t.numel() > 0:
             out.append(t)
     return out
 

@@ -246,7 +246,10 @@ class Runtime:
         return p
 
     def shared_expert_weights(self, up_leaf: torch.Tensor, down_leaf: torch.Tensor, j: int = 0):
-        up_path, down_path = self._path_of[id(up_leaf)], self._path_of[id(down_leaf)]
+        # leaves that were replaced after registration (ModelWeights.quantize) are found by the layer being applied; the shared
+        # expert then runs from the bf16 copies of the registered masters
+        up_path = self._path_of.get(id(up_leaf), f"layers/{self._layer}/mlp/mlp_up")
+        down_path = self._path_of.get(id(down_leaf), f"layers/{self._layer}/mlp/mlp_down")
         return self._views[f"{up_path}#shared{j}"], self._views[f"{down_path}#shared{j}"]
 
     def tp_all_reduce(self, t):
