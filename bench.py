@@ -141,7 +141,12 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    impl = {"b200": "auto", "torch": "torch", "nccl": "nccl"}[args.impl]
+    # b200  : the product - own kernels for compute, own peer-memory kernels for every multi-GPU data path
+    # nccl  : stand-in for a library-collective build, NOT the reference: the same compute kernels, but weights, gradients and
+    #         expert tokens move through torch.distributed (NCCL) broadcast / reduce / all_to_all as in lyra/training/steps.py:75-91
+    #         and lyra/kernels/ep_moe.py:130-149
+    # torch : PyTorch library ops (cuBLAS, eager attention) for compute and NCCL for communication
+    impl = {"b200": "auto", "torch": "torch", "nccl": "auto"}[args.impl]
     mcfg = replace(model_variant(args.variant), implementation=impl)
     valid = True
     if args.layers is not None:
@@ -170,6 +175,16 @@ def main() -> None:
     tight = local_params * 14 > 150e9
     cuda_ops.set_memory_mode(keep_shadows=not tight, grad_dtype=torch.bfloat16 if tight else torch.float32, save_preact=not tight)
 
+    if args.impl == "torch":
+        # eager attention keeps [heads, T, T] fp32 scores of every layer for backward: this does not fit for the 4096-token variants
+        est = mcfg.n_layers * mcfg.n_attn_heads * B * T * T * 4 * 2 + local_params * 12
+        if est > 170e9:
+            if rank == 0:
+                print(json.dumps({"impl": "torch", "unavailable": f"PyTorch eager path needs about {est / 1e9:.0f} GB per GPU for {args.variant} at "
+                                  f"{B}x{T} tokens (attention scores of all layers are kept for backward)"}))
+            if world > 1:
+                dist.destroy_process_group()
+            return
     shard_fn = rt.shard_info if rt is not None else None
     weights = ModelWeights.init(mcfg.seed, mcfg, device=device, shard_fn=shard_fn)
     state = init_train_state(weights, mcfg, tcfg)
@@ -233,10 +248,29 @@ def main() -> None:
     ms_e2e = t0.elapsed_time(t1)
     native.check_status()
 
-    times = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=device)
+    # ---- one more untimed step with CUDA events around the phases of a step (device time, max over ranks)
+    from lyra_b200.utils.phases import collect
+
+    names = ["forward_backward", "ep_wait", "gradient_reduce", "optimizer", "weight_refresh", "step"]
+    barrier()
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with collect() as spans:
+        p0.record()
+        stepper.train_step(dev_x[step_idx % len(dev_x)], dev_y[step_idx % len(dev_y)], step_idx)
+        p1.record()
+        sums = spans.totals_ms()
+    sums["step"] = p0.elapsed_time(p1)
+    step_idx += 1
+    native.check_status()
+
+    times = torch.tensor([ms, ms_e2e] + [sums.get(n, 0.0) for n in names], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     ms, ms_e2e = float(times[0]), float(times[1])
+    phases = {n: round(float(v), 1) for n, v in zip(names, times[2:])}
+    phases["note"] = ("ms of one extra step, CUDA events, max over ranks per phase; ep_wait (flag and arrival-counter wait kernels of the expert "
+                      "exchange) lies inside forward_backward; tile waits inside the grouped GEMMs are not separable; step - (forward_backward + "
+                      "gradient_reduce + optimizer + weight_refresh) is host gaps")
 
     tokens_per_step = acc * B * T * world
     value = tokens_per_step * args.steps / (ms / 1e3)
@@ -262,6 +296,7 @@ def main() -> None:
             "clocks": clocks.summary(),
             "e2e": {"value": round(value_e2e, 1), "unit": "tokens/s", "h2d_bytes_per_step": stepper.h2d_bytes // max(args.steps, 1),
                     "d2h_bytes_per_step": d2h // max(args.steps, 1), "ms_per_step": round(ms_e2e / args.steps, 2), "loss": round(loss_e2e, 4)},
+            "phases": phases,
             "gpu_launches": launches,
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
             "baseline_note": "the reference's only published end-to-end figure is lyra-small, 34,150 tok/s on one TPU v6e (README.md:33); vs_baseline is that ratio for --variant lyra-small and null for variants without a published number",

@@ -9,6 +9,11 @@
 //   ep_*          : expert-parallel token exchange - counts push, layout, row dispatch into the owner's expert-sorted
 //                   receive buffer, and the return of expert outputs to the source rank's combine buffer
 //                   (roles of lyra/kernels/ep_moe.py:9-37,94-127 in the reference)
+//   ep_*_sorted / arrivals : the tile-granular form of the exchange. Senders walk their assignments in the order in which
+//                   the receivers will consume them (destination rank by destination rank, starting with themselves) and
+//                   bump one arrival counter per 128-row tile of the receiver's buffer; the receiver's grouped GEMM waits
+//                   for a tile's counter inside its TMA producer (csrc/gemm/gemm.cu) instead of behind an all-rank barrier.
+//                   Counters only ever grow: the receiver keeps the running total it expects per tile, so nothing is reset.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -187,13 +192,15 @@ __global__ void ep_layout_kernel(const int* __restrict__ counts, int world, int 
       for (int j = 0; j < e_local; ++j) {
         const int e = d * e_local + j;
         base[e] = off;
-        if (d == my_rank) recv_offsets[j] = off;
+        if (d == my_rank) recv_offsets[j] = off < cap_rows ? off : cap_rows;
         off += (total[e] + 127) / 128 * 128;
       }
+      // Too small a buffer is reported, never written past: senders drop rows beyond the capacity and every offset that later
+      // kernels index with is clamped to it, so the step's numbers are wrong but no access leaves the buffers.
       if (off > cap_rows) atomicExch(status, STATUS_EP_OVERFLOW);
       if (d == my_rank) {
-        recv_offsets[e_local] = off;
-        *recv_total = off;
+        recv_offsets[e_local] = off < cap_rows ? off : cap_rows;
+        *recv_total = off < cap_rows ? off : cap_rows;
       }
     }
   }
@@ -279,6 +286,178 @@ __global__ void ep_zero_pad_kernel(__nv_bfloat16* __restrict__ rows, const int* 
   if (row - recv_offsets[j] < valid) return;
   uint4* o = reinterpret_cast<uint4*>(rows + (long long)row * C);
   for (int c = threadIdx.x; c < C / 8; c += blockDim.x) o[c] = make_uint4(0, 0, 0, 0);
+}
+
+// ------------------------------------------------------------------------------------------------ tile-granular exchange
+// Block-wide exclusive scan of one 0/1 flag per thread (blockDim.x <= 1024); returns this thread's rank among the set
+// flags and, through `total`, their number. `warp_sums` is 32 ints of shared memory.
+__device__ __forceinline__ int block_rank_of_flag(bool flag, int* warp_sums, int& total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+  const int in_warp = __popc(ballot & ((1u << lane) - 1u));
+  if (lane == 0) warp_sums[warp] = __popc(ballot);
+  __syncthreads();
+  int before = 0, all = 0;
+  for (int w = 0; w < n_warps; ++w) {
+    const int c = warp_sums[w];
+    if (w < warp) before += c;
+    all += c;
+  }
+  __syncthreads();
+  total = all;
+  return before + in_warp;
+}
+
+// Layout of one exchange, one block. Everything `ep_layout_kernel` computes, plus what the tile-granular path needs:
+//   starts[E + 1]      : exclusive prefix of this rank's own per-expert counts (position of expert e's run in the sender's
+//                        expert-sorted assignment list); starts[E] = number of assignments
+//   send_rot           : starts[my_rank * e_local] - the sorted position where this rank's own experts begin. A sender walks
+//                        its sorted list cyclically from there, i.e. destination my_rank first, then my_rank + 1, ...
+//   tile_valid[t]      : real (non-padding) rows in 128-row tile t of the receive buffer, 0 for unused tiles
+//   tile_perm[i]       : the used tiles in the order in which they complete under that sending order: by the step
+//                        (my_rank - source) mod world of the last source that contributes rows to the tile, then by row;
+//                        -1 after the last used tile. The grouped GEMM enumerates its row tiles through this list.
+__global__ void ep_layout_tiles_kernel(const int* __restrict__ counts, int world, int my_rank, int n_experts, int e_local, int cap_rows,
+                                       int* __restrict__ send_base, int* __restrict__ recv_offsets, int* __restrict__ tile_group,
+                                       int* __restrict__ recv_total, int* __restrict__ starts, int* __restrict__ send_rot,
+                                       int* __restrict__ tile_valid, int* __restrict__ tile_perm, int* status) {
+  extern __shared__ int sh[];  // totals [E], padded bases [E], warp sums [32], step of each tile [cap_rows / 128]
+  int* total = sh;
+  int* base = sh + n_experts;
+  int* warp_sums = base + n_experts;
+  int* step_of = warp_sums + 32;
+  __shared__ int filled;
+  const int n_tiles = cap_rows / 128;
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int t = 0;
+    for (int s = 0; s < world; ++s) t += counts[s * n_experts + e];
+    total[e] = t;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int d = 0; d < world; ++d) {
+      int off = 0;
+      for (int j = 0; j < e_local; ++j) {
+        const int e = d * e_local + j;
+        base[e] = off;
+        if (d == my_rank) recv_offsets[j] = off < cap_rows ? off : cap_rows;
+        off += (total[e] + 127) / 128 * 128;
+      }
+      // Too small a buffer is reported, never written past: senders drop rows beyond the capacity and every offset that later
+      // kernels index with is clamped to it, so the step's numbers are wrong but no access leaves the buffers.
+      if (off > cap_rows) atomicExch(status, STATUS_EP_OVERFLOW);
+      if (d == my_rank) {
+        recv_offsets[e_local] = off < cap_rows ? off : cap_rows;
+        *recv_total = off < cap_rows ? off : cap_rows;
+      }
+    }
+    int run = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      starts[e] = run;
+      run += counts[my_rank * n_experts + e];
+    }
+    starts[n_experts] = run;
+    *send_rot = starts[my_rank * e_local];
+    filled = 0;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    int before = 0;
+    for (int s = 0; s < my_rank; ++s) before += counts[s * n_experts + e];
+    send_base[e] = base[e] + before;
+  }
+  const int used = recv_offsets[e_local] < cap_rows ? recv_offsets[e_local] : cap_rows;
+  for (int t = threadIdx.x; t < n_tiles; t += blockDim.x) {
+    const int row = t * 128;
+    int g = -1, valid = 0, step = -1;
+    if (row < used) {
+      for (int j = 0; j < e_local; ++j)
+        if (row >= recv_offsets[j] && row < recv_offsets[j + 1]) g = j;
+    }
+    if (g >= 0) {
+      const int e = my_rank * e_local + g;
+      const int r0 = row - recv_offsets[g];
+      const int r1 = min(r0 + 128, total[e]);
+      valid = max(r1 - r0, 0);
+      int lo = 0;                               // rows of sources before s in this expert
+      for (int s = 0; s < world; ++s) {
+        const int c = counts[s * n_experts + e];
+        if (c > 0 && lo < r1 && lo + c > r0) step = max(step, (my_rank - s + world) % world);
+        lo += c;
+      }
+    }
+    tile_group[t] = g;
+    tile_valid[t] = valid;
+    step_of[t] = valid > 0 ? step : -1;
+  }
+  __syncthreads();
+  for (int k = 0; k < world; ++k) {
+    for (int t0 = 0; t0 < n_tiles; t0 += blockDim.x) {
+      const int t = t0 + threadIdx.x;
+      const bool mine = t < n_tiles && step_of[t] == k;
+      int n_set;
+      const int pos = block_rank_of_flag(mine, warp_sums, n_set);
+      if (mine) tile_perm[filled + pos] = t;
+      __syncthreads();
+      if (threadIdx.x == 0) filled += n_set;
+      __syncthreads();
+    }
+  }
+  for (int i = filled + threadIdx.x; i < n_tiles; i += blockDim.x) tile_perm[i] = -1;
+}
+
+// expect[t] += tile_valid[t]: the receiver's running total of rows that must have arrived in tile t once the dispatch that is
+// about to start has landed. Wrap-around is harmless (waits compare differences).
+__global__ void ep_expect_bump_kernel(int* __restrict__ expect, const int* __restrict__ tile_valid, int n_tiles) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t < n_tiles) expect[t] += tile_valid[t];
+}
+
+// One block per assignment, taken in the sender's cyclic expert-sorted order (see ep_layout_tiles_kernel): copies the source
+// row into the owner's receive buffer, records (rank, slot) and optionally the routing score beside it, then adds one to the
+// arrival counter of the row's 128-row tile on the owner (release at system scope: the row is visible before the count).
+__global__ void ep_dispatch_sorted_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ order, const int* __restrict__ expert_of,
+                                          const int* __restrict__ starts, const int* __restrict__ send_base, const int* __restrict__ send_rot,
+                                          const float* __restrict__ scores, PeerPtrs recv_bufs, PeerPtrs recv_meta, PeerPtrs recv_score,
+                                          PeerPtrs arrive, int my_rank, int e_local, int cap_rows, int n_assign, int src_div, int C) {
+  int j = blockIdx.x + *send_rot;
+  if (j >= n_assign) j -= n_assign;
+  if (j < 0 || j >= n_assign) return;
+  const int a = order[j];
+  const int e = expert_of[a];
+  const int d = e / e_local;
+  const int row = send_base[e] + (j - starts[e]);
+  if (row >= cap_rows) return;  // overflow was flagged by the layout kernel
+  const uint4* s = reinterpret_cast<const uint4*>(src + (long long)(a / src_div) * C);
+  uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recv_bufs.p[d]) + (long long)row * C);
+  for (int c = threadIdx.x; c < C / 8; c += blockDim.x) o[c] = s[c];
+  if (threadIdx.x == 0) {
+    if (recv_meta.p[d]) reinterpret_cast<int*>(recv_meta.p[d])[row] = (my_rank << 24) | a;
+    if (scores && recv_score.p[d]) reinterpret_cast<float*>(recv_score.p[d])[row] = scores[a];
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    asm volatile("red.release.sys.global.add.s32 [%0], 1;" ::"l"(reinterpret_cast<int*>(arrive.p[d]) + row / 128) : "memory");
+  }
+}
+
+// Stream-ordered wait for rows that other ranks store into a buffer of this rank: *expect += add (this rank's running total,
+// kept on the device so that a replayed CUDA graph advances it), then spin until the arrival counter that the storing kernels
+// bump has caught up. Bounded like every wait here.
+__global__ void wait_arrivals_kernel(const int* __restrict__ arrived, int* __restrict__ expect, int add, int* status, long long limit_ns) {
+  if (threadIdx.x != 0) return;
+  const int want = *expect + add;
+  *expect = want;
+  const long long start = now_ns();
+  while (ld_acquire_sys(arrived) - want < 0) {
+    if (*reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier kernel already failed (e.g. rows dropped on overflow): do not wait for them
+    if (now_ns() - start > limit_ns) {
+      atomicCAS(status, 0, STATUS_PEER_TIMEOUT);
+      return;
+    }
+    __nanosleep(200);
+  }
 }
 
 static PeerPtrs make_ptrs(const long long* ptrs, int world) {
@@ -408,6 +587,53 @@ extern "C" int lyra_ep_zero_pad(void* rows, const int* recv_offsets, const int* 
                                 int cap_rows, int C, void* stream) {
   ep_zero_pad_kernel<<<cap_rows, 128, 0, ST(stream)>>>(reinterpret_cast<__nv_bfloat16*>(rows), recv_offsets, counts, world, my_rank, n_experts,
                                                        e_local, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_layout_tiles(const int* counts, int world, int my_rank, int n_experts, int e_local, int cap_rows, int* send_base,
+                                    int* recv_offsets, int* tile_group, int* recv_total, int* starts, int* send_rot, int* tile_valid,
+                                    int* tile_perm, int* status, void* stream) {
+  if (world > MAX_RANKS || cap_rows % 128) return -53;
+  const size_t smem = (2 * (size_t)n_experts + 32 + cap_rows / 128) * sizeof(int);
+  if (smem > 200 * 1024) return -54;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(ep_layout_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) return -4;
+    configured = true;
+  }
+  ep_layout_tiles_kernel<<<1, 1024, smem, ST(stream)>>>(counts, world, my_rank, n_experts, e_local, cap_rows, send_base, recv_offsets, tile_group,
+                                                          recv_total, starts, send_rot, tile_valid, tile_perm, status);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_expect_bump(int* expect, const int* tile_valid, int n_tiles, void* stream) {
+  if (n_tiles <= 0) return 0;
+  ep_expect_bump_kernel<<<(n_tiles + 255) / 256, 256, 0, ST(stream)>>>(expect, tile_valid, n_tiles);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_ep_dispatch_sorted(const void* src, const int* order, const int* expert_of, const int* starts, const int* send_base,
+                                       const int* send_rot, const float* scores, const long long* recv_bufs, const long long* recv_meta,
+                                       const long long* recv_score, const long long* arrive, int world, int my_rank, int e_local, int cap_rows,
+                                       int n_assign, int src_div, int C, void* stream) {
+  if (n_assign <= 0) return 0;
+  if (C % 8 || world > MAX_RANKS || !arrive) return -52;
+  const PeerPtrs none = make_ptrs(recv_bufs, 0);
+  ep_dispatch_sorted_kernel<<<n_assign, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(src), order, expert_of, starts, send_base, send_rot,
+                                                              scores, make_ptrs(recv_bufs, world), recv_meta ? make_ptrs(recv_meta, world) : none,
+                                                              recv_score ? make_ptrs(recv_score, world) : none, make_ptrs(arrive, world), my_rank,
+                                                              e_local, cap_rows, n_assign, src_div, C);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+extern "C" int lyra_wait_arrivals(const int* arrived, int* expect, int add, int* status, int limit_ms, void* stream) {
+  long long ns = (long long)limit_ms * 1000000LL;
+  if (ns <= 0 || ns > PEER_WAIT_NS) ns = PEER_WAIT_NS;
+  wait_arrivals_kernel<<<1, 32, 0, ST(stream)>>>(arrived, expect, add, status, ns);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

@@ -13,10 +13,23 @@
 // by further CTAs along grid.z). fp32 partials go to a scratch buffer; a finishing kernel sums the K splits, adds the
 // bias and applies the clamped SwiGLU.
 
+//
+// Block-scaled e4m3 on the tensor cores (`decode_gemm_f8_kernel`, role of the quantised paths of lyra/kernels/decode_gemm.py:234-244
+// and lyra/kernels/gemm.py:557-589): tcgen05 tiles need 128 rows, which a decode step's tokens cannot fill - but the weights
+// can. The operand roles are swapped: the accumulator tile is D^T[128 weight columns x NTOK tokens] = W^T x^T, with the
+// e4m3 weight panel as the 128-row A operand (TMA, [K, N] storage = MN-major) and the tokens, quantised to e4m3 with one
+// scale per (row, K block) like the reference's `quantize(lhs, (1, scale_k))`, as the narrow B operand. Scales are applied
+// in software: every K block of `bk` values accumulates into one of two TMEM accumulators (kind::f8f6f4, fp32), the four
+// epilogue warps read it back (tcgen05.ld), multiply by w_scale[k block, column block] * x_scale[token, k block] and add
+// into fp32 registers while the tensor core already works on the next K block in the other accumulator.
+
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include "../common/sm100.cuh"
+#include "../common/tmap.h"
 
 namespace {
 
@@ -245,6 +258,207 @@ int launch_tn(const DGParams& p, int tn, cudaStream_t stream) {
   return launch<FP8, 64>(p, stream);
 }
 
+
+// ------------------------------------------------------------------------------------------------ e4m3 x e4m3 on tcgen05
+constexpr int F8_KSTAGE = 128;               // K values per shared-memory stage: 128 rows of 128 weight bytes, 128 bytes per token row
+constexpr int F8_THREADS = 192;              // warp 0: TMA, warp 1: MMA issue + TMEM, warps 2..5: scale-and-accumulate
+constexpr int F8_MAX_KBLOCKS = 64;           // K blocks (scale rows) one CTA can hold
+
+constexpr int f8_stages(int ntok) { return ntok >= 64 ? 3 : 4; }   // sized so that two CTAs fit one SM (two weight streams in flight)
+
+struct F8Params {
+  const float* xs;          // [R, K / bk] activation scales
+  const float* ws;          // [G, K / bk, N / bn] weight scales
+  const int* offsets;
+  const int* counts;
+  float* part;              // [splits, R, N]
+  int R, K, N, G, splits, k_per_split, bk, bn, zblocks;
+  int* status;
+};
+
+template <int NTOK>
+__global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
+                                                                   const F8Params p) {
+  using namespace lyra;
+  constexpr int A_BYTES = F8_KSTAGE * 128;                 // 128 k rows x 128 weight columns (one byte each)
+  constexpr int B_BYTES = NTOK * 128;                      // NTOK token rows x 128 k values
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int F8_STAGES = f8_stages(NTOK);
+  constexpr uint32_t TMEM_COLS = 2 * NTOK < 32 ? 32 : 2 * NTOK;
+  constexpr uint32_t IDESC = make_idesc(128, NTOK, 0, 0, 1, 0);   // e4m3 x e4m3, A (weights) MN-major, B (tokens) K-major
+
+  const int n0 = blockIdx.x * 128, g = blockIdx.y;
+  const int split = blockIdx.z % p.splits, zb = blockIdx.z / p.splits;
+  const int gbeg = p.offsets ? p.offsets[g] : 0;
+  const int gend = p.offsets ? (p.counts ? gbeg + p.counts[g] : p.offsets[g + 1]) : p.R;
+  const int r0 = gbeg + zb * NTOK;
+  if (r0 >= gend) return;                                  // group without rows (uniform for the CTA: before any barrier or TMEM use)
+  const int cnt = min(NTOK, gend - r0);
+  const int kbeg = split * p.k_per_split, kend = min(p.K, kbeg + p.k_per_split);
+  const int n_steps = (kend - kbeg) / 32;                  // MMAs (K = 32 each)
+  const int n_kb = (kend - kbeg) / p.bk;                   // K blocks = promotions
+  const int steps_per_kb = p.bk / 32;
+  const int kb0 = kbeg / p.bk;
+  const int ws_n = p.bn >= 128 ? 1 : 128 / p.bn;           // weight-scale columns this tile touches (its 128 columns start on a block boundary)
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* xs_s = reinterpret_cast<float*>(smem + F8_STAGES * STAGE_BYTES);        // [n_kb][NTOK]
+  float* ws_s = xs_s + F8_MAX_KBLOCKS * NTOK;                                    // [n_kb][ws_n]
+  __shared__ uint64_t full_bar[F8_STAGES], empty_bar[F8_STAGES], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t tmem_base_holder;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < F8_STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&tfull_bar[a]), 1);
+      mbar_init(smem_u32(&tempty_bar[a]), 4);
+    }
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_base_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  // scales of this CTA's K range: tokens x K blocks and K blocks x (one or two) column blocks
+  for (int i = threadIdx.x; i < n_kb * NTOK; i += F8_THREADS) {
+    const int kb = i / NTOK, t = i - kb * NTOK;
+    xs_s[i] = t < cnt ? p.xs[static_cast<size_t>(r0 + t) * (p.K / p.bk) + kb0 + kb] : 0.f;
+  }
+  for (int i = threadIdx.x; i < n_kb * ws_n; i += F8_THREADS) {
+    const int kb = i / ws_n, j = i - kb * ws_n;
+    const int nb = n0 / p.bn + j;
+    ws_s[i] = nb < p.N / p.bn ? p.ws[(static_cast<size_t>(g) * (p.K / p.bk) + kb0 + kb) * (p.N / p.bn) + nb] : 0.f;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_holder;
+  volatile int* abortp = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tma_w);
+      tma_prefetch_desc(&tma_x);
+      const int n_stage_loads = (kend - kbeg + F8_KSTAGE - 1) / F8_KSTAGE;
+      for (int it = 0; it < n_stage_loads; ++it) {
+        const int s = it % F8_STAGES;
+        const uint32_t ph = (it / F8_STAGES) & 1;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abortp)) {
+          atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
+          abort_flag = 1;
+          break;
+        }
+        const uint32_t bar = smem_u32(&full_bar[s]);
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int k0 = kbeg + it * F8_KSTAGE;              // rows past K (and token rows past R) read as zeros
+        tma_load_3d(sa, &tma_w, bar, n0, k0, g);
+        tma_load_2d(sa + A_BYTES, &tma_x, bar, k0, r0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int q = 0; q < n_steps; ++q) {
+        const int it = q / (F8_KSTAGE / 32), j = q % (F8_KSTAGE / 32);
+        const int s = it % F8_STAGES;
+        const int kb = q / steps_per_kb, first = q % steps_per_kb == 0, last = (q + 1) % steps_per_kb == 0;
+        const int acc = kb & 1;
+        if (j == 0) {
+          if (!mbar_wait(smem_u32(&full_bar[s]), (it / F8_STAGES) & 1, abortp)) {
+            atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
+            abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+        }
+        if (first) {
+          if (!mbar_wait(smem_u32(&tempty_bar[acc]), ((kb >> 1) & 1) ^ 1, abortp)) {
+            atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
+            abort_flag = 1;
+            break;
+          }
+          tc_fence_after();
+        }
+        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+        const uint64_t da = make_smem_desc(sa + j * 4096, 128 * 128, 1024);          // 32 k rows of 128 bytes, 8-row groups 1024 bytes apart
+        const uint64_t db = make_smem_desc(sa + A_BYTES + j * 32, 16, 1024);         // 32 bytes along each token row
+        tc_mma_ss_f8(tmem_base + acc * NTOK, da, db, IDESC, first ? 0u : 1u);
+        if (j == F8_KSTAGE / 32 - 1 || q == n_steps - 1) tc_commit(smem_u32(&empty_bar[s]));
+        if (last) tc_commit(smem_u32(&tfull_bar[acc]));
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int col = n0 + quarter * 32 + lane;              // this thread's weight column = TMEM lane
+    const int wsel = p.bn >= 128 ? 0 : (quarter * 32 + lane) / p.bn;
+    float racc[NTOK];
+#pragma unroll
+    for (int t = 0; t < NTOK; ++t) racc[t] = 0.f;
+    bool ok = true;
+    for (int kb = 0; kb < n_kb && ok; ++kb) {
+      const int acc = kb & 1;
+      if (!mbar_wait(smem_u32(&tfull_bar[acc]), (kb >> 1) & 1, abortp)) {
+        if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
+        abort_flag = 1;
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * NTOK + (uint32_t(quarter * 32) << 16);
+      const float wsv = ws_s[kb * ws_n + wsel];
+      const float* xrow = xs_s + kb * NTOK;
+#pragma unroll
+      for (int c = 0; c < NTOK / 16; ++c) {
+        uint32_t r[16];
+        tmem_ld16(taddr + c * 16, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) racc[c * 16 + i] = fmaf(__uint_as_float(r[i]), wsv * xrow[c * 16 + i], racc[c * 16 + i]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
+    }
+    if (ok && col < p.N) {
+      float* out = p.part + static_cast<size_t>(split) * p.R * p.N + col;
+#pragma unroll
+      for (int t = 0; t < NTOK; ++t)
+        if (t < cnt) out[static_cast<size_t>(r0 + t) * p.N] = racc[t];
+    }
+  }
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);        // let copies still in flight land before the shared memory is released
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+template <int NTOK>
+int launch_f8(const CUtensorMap& tw, const CUtensorMap& tx, const F8Params& p, cudaStream_t stream) {
+  constexpr int smem = f8_stages(NTOK) * (F8_KSTAGE * 128 + NTOK * 128) + F8_MAX_KBLOCKS * (NTOK + 2) * 4 + 1024;
+  static bool configured[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 64 && !configured[dev]) {
+    if (cudaFuncSetAttribute(decode_gemm_f8_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -91;
+    configured[dev] = true;
+  }
+  dim3 grid((p.N + 127) / 128, p.G, p.splits * p.zblocks);
+  decode_gemm_f8_kernel<NTOK><<<grid, F8_THREADS, smem, stream>>>(tw, tx, p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -92;
+}
+
 }  // namespace
 
 // x [R, K] bf16 (rows sorted by group); w [G, K, N] bf16 (quant = 0) or e4m3 with wscale [G, K/bk, N/bn] (quant = 1);
@@ -282,6 +496,44 @@ extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscal
   const int rc = quant ? launch_tn<true>(p, panel, stream) : launch_tn<false>(p, panel, stream);
   if (rc) return rc;
   if (swiglu && (residual || alpha != 1.f)) return -90;
+  decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,
+                                                   swiglu_limit, static_cast<const __nv_bfloat16*>(residual), alpha);
+  return cudaGetLastError() == cudaSuccess ? 0 : -93;
+}
+
+
+// The same product with e4m3 activations on the tensor cores: xq [R, K] e4m3 with xs [R, K / bk] fp32 (one scale per row and K
+// block: `lyra_fp8_quantize_2d` with a (1 x bk) block), w [G, K, N] e4m3 with ws [G, K / bk, N / bn]. `ntok` = token columns
+// per tile (16, 32 or 64: the smallest that holds the largest group keeps the epilogue short; larger groups take more
+// blocks along grid.z). bk must be a multiple of 32 that divides or is a multiple of 128; bn 64 or a multiple of 128; K a
+// multiple of bk; N a multiple of 16 and of bn.
+extern "C" int lyra_decode_gemm_f8(const void* xq, const float* xs, const void* w, const float* ws, int bk, int bn, const int* offsets,
+                                   const int* counts, const float* bias, float* part, void* out, int R, int K, int N, int G, int splits, int swiglu,
+                                   float swiglu_beta, float swiglu_limit, int ntok, int max_group_rows, const void* residual, float alpha,
+                                   int* status, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (ntok != 16 && ntok != 32 && ntok != 64) return -90;
+  if (bk < 32 || bk % 32 || (128 % bk && bk % 128) || K % bk || (bn != 64 && bn % 128) || N % bn || N % 16 || K % 16) return -90;
+  if (splits < 1 || (K / bk) % splits || ((K / splits) % 128 && splits > 1) || (K / splits) / bk > F8_MAX_KBLOCKS) return -90;
+  if (G < 1 || (!offsets && G != 1) || (swiglu && (residual || alpha != 1.f))) return -90;
+  F8Params p;
+  p.xs = xs; p.ws = ws; p.offsets = offsets; p.counts = offsets ? counts : nullptr; p.part = part;
+  p.R = R; p.K = K; p.N = N; p.G = G; p.splits = splits; p.k_per_split = K / splits; p.bk = bk; p.bn = bn; p.status = status;
+  if (max_group_rows <= 0 || max_group_rows > R) max_group_rows = R;
+  p.zblocks = (max_group_rows + ntok - 1) / ntok;
+  CUtensorMap tw, tx;
+  {
+    uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, (uint64_t)G}, strides[2] = {(uint64_t)N, (uint64_t)K * N};
+    uint32_t box[3] = {128, F8_KSTAGE, 1};
+    if (lyra::make_tmap(&tw, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -94;
+  }
+  {
+    uint64_t dims[2] = {(uint64_t)K, (uint64_t)R}, strides[1] = {(uint64_t)K};
+    uint32_t box[2] = {128, (uint32_t)ntok};
+    if (lyra::make_tmap(&tx, xq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -95;
+  }
+  const int rc = ntok == 64 ? launch_f8<64>(tw, tx, p, stream) : ntok == 32 ? launch_f8<32>(tw, tx, p, stream) : launch_f8<16>(tw, tx, p, stream);
+  if (rc) return rc;
   decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,
                                                    swiglu_limit, static_cast<const __nv_bfloat16*>(residual), alpha);
   return cudaGetLastError() == cudaSuccess ? 0 : -93;

@@ -56,6 +56,13 @@ struct GemmParams {
   // of the buffer peer_out[row_dest[r] >> 24] (another GPU's memory, plain 16-byte stores); rows with row_dest < 0 are dropped
   const int* row_dest;
   void* peer_out[AG_MAX_RANKS];
+  const float* row_scale;   // scattered output: optional per-row factor (the routing score of the row's assignment) applied after the bias
+  int* peer_count[AG_MAX_RANKS];  // scattered output: per destination rank, a counter in that rank's memory to which every tile adds the
+                            // number of rows it has stored there (release, system scope); null = no counting
+  // tile-granular dispatch (grouped-M): the rows of A are stored into this GPU's memory by other GPUs while the kernel runs
+  const int* tile_perm;     // logical -> physical 128-row tile, -1 = no more tiles; null = identity
+  const int* arrive;        // per physical tile: rows that have landed so far (running total, bumped by the senders)
+  const int* expect;        // per physical tile: running total that means "this tile is complete"
   int sym_tiles;            // tiles per matrix that are enumerated when sym_upper is set
   int sym_upper;            // 1: the result is symmetric (A A^T): tiles wholly below the diagonal are not enumerated; bf16 outputs are mirrored by
                             //    the epilogue of the upper tiles, fp32 outputs by `lyra_symmetrize`
@@ -138,13 +145,15 @@ __device__ __forceinline__ TileInfo decode_tile(const GemmParams& p, int tile) {
     m_blk = local / p.n_tiles;
     n_blk = local - m_blk * p.n_tiles;
   }
-  t.m0 = m_blk * BM;
-  t.n0 = n_blk * NSTEP;
   if (p.group_mode == GROUP_M) {
-    const int g = p.tile_group[m_blk];
+    if (p.tile_perm) m_blk = p.tile_perm[m_blk];
+    const int g = m_blk >= 0 ? p.tile_group[m_blk] : -1;
     t.valid = g >= 0;
     t.gb = g < 0 ? 0 : g;
+    if (m_blk < 0) m_blk = 0;
   }
+  t.m0 = m_blk * BM;
+  t.n0 = n_blk * NSTEP;
   return t;
 }
 
@@ -202,9 +211,33 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       tma_prefetch_desc(&tma_b);
       uint32_t it = 0;
       bool ok = true;
+      int ready_tile = -1;
       for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
         const TileInfo t = decode_tile<BN, EPI>(p, tile);
         if (!t.valid) continue;
+        if (p.arrive) {  // rows of this 128-row tile are being stored by other GPUs: wait until all of them have landed
+          const int mt = t.m0 / BM;
+          if (mt != ready_tile) {
+            const int want = p.expect[mt];
+            const long long t0 = clock64();
+            int v;
+            do {
+              asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p.arrive + mt) : "memory");
+              // give up after the time limit - or after 2 ms if an earlier kernel has already reported a failure (rows dropped on
+              // overflow never arrive; a healthy exchange delivers a tile within microseconds of its neighbours)
+              const long long waited = clock64() - t0;
+              if (v - want < 0 && (waited > WAIT_LIMIT_CYCLES || *abortp || (waited > 4000000 && *reinterpret_cast<volatile int*>(p.status) != 0))) {
+                atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER);
+                abort_flag = 1;
+                ok = false;
+                break;
+              }
+            } while (v - want < 0);
+            if (!ok) break;
+            asm volatile("fence.proxy.async.global;" ::: "memory");
+            ready_tile = mt;
+          }
+        }
         if (p.ag_world > 0) {  // this tile's 256-column panel of B must have landed in local memory before TMA reads it
           const int* flag = p.ag_flags + t.n0 / BN;
           const int want = p.ag_epoch * ((p.K + BK - 1) / BK);
@@ -213,7 +246,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           do {
             asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
             if (v < want && (clock64() - t0 > WAIT_LIMIT_CYCLES || *abortp)) {
-              atomicExch(p.status, STATUS_TIMEOUT_PEER);
+              atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER);
               abort_flag = 1;
               ok = false;
               break;
@@ -226,7 +259,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abortp)) {
-            atomicExch(p.status, STATUS_TIMEOUT_EMPTY);
+            atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
             abort_flag = 1;
             ok = false;
             break;
@@ -272,7 +305,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         const int acc = tile_it & 1;
         const uint32_t aph = (tile_it >> 1) & 1;
         if (!mbar_wait(smem_u32(&tempty_bar[acc]), aph ^ 1, abortp)) {
-          atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+          atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
           abort_flag = 1;
           break;
         }
@@ -282,7 +315,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1;
           if (!mbar_wait(smem_u32(&full_bar[s]), ph, abortp)) {
-            atomicExch(p.status, STATUS_TIMEOUT_FULL);
+            atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
             abort_flag = 1;
             ok = false;
             break;
@@ -358,7 +391,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
       if (have_acc) {
         const uint32_t aph = (tile_it >> 1) & 1;
         if (!mbar_wait(smem_u32(&tfull_bar[acc]), aph, abortp)) {
-          if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+          if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
           abort_flag = 1;
           break;
         }
@@ -378,6 +411,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
         __nv_bfloat16* stg = reinterpret_cast<__nv_bfloat16*>(smem + STAGES * STAGE_BYTES);
         int* sdest = reinterpret_cast<int*>(smem + STAGES * STAGE_BYTES + 128 * SCATTER_LD * 2);
         sdest[row_in_tile] = rdest;
+        const float rscale = (p.row_scale && rdest >= 0) ? p.row_scale[row] : 1.0f;
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t r[32];
@@ -396,6 +430,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
 #pragma unroll
             for (int i = 0; i < 32; ++i)
               if (col + i < p.N) v[i] += bias[col + i];
+          }
+          if (p.row_scale) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] *= rscale;
           }
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -420,6 +458,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
           }
+        }
+        if (p.peer_count[0]) {
+          // Every store of this tile has been issued (the loop ends behind a barrier of the four warps). Thread r tells rank r how
+          // many rows of this (row tile, column tile) now sit in its buffer: the receiving rank sums these until it has seen
+          // rows x column tiles of everything it sent out. The fence + release make the rows visible before the count.
+          if (row_in_tile < AG_MAX_RANKS && p.peer_count[row_in_tile]) {
+            int n = 0;
+            for (int i = 0; i < 128; ++i) {
+              const int d = sdest[i];
+              n += (d >= 0 && (d >> 24) == row_in_tile) ? 1 : 0;
+            }
+            if (n > 0) {
+              __threadfence_system();
+              asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p.peer_count[row_in_tile]), "r"(n) : "memory");
+            }
+          }
+          asm volatile("bar.sync 1, 128;" ::: "memory");
         }
       } else if (EPI == EPI_STORE) {
 #pragma unroll 1
@@ -684,11 +739,15 @@ extern "C" int lyra_gemm_bf16(
     int group_mode, int num_groups, const int* tile_group, const int* group_offsets, int total_rows,
     int epilogue, int n_split, float swiglu_beta, float swiglu_limit, int sym_upper,
     const int* row_dest, const long long* peer_out, int n_peers,
+    const float* row_scale, const long long* peer_count, const int* tile_perm, const int* arrive, const int* expect,
     int* status, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   if ((lda % 8) || (ldb % 8) || (ldc % (out_fp32 ? 4 : 8))) return -10;
   if (sym_upper && (M != N || epilogue != EPI_STORE || group_mode == GROUP_M || group_mode == GROUP_K)) return -14;
   if (row_dest && (epilogue != EPI_STORE || out_fp32 || Cin || !peer_out || n_peers < 1 || n_peers > AG_MAX_RANKS || sym_upper)) return -15;
+  if ((row_scale || peer_count) && !row_dest) return -16;
+  if ((tile_perm || arrive || expect) && group_mode != GROUP_M) return -17;
+  if ((arrive != nullptr) != (expect != nullptr)) return -17;
   const int G = num_groups > 0 ? num_groups : 1;
   constexpr int BN = 256;
 
@@ -705,6 +764,8 @@ extern "C" int lyra_gemm_bf16(
   p.total_tiles = p.m_tiles * p.n_tiles * ((group_mode == GROUP_K || group_mode == GROUP_BATCH) ? G : 1);
   p.raster_group = default_raster_group(p.n_tiles);
   for (int r = 0; r < AG_MAX_RANKS; ++r) p.peer_out[r] = (row_dest && r < n_peers) ? reinterpret_cast<void*>(peer_out[r]) : nullptr;
+  for (int r = 0; r < AG_MAX_RANKS; ++r) p.peer_count[r] = (row_dest && peer_count && r < n_peers) ? reinterpret_cast<int*>(peer_count[r]) : nullptr;
+  p.row_scale = row_scale; p.tile_perm = tile_perm; p.arrive = arrive; p.expect = expect;
   p.sym_tiles = 0;
   if (sym_upper) {
     for (int m = 0; m < p.m_tiles; ++m) p.sym_tiles += p.n_tiles - (p.n_tiles < m * BM / BN ? p.n_tiles : m * BM / BN);
@@ -800,6 +861,8 @@ extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long lo
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
   p.ag_world = 0;
   p.raster_n_major = 1; p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0; p.row_dest = nullptr;
+  p.row_scale = nullptr; p.tile_perm = nullptr; p.arrive = nullptr; p.expect = nullptr;
+  for (int r = 0; r < AG_MAX_RANKS; ++r) p.peer_count[r] = nullptr;
   p.ce_y = y; p.ce_part_m = part_m; p.ce_part_l = part_l; p.ce_tgt = tgt; p.ce_lse = lse; p.ce_gscale = gscale;
   p.m_tiles = (M + BM - 1) / BM;
   p.n_tiles = (vocab + BN - 1) / BN;
@@ -877,6 +940,8 @@ extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_lo
   p.group_mode = GROUP_NONE; p.tile_group = nullptr; p.group_offsets = nullptr; p.num_groups = 1;
   p.n_split = 0; p.swiglu_beta = 0.f; p.swiglu_limit = 0.f; p.status = status;
   p.raster_group = 0; p.sym_upper = 0; p.sym_tiles = 0; p.row_dest = nullptr;
+  p.row_scale = nullptr; p.tile_perm = nullptr; p.arrive = nullptr; p.expect = nullptr;
+  for (int r = 0; r < AG_MAX_RANKS; ++r) p.peer_count[r] = nullptr;
   p.raster_n_major = 1;  // tiles walk M first, column panel by column panel: the order in which the panels of B arrive
   p.ce_y = nullptr; p.ce_part_m = nullptr; p.ce_part_l = nullptr; p.ce_tgt = nullptr; p.ce_lse = nullptr; p.ce_gscale = nullptr;
   p.ag_world = world; p.ag_rows_per_rank = rows_per_rank; p.ag_my_rank = my_rank; p.ag_row_bytes = ldw * 2;

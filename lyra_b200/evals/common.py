@@ -74,34 +74,54 @@ class Scorer:
         prompt += self.harmony.encode("<|channel|>final<|message|>", allowed_special="all")
         return prompt, self.harmony.encode(continuation)
 
-    def requests(self, docs: list[Doc]) -> list[tuple[int, int, list[int], int]]:
-        out = []
+    def requests(self, docs: list[Doc]) -> list["Request"]:
+        """One request per (document, choice). The continuation is the choice joined to the context by a single space (trailing
+        whitespace of the context moves to the continuation side); the context loses tokens from the left until context +
+        continuation fit the model's window."""
+        window = self.config.seq_len
+        reqs: list[Request] = []
         for d, doc in enumerate(docs):
-            context = doc.context.rstrip()
+            stem = doc.context.rstrip()
+            tail = doc.context[len(stem):]
             for c, choice in enumerate(doc.choices):
-                ctx, cont = self._encode(context, doc.context[len(context):] + " " + choice)
-                ctx = ctx[-(self.config.seq_len - len(cont)):]
-                out.append((d, c, ctx + cont, len(ctx)))
-        return out
+                context_ids, continuation_ids = self._encode(stem, f"{tail} {choice}")
+                keep = max(window - len(continuation_ids), 0)
+                context_ids = context_ids[len(context_ids) - keep:] if keep else []
+                reqs.append(Request(doc=d, choice=c, ids=context_ids + continuation_ids, scored_from=len(context_ids)))
+        return reqs
 
     def score(self, docs: list[Doc]) -> list[list[float]]:
-        reqs = self.requests(docs)
-        width = max(len(ids) for _, _, ids, _ in reqs)
+        """``scores[d][c]`` = summed log-probability of choice ``c``'s continuation tokens. There is no compiled step whose
+        shape must stay fixed, so requests are visited longest first and every batch is padded only to its own longest row
+        (rounded up to a multiple of 64); a short last batch is filled with padding rows."""
+        reqs = sorted(self.requests(docs), key=lambda r: -len(r.ids))
         scores = [[0.0] * len(doc.choices) for doc in docs]
-        for start in range(0, len(reqs), self.batch_size):
-            batch = reqs[start:start + self.batch_size]
-            tokens = np.full((self.batch_size, width), self.tokenizer.pad_token, dtype=np.int64)
-            targets = np.zeros((self.batch_size, width), dtype=np.int64)
-            mask = np.zeros((self.batch_size, width), dtype=np.float32)
-            for row, (_, _, ids, cont_start) in enumerate(batch):
-                tokens[row, :len(ids)] = ids
-                targets[row, :len(ids) - 1] = ids[1:]
-                mask[row, cont_start - 1:len(ids) - 1] = 1.0   # continuation tokens only
-            to = lambda a: torch.from_numpy(a).to(self.device)
-            sums = continuation_logprob(self.model, self.config, to(tokens), to(targets), to(mask), self.rt).cpu().numpy()
-            for row, (d, c, _, _) in enumerate(batch):
-                scores[d][c] = float(sums[row])
+        rows = self.batch_size
+        for first in range(0, len(reqs), rows):
+            group = reqs[first:first + rows]
+            width = min(-(-len(group[0].ids) // 64) * 64, max(self.config.seq_len, len(group[0].ids)))
+            tokens = np.full((rows, width), self.tokenizer.pad_token, dtype=np.int64)
+            targets = np.zeros((rows, width), dtype=np.int64)
+            scored = np.zeros((rows, width), dtype=np.float32)
+            for row, r in enumerate(group):
+                n = len(r.ids)
+                tokens[row, :n] = r.ids
+                targets[row, :n - 1] = r.ids[1:]                     # position t predicts token t + 1
+                scored[row, r.scored_from - 1:n - 1] = 1.0           # ... and only the continuation's tokens count
+            on_device = [torch.from_numpy(a).to(self.device) for a in (tokens, targets, scored)]
+            sums = continuation_logprob(self.model, self.config, *on_device, self.rt).tolist()
+            for r, total in zip(group, sums):
+                scores[r.doc][r.choice] = float(total)
         return scores
+
+
+@dataclass(frozen=True)
+class Request:
+    doc: int
+    choice: int
+    ids: list[int]
+    scored_from: int
+    """Index in ``ids`` of the first continuation token."""
 
 
 def evaluate(task: str, docs: list[Doc], scorer: Scorer) -> EvalResult:

@@ -321,6 +321,12 @@ def calculate_aux_loss(router_logits, expert_indices, config: ModelConfig, *, pr
     return aux.float()
 
 
+ROUTING_TAPE: dict | None = None
+"""Numerics tests that compare two implementations of the model set this to ``{"replay": False, "choices": []}`` for the first
+run (the experts chosen by every MoE layer call are recorded) and flip ``replay`` for the second, which then takes the recorded
+experts instead of its own top-k: near-tie choices that flip between two bf16 paths no longer blur the comparison."""
+
+
 def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE, rt=None):
     """fp32 router, top-k over routed experts, softmax over the selected logits, shared experts appended
     with score 1 (lyra/model.py:451-480). Returns ``(scores [F, K], indices [F, K], aux_loss)``."""
@@ -331,7 +337,13 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
         if w.router_bias is not None:
             logits = logits + W(w.router_bias).float()
     k = c.n_active_routed_experts
-    vals, idx = torch.topk(logits, k, dim=-1)  # ties -> lower index first, like lax.top_k
+    if ROUTING_TAPE is not None and ROUTING_TAPE["replay"]:
+        idx = ROUTING_TAPE["choices"].pop(0)
+        vals = torch.gather(logits, -1, idx)
+    else:
+        vals, idx = torch.topk(logits, k, dim=-1)  # ties -> lower index first, like lax.top_k
+        if ROUTING_TAPE is not None:
+            ROUTING_TAPE["choices"].append(idx)
     scores = torch.softmax(vals, dim=-1)
     aux = calculate_aux_loss(logits, idx, c, probe=probe)
     meter = getattr(rt, "load_meter", None)

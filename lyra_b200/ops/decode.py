@@ -121,6 +121,9 @@ def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, coun
     if quant:
         bk, bn = w.block[-2], w.block[-1]
         scale = w.scale.float().contiguous()
+        if F8_TENSOR_CORES and f8_gemm_supported(K, N, bk, bn) and hasattr(lib, "lyra_decode_gemm_f8"):
+            return _decode_gemm_f8(lib, x, wq, scale, bk, bn, offsets, counts, bias, swiglu, swiglu_beta, swiglu_limit, active_groups,
+                                   max_group_rows, residual, alpha)
     panel = _gemm_panel(N)
     splits = _gemm_splits(N, panel, min(G, R) if active_groups is None else active_groups, K // 64)
     part = torch.empty(splits, R, N, dtype=torch.float32, device=x.device)
@@ -137,6 +140,46 @@ def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, coun
     return out
 
 
+
+
+def f8_gemm_supported(K: int, N: int, bk: int, bn: int) -> bool:
+    """Shapes the e4m3 x e4m3 tcgen05 kernel takes: K blocks of 32..., column blocks of 64 or multiples of 128."""
+    return (bk >= 32 and bk % 32 == 0 and (128 % bk == 0 or bk % 128 == 0) and K % bk == 0 and (bn == 64 or bn % 128 == 0) and N % bn == 0
+            and N % 16 == 0 and K % 16 == 0 and K // bk <= 64)
+
+
+def _decode_gemm_f8(lib, x, wq, wscale, bk, bn, offsets, counts, bias, swiglu, swiglu_beta, swiglu_limit, active_groups, max_group_rows, residual, alpha):
+    """e4m3 weights x e4m3 activations on the tensor cores (``decode_gemm_f8_kernel``). The activations are quantised here with
+    one scale per (row, K block of ``bk``), the (1 x scale_k) block of the reference's quantised grouped GEMM
+    (lyra/kernels/gemm.py:1551-1556); the weights stream once, as stored."""
+    from lyra_b200.nn.quant import quantize
+
+    G, K, N = wq.shape
+    R = x.shape[0]
+    xq = quantize(x, torch.float8_e4m3fn, (1, bk))
+    most = min(R, max_group_rows) if max_group_rows else R
+    ntok = 16 if most <= 16 else 32 if most <= 32 else 64
+    groups = min(G, R) if active_groups is None else active_groups
+    ctas = max(1, (N + 127) // 128 * max(1, groups))
+    splits = 1
+    for cand in range(1, K // 128 + 1):            # K splits for layers with few column panels (about two CTAs per SM)
+        if K % (cand * 128) == 0 and (K // bk) % cand == 0 and cand * ctas <= 2 * 148:
+            splits = cand
+    part = torch.empty(splits, R, N, dtype=torch.float32, device=x.device)
+    out = torch.empty(R, N // 2 if swiglu else N, dtype=BF16, device=x.device)
+    b = bias.detach().float().contiguous() if bias is not None else None
+    if residual is not None:
+        assert not swiglu and residual.dtype == BF16 and residual.shape == (R, N) and residual.is_contiguous()
+    lib.lyra_decode_gemm_f8.restype = c_int
+    rc = lib.lyra_decode_gemm_f8(ptr(xq.qval), ptr(xq.scale), ptr(wq), ptr(wscale), c_int(bk), c_int(bn), ptr(offsets), ptr(counts), ptr(b), ptr(part),
+                                 ptr(out), c_int(R), c_int(K), c_int(N), c_int(G), c_int(splits), c_int(int(swiglu)), c_float(swiglu_beta),
+                                 c_float(swiglu_limit), c_int(ntok), c_int(most), ptr(residual), c_float(alpha), ptr(native.status_word()),
+                                 native.stream_ptr())
+    native.check(rc, "lyra_decode_gemm_f8")
+    native.count_launch(2)
+    return out
+
+
 def decode_gemm_supported(K: int, N: int, w) -> bool:
     if K % 64 or N % 64:
         return False
@@ -148,6 +191,7 @@ def decode_gemm_supported(K: int, N: int, w) -> bool:
 
 import os as _os
 
+F8_TENSOR_CORES = _os.environ.get("LYRA_DECODE_F8_TC", "1") != "0"   # quantised weights: e4m3 x e4m3 tcgen05 kernel (0: dequantise in flight, mma.sync)
 DECODE_GEMM_MAX_ROWS = int(_os.environ.get("LYRA_DECODE_GEMM_MAX_ROWS", "512"))   # assignments (tokens x experts per token); above this the 128-row-tile tcgen05 grouped GEMM takes over
 
 

@@ -24,6 +24,7 @@ TILE_M = 128
 def _raw(
     a, lda, a_gs, a_mn, b, ldb, b_gs, b_mn, c, c_in, ldc, c_gs, out_fp32, M, N, K, alpha, beta, bias, bias_gs,
     group_mode, num_groups, tile_group, group_offsets, total_rows, epilogue, n_split, swiglu_beta, swiglu_limit, sym_upper=False, row_dest=None, peer_out=None,
+    row_scale=None, peer_count=None, tile_perm=None, arrive=None, expect=None,
 ):
     import ctypes
 
@@ -31,6 +32,7 @@ def _raw(
     fn = lib.lyra_gemm_bf16
     fn.restype = c_int
     peers = (ctypes.c_longlong * len(peer_out))(*peer_out) if peer_out else None
+    counters = (ctypes.c_longlong * len(peer_count))(*peer_count) if peer_count else None
     rc = fn(
         ptr(a), c_ll(lda), c_ll(a_gs), c_int(int(a_mn)),
         ptr(b), c_ll(ldb), c_ll(b_gs), c_int(int(b_mn)),
@@ -40,6 +42,7 @@ def _raw(
         c_int(group_mode), c_int(num_groups), ptr(tile_group), ptr(group_offsets), c_int(total_rows),
         c_int(epilogue), c_int(n_split), c_float(swiglu_beta), c_float(swiglu_limit), c_int(int(sym_upper)),
         ptr(row_dest), peers, c_int(len(peer_out) if peer_out else 0),
+        ptr(row_scale), counters, ptr(tile_perm), ptr(arrive), ptr(expect),
         ptr(native.status_word()), native.stream_ptr(),
     )
     native.check(rc, "lyra_gemm_bf16")
@@ -132,12 +135,26 @@ def grouped_gemm(
     out: torch.Tensor | None = None,
     row_dest: torch.Tensor | None = None,
     peer_out: list[int] | None = None,
+    row_scale: torch.Tensor | None = None,
+    peer_count: list[int] | None = None,
+    tile_perm: torch.Tensor | None = None,
+    arrive: torch.Tensor | None = None,
+    expect: torch.Tensor | None = None,
 ) -> torch.Tensor | None:
     """Ragged grouped GEMM over rows sorted by group and padded so every 128-row tile has one group.
 
     With ``row_dest [R]`` (int32: ``rank << 24 | row``, negative = drop the row) and ``peer_out`` (one peer-mapped buffer
     address per rank, rows of ``N`` bf16) the epilogue stores every result row straight into that rank's buffer over
     NVLink instead of a local output: the return leg of the expert-parallel exchange fused into the product.
+
+    Scattered mode extras: ``row_scale [R]`` fp32 multiplies each stored row (after the bias) - the routing score, so that the
+    source rank's combine is a plain K-way sum; ``peer_count`` (one address per rank of an int32 counter in that rank's memory)
+    makes every output tile add the number of rows it stored on a rank to that rank's counter, which the rank waits on
+    (``lyra_wait_arrivals``) instead of an all-rank barrier.
+
+    Tile-granular input (``arrive`` / ``expect`` int32 ``[R/128]``): other GPUs are still storing the rows of ``x`` while the
+    kernel runs; the TMA producer waits until ``arrive[t] - expect[t] >= 0`` before it first reads 128-row tile ``t``.
+    ``tile_perm [R/128]`` int32 lists the used tiles in the order in which they should be visited (-1 ends the list).
 
     ``x [R, K]``; ``tile_group [R/128]`` int32 (-1 marks unused tiles, whose output rows are left untouched);
     ``w [G, K, N]`` (forward, MN-major) or, with ``w_kmajor``, ``w [G, N, K]`` (data gradient of an ``[in, out]`` weight).
@@ -152,17 +169,22 @@ def grouped_gemm(
         Kw, N = w.shape[1], w.shape[2]
     assert Kw == K
     n_out = N // 2 if swiglu else N
+    for t in (tile_perm, arrive, expect):
+        assert t is None or (t.dtype == torch.int32 and t.numel() >= R // TILE_M and t.is_contiguous())
+    waits = dict(tile_perm=tile_perm, arrive=arrive, expect=expect)
     if row_dest is not None:
         assert not swiglu and peer_out and row_dest.dtype == torch.int32 and row_dest.numel() >= R
+        assert row_scale is None or (row_scale.dtype == torch.float32 and row_scale.numel() >= R)
+        assert peer_count is None or len(peer_count) == len(peer_out)
         _raw(x, x.stride(0), 0, False, w, w.stride(1), w.stride(0), not w_kmajor, x, None, N, 0, False,
              R, N, K, 1.0, 0.0, bias, (bias.stride(0) if bias is not None else 0), GROUP_M, G, tile_group, None, 0,
-             EPI_STORE, 0, swiglu_beta, swiglu_limit, row_dest=row_dest, peer_out=peer_out)
+             EPI_STORE, 0, swiglu_beta, swiglu_limit, row_dest=row_dest, peer_out=peer_out, row_scale=row_scale, peer_count=peer_count, **waits)
         return None
     if out is None:
         out = torch.empty(R, n_out, dtype=torch.bfloat16, device=x.device)
     _raw(x, x.stride(0), 0, False, w, w.stride(1), w.stride(0), not w_kmajor, out, None, out.stride(0), 0, False,
          R, N, K, 1.0, 0.0, bias, (bias.stride(0) if bias is not None else 0), GROUP_M, G, tile_group, None, 0,
-         EPI_SWIGLU if swiglu else EPI_STORE, N // 2 if swiglu else 0, swiglu_beta, swiglu_limit)
+         EPI_SWIGLU if swiglu else EPI_STORE, N // 2 if swiglu else 0, swiglu_beta, swiglu_limit, **waits)
     return out
 
 

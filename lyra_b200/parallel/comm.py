@@ -28,9 +28,13 @@ class SymmetricSlab:
 
         nbytes = max((nbytes + ALIGN - 1) // ALIGN * ALIGN, ALIGN)
         self.buffer = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+        # Cleared and finished BEFORE the handle exchange: a peer can store into this buffer as soon as it holds the address,
+        # and the exchange cannot complete on any rank before every rank has entered it. (Clearing afterwards let a fast peer's
+        # first rows land before a slower owner's queued memset ran, which then wiped them.)
+        self.buffer.zero_()
+        torch.cuda.synchronize(device)
         self.handle = symm_mem.rendezvous(self.buffer, group_name)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
-        self.buffer.zero_()
 
     def view(self, offset: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
@@ -84,7 +88,7 @@ class Comm:
         self._reduced: dict[str, torch.Tensor] = {}
         for name, shape, owner in entries:
             if owner == self.rank:
-                self._reduced[name] = torch.empty(self.numel[name], dtype=torch.float32 if grad_dtype == torch.float32 else BF16, device=self.device)
+                self._reduced[name] = torch.empty((self.numel[name] + 7) // 8 * 8, dtype=torch.float32 if grad_dtype == torch.float32 else BF16, device=self.device)
 
     # ------------------------------------------------------------------ views
     def weight_view(self, name: str) -> torch.Tensor:
@@ -201,17 +205,12 @@ class Comm:
             if owner != self.rank:
                 continue
             n = self.numel[name]
-            dst = self._reduced[name]
-            n8 = n // 8 * 8
+            n8 = (n + 7) // 8 * 8                                # every leaf's region is 256-byte aligned and its padding stays zero
+            dst = self._reduced[name]                            # (padded to n8 elements)
             nat.check(self.lib.lyra_reduce_pull(nat.ptr(dst), _ptr_array(self.g_slab.peers_at(self.g_off[name])), self.world,
                                                 ctypes.c_longlong(n8), in_bf16, in_bf16, stream), "reduce_pull")
             nat.count_launch()
-            if n8 != n:  # ragged tail: a handful of elements
-                tail = torch.zeros(n - n8, dtype=torch.float32, device=self.device)
-                parts = [self.grad_view(name)[n8:].float()]
-                gathered = [torch.zeros_like(parts[0]) for _ in range(self.world)]
-                dist.all_gather(gathered, parts[0])
-                dst[n8:] = sum(gathered, tail).to(dst.dtype)
+            dst = dst[:n]
             out[name] = dst
         self.barrier()                                           # buffers may be zeroed for the next step after this
         return out

@@ -109,6 +109,9 @@ def optimizer_step_cuda(params: dict[str, torch.Tensor], grads: dict[str, torch.
     nesterov = tcfg.muon_momentum if tcfg.muon_nesterov else -1.0
     for p in muon_paths:
         w, g, mom = params[p], grads[p].contiguous(), state.muon_moment[p]
+        if w.dtype != torch.float32 or mom.dtype != BF16 or g.dtype not in (BF16, torch.float32):
+            raise TypeError(f"{p}: the fused Muon kernels need fp32 parameters, a bf16 moment and bf16 or fp32 gradients "
+                            f"(got {w.dtype}, {mom.dtype}, {g.dtype})")
         stack, mats_lo, rows, cols, stride_lo = _matrix_geometry(p, tuple(w.shape))
         per_stack = mats_lo * rows * cols
         d = torch.empty(w.shape, dtype=BF16, device=dev)

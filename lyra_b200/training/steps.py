@@ -23,6 +23,7 @@ from lyra_b200.training.optimizer import optimizer_step
 from lyra_b200.training.probe import Probe, mean_over_ranks
 from lyra_b200.training.state import TrainState
 from lyra_b200.utils.nvtx import scope
+from lyra_b200.utils.phases import span
 
 
 def loss_parts(params: ModelWeights, x: torch.Tensor, y: torch.Tensor, config: ModelConfig, rt=None):
@@ -67,9 +68,14 @@ class Stepper:
         if not t.is_pinned():
             t = t.pin_memory()
         self.h2d_bytes += t.numel() * t.element_size()
+        main = torch.cuda.current_stream()
         with torch.cuda.stream(self.copy_stream):
             d = t.to(self.device, non_blocking=True)
-        torch.cuda.current_stream().wait_stream(self.copy_stream)
+        main.wait_stream(self.copy_stream)
+        # The block belongs to the copy stream's pool but only the main stream reads it (embedding backward and the
+        # cross-entropy backward read it last, long after the host has dropped its reference). Without this the allocator
+        # would hand the block to the next staged microbatch while those kernels are still queued.
+        d.record_stream(main)
         return d
 
     def _scales(self, A: int, B: int, T: int) -> tuple[float, float]:
@@ -81,7 +87,7 @@ class Stepper:
         A, B, T = xs.shape
         ce_scale, aux_scale = self._scales(A, B, T)
         totals = torch.zeros(3, dtype=torch.float32, device=self.device)
-        with scope("gradient_accumulation"):
+        with scope("gradient_accumulation"), span("forward_backward"):
             staged = [(self.to_device(xs[0]), self.to_device(ys[0]))]
             for a in range(A):
                 x, y = staged[a]
@@ -98,12 +104,17 @@ class Stepper:
                 staged[a] = None
         grads = {p: (t.grad if t.grad is not None else torch.zeros_like(t)) for p, t in self.params.items() if t.requires_grad}
         if self.rt is not None:
-            totals = self.rt.sum_scalars(totals)
-            grads = self.rt.reduce_grads(grads)
-        with scope("optimizer"):
+            with span("gradient_reduce"):
+                totals = self.rt.sum_scalars(totals)
+                grads = self.rt.reduce_grads(grads)
+        with scope("optimizer"), span("optimizer"):
             trainable = {p: t for p, t in self.params.items() if p in grads}
+            t = self.tcfg
             fused = (self.device.type == "cuda" and self.mcfg.implementation in ("auto", "b200")
-                     and (self.rt is None or not self.rt.owns_optimizer))
+                     and (self.rt is None or not self.rt.owns_optimizer)
+                     # the fused kernels hard-code fp32 masters, bf16 first moments and an fp32 second moment; other choices take the PyTorch step
+                     and self.mcfg.param_dtype == torch.float32 and t.muon_moment_dtype == torch.bfloat16
+                     and t.adam_mu_dtype == torch.bfloat16 and t.adam_nu_dtype == torch.float32)
             if fused:
                 from lyra_b200.ops import cuda_ops
                 from lyra_b200.training.optimizer_cuda import optimizer_step_cuda
@@ -119,7 +130,8 @@ class Stepper:
         for t in self.params.values():
             t.grad = None
         if self.rt is not None:
-            self.rt.after_optimizer(self.params)
+            with span("weight_refresh"):
+                self.rt.after_optimizer(self.params)
         return {"loss": totals[0], "ce_loss": totals[1], "aux_loss": totals[2], **metrics}
 
     # ------------------------------------------------------------------ validation / numerics

@@ -6,7 +6,6 @@ from __future__ import annotations
 import itertools
 import json
 import math
-import shutil
 import time
 from contextlib import AbstractContextManager, nullcontext
 from dataclasses import asdict, dataclass, field, replace
@@ -157,171 +156,260 @@ class TrainHooks:
         pass
 
 
-def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *, hooks: TrainHooks | None = None, rt=None,
-          device=None) -> TrainState:
-    hooks = hooks or TrainHooks()
-    primary = rt is None or rt.rank == 0
-    device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
-    out = checkpoint_path(tcfg.checkpoint_path)
-    run_dir = out
-    if primary:
-        run_dir.mkdir(parents=True, exist_ok=True)
-    if tcfg.resume_from is None and checkpoint_steps(out):
-        raise FileExistsError(f"{out} already has checkpoints. Pass --resume, or choose another --out.")
-    data_ranks = rt.data_size if rt is not None else 1
-    if tcfg.batch_size % data_ranks:
-        raise ValueError(f"--batch-size {tcfg.batch_size} must be a multiple of the {data_ranks} data-parallel devices.")
-    local_batch = tcfg.batch_size // data_ranks
+class _Periodic:
+    """Decides which of the loop's side jobs fall on a step: a job is due on its own cadence and always on the last step."""
 
-    # every rank reads its own rows of each global block
-    loader = DataLoader(tcfg.data_path, tcfg.batch_size, mcfg.seq_len, config=tcfg.data_loader, quiet=not primary)
-    loader.check_steps(tcfg.steps, tcfg.accumulation_steps)
-    signature = resume_signature(mcfg, tcfg, loader)
-    eval_loader = None
-    if tcfg.eval_data_path is not None:
-        eval_config = replace(tcfg.data_loader, shuffle=False, num_epochs=None, worker_count=1)
-        eval_loader = DataLoader(tcfg.eval_data_path, tcfg.batch_size, mcfg.seq_len, config=eval_config, quiet=not primary)
-        eval_start = eval_loader.get_state()
+    def __init__(self, tcfg: TrainingConfig, first_step: int, has_eval: bool):
+        self.t, self.first, self.has_eval = tcfg, first_step, has_eval
 
-    def local_rows(a: np.ndarray) -> np.ndarray:
-        if data_ranks == 1:
-            return a
-        r = rt.data_rank
-        return a[..., r * local_batch:(r + 1) * local_batch, :]
+    def _every(self, every: int | None, step: int) -> bool:
+        return step == self.t.steps or (every is not None and step % every == 0)
 
-    if tcfg.resume_from is None:
-        assert model is not None, "a new run needs initial weights"
-        start_step = 0
-        state = init_train_state(model, mcfg, tcfg)
-        if primary:
-            for name in RUN_ARTIFACTS:
-                (run_dir / name).unlink(missing_ok=True)
-    else:
-        path = resolve_checkpoint(tcfg.resume_from)
-        check_resume(path, signature)
-        restored = load_train_state(path, mcfg, tcfg, device=device, rt=rt)
-        state, start_step = restored.state, restored.step
-        loader.set_state(restored.loader_state)
-        if primary:
+    def numerics(self, step: int) -> bool:
+        return self.t.numerics_every is not None and (step == 1 or self._every(self.t.numerics_every, step))
+
+    def checkpoint(self, step: int) -> bool:
+        return self._every(self.t.checkpoint_every, step)
+
+    def evaluation(self, step: int) -> bool:
+        return self.has_eval and self._every(self.t.eval_every, step)
+
+    def sampling(self, step: int) -> bool:
+        return self.t.sample_every is not None and self._every(self.t.sample_every, step)
+
+    def log_line(self, step: int) -> bool:
+        return step == self.first or step % self.t.log_every == 0 or self.checkpoint(step) or self.evaluation(step)
+
+    def rebalance(self, step: int) -> bool:
+        every = self.t.rebalance_experts_every
+        return every is not None and step % every == 0 and step < self.t.steps
+
+
+class TrainingRun:
+    """One run of the loop, built in the order the device-side state needs: data -> state (fresh or restored) -> ``Stepper``
+    (which binds the sharding runtime to the parameter tree) -> logs. ``advance`` is one optimizer step plus whatever side
+    jobs fall on it; ``close`` releases files and says goodbye to the other ranks. ``train`` below drives it.
+
+    Behaviour follows lyra/training/train.py:160-292 (refusal to reuse a run directory, resume signature, artifacts restored
+    from the checkpoint, throughput that leaves out evaluation / sampling / checkpoint time); the additions are the rank
+    roll call at step boundaries, the kernel status check before anything is logged or saved, and expert re-placement."""
+
+    def __init__(self, model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, hooks: TrainHooks, rt, device):
+        self.mcfg, self.tcfg, self.hooks, self.rt = mcfg, tcfg, hooks, rt
+        self.primary = rt is None or rt.rank == 0
+        self.device = torch.device(device or ("cuda" if torch.cuda.is_available() else "cpu"))
+        self.out = checkpoint_path(tcfg.checkpoint_path)
+        if self.primary:
+            self.out.mkdir(parents=True, exist_ok=True)
+        if tcfg.resume_from is None and checkpoint_steps(self.out):
+            raise FileExistsError(f"{self.out} already has checkpoints. Pass --resume, or choose another --out.")
+        self.data_ranks = rt.data_size if rt is not None else 1
+        if tcfg.batch_size % self.data_ranks:
+            raise ValueError(f"--batch-size {tcfg.batch_size} must be a multiple of the {self.data_ranks} data-parallel devices.")
+        self.local_batch = tcfg.batch_size // self.data_ranks
+        self.tokens_per_step = tcfg.accumulation_steps * tcfg.batch_size * mcfg.seq_len
+        self.heartbeat = self.metrics = self.loader = self.eval_loader = None
+        try:
+            self._open_data()
+            self._open_state(model)
+            self._open_stepper()
+        except BaseException:
+            self.close()
+            raise
+
+    def _open_stepper(self) -> None:
+        mcfg, tcfg, hooks, rt = self.mcfg, self.tcfg, self.hooks, self.rt
+        self.run_config = _jsonable({"model": mcfg.to_dict(), "training": asdict(tcfg), "resume_signature": self.signature})
+        if self.primary:
+            (self.out / "config.json").write_text(json.dumps(self.run_config, indent=2))
+        built = time.perf_counter()
+        self.stepper = Stepper(self.state, mcfg, tcfg, device=self.device, rt=rt)
+        hooks.on_lowered(self.stepper)
+        hooks.on_compiled(self.stepper, {"lower_seconds": 0.0, "xla_compile_seconds": 0.0, "total_seconds": time.perf_counter() - built})
+        self.metrics = MetricsLogger(self.out, tokens_per_step=self.tokens_per_step, initial_step=self.start_step, enabled=self.primary)
+        self.due = _Periodic(tcfg, self.start_step + 1, self.eval_loader is not None)
+        self.probe = Probe(routing_only=True) if tcfg.numerics_every is not None else None
+        self._sampler = self._build_sampler() if tcfg.sample_every is not None else None
+        self.rebalancing = tcfg.rebalance_experts_every is not None and rt is not None and rt.meter_expert_load()
+        self._join_roll_call()
+
+    # ------------------------------------------------------------------ construction
+    def _open_data(self) -> None:
+        t = self.tcfg
+        self.loader = DataLoader(t.data_path, t.batch_size, self.mcfg.seq_len, config=t.data_loader, quiet=not self.primary)
+        self.loader.check_steps(t.steps, t.accumulation_steps)
+        self.signature = resume_signature(self.mcfg, t, self.loader)
+        if t.eval_data_path is not None:   # validation replays the same batches every time
+            fixed = replace(t.data_loader, shuffle=False, num_epochs=None, worker_count=1)
+            self.eval_loader = DataLoader(t.eval_data_path, t.batch_size, self.mcfg.seq_len, config=fixed, quiet=not self.primary)
+            self._eval_start = self.eval_loader.get_state()
+
+    def _open_state(self, model: ModelWeights | None) -> None:
+        t = self.tcfg
+        if t.resume_from is None:
+            assert model is not None, "a new run needs initial weights"
+            self.start_step, self.state = 0, init_train_state(model, self.mcfg, t)
+            if self.primary:
+                for name in RUN_ARTIFACTS:
+                    (self.out / name).unlink(missing_ok=True)
+            return
+        path = resolve_checkpoint(t.resume_from)
+        check_resume(path, self.signature)
+        restored = load_train_state(path, self.mcfg, t, device=self.device, rt=self.rt)
+        self.state, self.start_step = restored.state, restored.step
+        self.loader.set_state(restored.loader_state)
+        if self.primary:   # the logs are cut back to what the checkpoint had seen
             for name, text in checkpoint_run_config(path)["run_artifacts"].items():
-                (run_dir / name).write_text(text)
-            print(f"Resumed from {path} at step {start_step:,}")
+                (self.out / name).write_text(text)
+            print(f"Resumed from {path} at step {self.start_step:,}")
 
-    run_config = _jsonable({"model": mcfg.to_dict(), "training": asdict(tcfg), "resume_signature": signature})
-    if primary:
-        (run_dir / "config.json").write_text(json.dumps(run_config, indent=2))
-
-    acc = tcfg.accumulation_steps
-    tokens_per_step = acc * tcfg.batch_size * mcfg.seq_len
-    build_start = time.perf_counter()
-    stepper = Stepper(state, mcfg, tcfg, device=device, rt=rt)
-    hooks.on_lowered(stepper)
-    hooks.on_compiled(stepper, {"lower_seconds": 0.0, "xla_compile_seconds": 0.0, "total_seconds": time.perf_counter() - build_start})
-    metrics = MetricsLogger(run_dir, tokens_per_step=tokens_per_step, initial_step=start_step, enabled=primary)
-
-    def due(every: int | None, step: int) -> bool:
-        return step == tcfg.steps or (every is not None and step % every == 0)
-
-    def evaluate(step: int) -> None:
-        eval_loader.set_state(eval_start)
-        batches = ((local_rows(x), local_rows(y)) for x, y in eval_loader)
-        metrics.log_eval(step, run_validation(stepper, batches, eval_batches=tcfg.eval_batches, microbatches=acc))
-
-    if tcfg.sample_every is not None:
+    def _build_sampler(self):
         from lyra_b200.generate import sample_eval_step
         from lyra_b200.tokenizer import LyraTokenizer
 
-        tokenizer = LyraTokenizer()
-        encoded = [[tokenizer.eos_token, *tokenizer.encode_ordinary(prompt)] for prompt in tcfg.sample_prompts]
+        tok = LyraTokenizer()
+        prompts = [(text, [tok.eos_token, *tok.encode_ordinary(text)]) for text in self.tcfg.sample_prompts]
 
         def sample(step: int) -> None:
-            for index, (prompt, ids) in enumerate(zip(tcfg.sample_prompts, encoded)):
-                tokens = sample_eval_step(state.params, ids, index, tcfg.sample_tokens, mcfg, device=device, rt=rt)
-                completion = tokenizer.decode(tokens[: tokens.index(tokenizer.eos_token)] if tokenizer.eos_token in tokens else tokens)
-                record = {"step": step, "total_tokens": step * tokens_per_step, "prompt": prompt, "completion": completion}
-                if primary:
-                    with (run_dir / "samples.jsonl").open("a") as stream:
-                        stream.write(json.dumps(record, ensure_ascii=False) + "\n")
-                    print(f"\n{RULE}\nstep {step:,} | {prompt}{completion}\n{RULE}\n")
+            for index, (text, ids) in enumerate(prompts):
+                new = sample_eval_step(self.state.params, ids, index, self.tcfg.sample_tokens, self.mcfg, device=self.device, rt=self.rt)
+                if tok.eos_token in new:
+                    new = new[: new.index(tok.eos_token)]
+                completion = tok.decode(new)
+                self._append("samples.jsonl", {"step": step, "total_tokens": step * self.tokens_per_step, "prompt": text, "completion": completion},
+                             ensure_ascii=False)
+                if self.primary:
+                    print(f"\n{RULE}\nstep {step:,} | {text}{completion}\n{RULE}\n")
 
-    probe = Probe(routing_only=True) if tcfg.numerics_every is not None else None
+        return sample
 
-    with metrics.paused():
-        if eval_loader is not None:
-            evaluate(start_step)
-        if tcfg.sample_every is not None:
-            sample(start_step)
-
-    # With several ranks every step starts with a host-side roll call through the rendezvous store: a rank that died or left
-    # is noticed before the next kernels (which would wait for it) are launched.
-    heartbeat = None
-    if rt is not None and rt.world > 1 and torch.distributed.is_available() and torch.distributed.is_initialized():
+    def _join_roll_call(self) -> None:
+        """Several ranks: every step starts with a host-side roll call through the rendezvous store, so a rank that died or left
+        is noticed before kernels that would wait for it are launched."""
+        rt = self.rt
+        if rt is None or rt.world <= 1 or not (torch.distributed.is_available() and torch.distributed.is_initialized()):
+            return
         from torch.distributed.distributed_c10d import _get_default_store
 
         from lyra_b200.parallel.health import Heartbeat
 
-        # one key space per call of train() in this process group: the farewell of an earlier run must not read as a lost peer
-        heartbeat = Heartbeat(_get_default_store(), rt.rank, rt.world, prefix=f"lyra/hb/{next(_RUN_COUNTER)}")
+        # one key space per run in this process group: the farewell of an earlier run must not read as a lost peer
+        self.heartbeat = Heartbeat(_get_default_store(), rt.rank, rt.world, prefix=f"lyra/hb/{next(_RUN_COUNTER)}")
 
-    rebalancing = tcfg.rebalance_experts_every is not None and rt is not None and rt.meter_expert_load()
+    # ------------------------------------------------------------------ helpers
+    def _append(self, name: str, record: dict, **json_kw) -> None:
+        if self.primary:
+            with (self.out / name).open("a") as stream:
+                stream.write(json.dumps(record, **json_kw) + "\n")
 
-    run_start = time.perf_counter()
-    try:
-        for step in range(start_step + 1, tcfg.steps + 1):
-            if heartbeat is not None:
-                heartbeat.beat(step)
-                heartbeat.check(step, timeout=float(tcfg.peer_timeout_seconds))
-            xs, ys = (np.stack(arrays) for arrays in zip(*(next(loader) for _ in range(acc))))
-            xs, ys = local_rows(xs), local_rows(ys)
-            if probe is not None and (step == 1 or due(tcfg.numerics_every, step)):
-                record = {"kind": "step", "step": step, "records": to_floats(stepper.numerics_step(xs[:1], probe))}
-                if primary:
-                    with (run_dir / "numerics.jsonl").open("a") as stream:
-                        stream.write(json.dumps(record) + "\n")
+    def _local_rows(self, a: np.ndarray) -> np.ndarray:
+        if self.data_ranks == 1:
+            return a
+        r = self.rt.data_rank
+        return a[..., r * self.local_batch:(r + 1) * self.local_batch, :]
 
-            hooks.before_step(step, step - 1, state, xs, ys)
-            timed = hooks.times_step(step)
-            step_start = time.perf_counter()
-            with hooks.step_scope(step):
-                aux = stepper.train_step(xs, ys, step - 1)
-                if timed and device.type == "cuda":
-                    torch.cuda.synchronize()
-            metrics.record(aux)
-            hooks.after_step(step, state, aux, time.perf_counter() - step_start if timed else None)
-            if rebalancing and step % tcfg.rebalance_experts_every == 0 and step < tcfg.steps:
-                moved = rt.rebalance_experts(stepper.params, state.optimizer, min_gain=tcfg.rebalance_min_gain)
-                metrics.log_event("experts", step, moved)
-                if primary and moved["layers_moved"]:
-                    print(f"\n[experts] step {step:,}: re-placed {moved['layers_moved']} layers; heaviest rank's share of the tokens "
-                          f"{moved['max_share_before']:.3f} -> {moved['max_share_after']:.3f} (balanced: {1 / rt.world:.3f})")
+    def _next_batch(self) -> tuple[np.ndarray, np.ndarray]:
+        pairs = [next(self.loader) for _ in range(self.tcfg.accumulation_steps)]
+        return self._local_rows(np.stack([x for x, _ in pairs])), self._local_rows(np.stack([y for _, y in pairs]))
 
-            checkpoint = due(tcfg.checkpoint_every, step)
-            evaluating = eval_loader is not None and due(tcfg.eval_every, step)
-            sampling = tcfg.sample_every is not None and due(tcfg.sample_every, step)
-            if step == start_step + 1 or step % tcfg.log_every == 0 or checkpoint or evaluating:
-                metrics.log_train(step)
-            with metrics.paused() if checkpoint or evaluating or sampling else nullcontext():
-                if checkpoint:
-                    artifacts = {name: (run_dir / name).read_text() for name in RUN_ARTIFACTS if (run_dir / name).exists()}
-                    save_checkpoint(out, step, state, loader.get_state(), run_config | {"run_artifacts": artifacts},
-                                    keep=tcfg.checkpoint_keep, rt=rt)
-                    hooks.on_checkpoint(step, out, run_dir)
+    def device_health(self) -> None:
+        """Kernels report a wait that ran out (a peer flag, a TMA stage) or an overflowing expert receive buffer through a
+        status word instead of trapping; reading it synchronises, so it is read where the loop synchronises anyway. A bad
+        status raises: the step's results are garbage and must reach neither the log nor a checkpoint."""
+        if self.device.type == "cuda":
+            from lyra_b200.ops import native
+
+            native.check_status()
+
+    # ------------------------------------------------------------------ side jobs
+    def evaluate(self, step: int) -> None:
+        self.eval_loader.set_state(self._eval_start)
+        batches = ((self._local_rows(x), self._local_rows(y)) for x, y in self.eval_loader)
+        result = run_validation(self.stepper, batches, eval_batches=self.tcfg.eval_batches, microbatches=self.tcfg.accumulation_steps)
+        self.device_health()
+        self.metrics.log_eval(step, result)
+
+    def save(self, step: int) -> None:
+        self.device_health()
+        artifacts = {name: (self.out / name).read_text() for name in RUN_ARTIFACTS if (self.out / name).exists()}
+        save_checkpoint(self.out, step, self.state, self.loader.get_state(), self.run_config | {"run_artifacts": artifacts},
+                        keep=self.tcfg.checkpoint_keep, rt=self.rt)
+        self.hooks.on_checkpoint(step, self.out, self.out)
+
+    def replace_experts(self, step: int) -> None:
+        moved = self.rt.rebalance_experts(self.stepper.params, self.state.optimizer, min_gain=self.tcfg.rebalance_min_gain)
+        self.metrics.log_event("experts", step, moved)
+        if self.primary and moved["layers_moved"]:
+            print(f"\n[experts] step {step:,}: re-placed {moved['layers_moved']} layers; heaviest rank's share of the tokens "
+                  f"{moved['max_share_before']:.3f} -> {moved['max_share_after']:.3f} (balanced: {1 / self.rt.world:.3f})")
+
+    def before_first_step(self) -> None:
+        with self.metrics.paused():
+            if self.eval_loader is not None:
+                self.evaluate(self.start_step)
+            if self._sampler is not None:
+                self._sampler(self.start_step)
+
+    # ------------------------------------------------------------------ one step
+    def advance(self, step: int) -> None:
+        if self.heartbeat is not None:
+            self.heartbeat.beat(step)
+            self.heartbeat.check(step, timeout=float(self.tcfg.peer_timeout_seconds))
+        xs, ys = self._next_batch()
+        if self.probe is not None and self.due.numerics(step):
+            self._append("numerics.jsonl", {"kind": "step", "step": step, "records": to_floats(self.stepper.numerics_step(xs[:1], self.probe))})
+
+        hooks = self.hooks
+        hooks.before_step(step, step - 1, self.state, xs, ys)
+        timed = hooks.times_step(step)
+        began = time.perf_counter()
+        with hooks.step_scope(step):
+            aux = self.stepper.train_step(xs, ys, step - 1)
+            if timed and self.device.type == "cuda":
+                torch.cuda.synchronize()
+        self.metrics.record(aux)
+        hooks.after_step(step, self.state, aux, time.perf_counter() - began if timed else None)
+        if self.rebalancing and self.due.rebalance(step):
+            self.replace_experts(step)
+
+        saving, evaluating, sampling = self.due.checkpoint(step), self.due.evaluation(step), self.due.sampling(step)
+        if self.due.log_line(step):
+            self.device_health()
+            self.metrics.log_train(step)
+        if saving or evaluating or sampling:
+            with self.metrics.paused():
+                if saving:
+                    self.save(step)
                 if evaluating:
-                    evaluate(step)
+                    self.evaluate(step)
                 if sampling:
-                    sample(step)
-    finally:
-        if heartbeat is not None:   # finished or failed: tell the others now, so that none of them waits out its time limit
+                    self._sampler(step)
+
+    def close(self) -> None:
+        if self.heartbeat is not None:   # finished or failed: tell the others now, so that none of them waits out its time limit
             try:
-                heartbeat.leave()
+                self.heartbeat.leave()
             except Exception:
                 pass
-        metrics.close()
-        loader.close()
-        if eval_loader is not None:
-            eval_loader.close()
+        if self.metrics is not None:
+            self.metrics.close()
+        for loader in (self.loader, self.eval_loader):
+            if loader is not None:
+                loader.close()
 
-    if primary:
-        plot_run(run_dir)
-        print(f"{RULE}\nTraining finished in {format_duration(time.perf_counter() - run_start)}\n{RULE}")
-    return state
+
+def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *, hooks: TrainHooks | None = None, rt=None,
+          device=None) -> TrainState:
+    """Runs (or resumes) training to ``tcfg.steps`` and returns the final state."""
+    run = TrainingRun(model, mcfg, tcfg, hooks or TrainHooks(), rt, device)
+    began = time.perf_counter()
+    try:
+        run.before_first_step()
+        for step in range(run.start_step + 1, tcfg.steps + 1):
+            run.advance(step)
+    finally:
+        run.close()
+    if run.primary:
+        plot_run(run.out)
+        print(f"{RULE}\nTraining finished in {format_duration(time.perf_counter() - began)}\n{RULE}")
+    return run.state

@@ -76,3 +76,27 @@ def test_special_tokens_and_batch(tokenizer):
     assert tokenizer.encode_ordinary_batch(texts) == [tokenizer.encode_ordinary(t) for t in texts]
     ids = tokenizer.encode_ordinary("tokenization")
     assert b"".join(tokenizer.decode_single_token_bytes(i) for i in ids).decode() == "tokenization"
+
+
+def test_prepare_script_tokenizes_local_files_up_to_the_budget(tmp_path):
+    import importlib.util
+    import json
+    import sys
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("prepare_climbmix", Path(__file__).resolve().parents[1] / "data" / "prepare_climbmix.py")
+    prep = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = prep
+    spec.loader.exec_module(prep)
+    (tmp_path / "a.txt").write_text("the quick brown fox jumps over the lazy dog " * 4)
+    (tmp_path / "b.jsonl").write_text("\n".join(json.dumps({"text": f"document number {i} " * 30}) for i in range(5)))
+    out = tmp_path / "shards"
+    assert prep.main(["--text-files", str(tmp_path / "a.txt"), str(tmp_path / "b.jsonl"), "--output", str(out), "--max-tokens", "700",
+                      "--tokens-per-shard", "256", "--num-threads", "1"]) == 0
+    shards = sorted(out.glob("*.array_record"))
+    lengths = [np.load(str(s) + ".lengths.npy") for s in shards]
+    assert sum(int(n.sum()) for n in lengths) == 700 and [int(n.sum()) for n in lengths] == [256, 256, 188]
+    tok = LyraTokenizer()
+    stream = TokenBlocks(out, 1, 8).read(0, 700)
+    first = tok.encode_ordinary("the quick brown fox jumps over the lazy dog " * 4)
+    assert stream[:len(first)].tolist() == first and stream[len(first)] == tok.eos_token

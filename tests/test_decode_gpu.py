@@ -123,20 +123,50 @@ def test_decode_gemm_grouped(quant, shape):
     bias = torch.randn(G, N, device="cuda")
     wq = quantize(w.float(), torch.float8_e4m3fn, block=(64, 64)) if quant else w
     wref = (dequantize(wq, torch.bfloat16) if quant else w).float()
+    # quantised weights run e4m3 x e4m3 on the tensor cores: the activations are quantised too, one scale per (row, 64 k values),
+    # so the exact reference uses the same quantised activations; against unquantised activations the error is that of e4m3
+    xref = dequantize(quantize(x, torch.float8_e4m3fn, block=(1, 64)), torch.float32) if quant and decode.F8_TENSOR_CORES else x.float()
     off_dev = offsets.cuda()
     for swiglu in (False, True):
         y = decode.decode_gemm(x, wq, offsets=off_dev, bias=bias, swiglu=swiglu)
         native.check_status()
-        ref = torch.empty(R, N, device="cuda")
+        assert torch.equal(y, decode.decode_gemm(x, wq, offsets=off_dev, bias=bias, swiglu=swiglu))
+        ref, loose = torch.empty(R, N, device="cuda"), torch.empty(R, N, device="cuda")
         for g in range(G):
             a, b = int(offsets[g]), int(offsets[g + 1])
             if b > a:
-                ref[a:b] = x[a:b].float() @ wref[g] + bias[g]
+                ref[a:b] = xref[a:b] @ wref[g] + bias[g]
+                loose[a:b] = x[a:b].float() @ wref[g] + bias[g]
         if swiglu:
-            ref = _swiglu_ref(ref, 1.702, 7.0)
+            ref, loose = _swiglu_ref(ref, 1.702, 7.0), _swiglu_ref(loose, 1.702, 7.0)
         assert y.shape == ref.shape
         err = (y.float() - ref).abs().max().item()
         assert err < 3e-2 * max(1.0, ref.abs().max().item()), err
+        assert ((y.float() - loose).norm() / loose.norm()).item() < 6e-2
+
+
+def test_decode_gemm_f8_tensor_core_kernel_matches_the_dequantising_kernel(monkeypatch):
+    """The same e4m3 weights through both kernels (tcgen05 with e4m3 activations / mma.sync with bf16 activations), 256-wide scale
+    blocks and more than 64 rows in one group (several token blocks per weight panel)."""
+    from lyra_b200.nn.quant import dequantize, quantize
+    from lyra_b200.ops import decode, native
+
+    torch.manual_seed(3)
+    G, K, N, R = 4, 1024, 1536, 200
+    counts = torch.tensor([150, 0, 49, 1])
+    offsets = torch.zeros(G + 1, dtype=torch.int32)
+    offsets[1:] = torch.cumsum(counts, 0)
+    x = torch.randn(R, K, device="cuda").bfloat16()
+    wq = quantize(torch.randn(G, K, N, device="cuda") / K ** 0.5, torch.float8_e4m3fn, block=(256, 256))
+    y_tc = decode.decode_gemm(x, wq, offsets=offsets.cuda())
+    monkeypatch.setattr(decode, "F8_TENSOR_CORES", False)
+    y_sm = decode.decode_gemm(x, wq, offsets=offsets.cuda())
+    native.check_status()
+    xq = dequantize(quantize(x, torch.float8_e4m3fn, block=(1, 256)), torch.float32)
+    wref = dequantize(wq, torch.bfloat16).float()
+    ref = torch.cat([xq[int(offsets[g]):int(offsets[g + 1])] @ wref[g] for g in range(G)])
+    assert (y_tc.float() - ref).abs().max().item() < 3e-2
+    assert ((y_tc.float() - y_sm.float()).norm() / y_sm.float().norm()).item() < 6e-2
 
 
 def test_decode_gemm_dense_split_k():
@@ -221,4 +251,4 @@ def test_decode_moe_quantised_experts_match_dequantised_weights():
         a = decode.decode_moe(xn, scores, indices, up_q, None, down_q, None, 1.702, 7.0)
         b = cuda_ops.moe_experts(xn, scores, indices, dequantize(up_q, torch.bfloat16).view(E, C, 2, H), None,
                                  dequantize(down_q, torch.bfloat16), None, 1.702, 7.0)
-    assert (a.float() - b.float()).abs().max().item() < 3e-2
+    assert ((a.float() - b.float()).norm() / b.float().norm()).item() < 8e-2    # e4m3 activations in both products of the quantised path

@@ -6,6 +6,7 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+TOLERANCE = 0.10   # relative L2 error of any leaf's gradient; both paths compute in bf16 and take the same routing (measured: up to 0.08)
 
 
 def _cfgs():
@@ -21,7 +22,7 @@ def _cfgs():
 
 
 @pytest.mark.parametrize("name", ["tiny", "mid", "dense"])
-def test_loss_and_grads_match_torch_path(name):
+def test_loss_and_grads_match_torch_path(name, monkeypatch):
     from lyra_b200.model import ModelWeights
     from lyra_b200.nn.params import tree_dict
     from lyra_b200.ops import native
@@ -32,7 +33,12 @@ def test_loss_and_grads_match_torch_path(name):
     tokens = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len), device="cuda")
     labels = torch.randint(0, cfg.vocab_size, (2, cfg.seq_len), device="cuda")
     results = {}
+    import lyra_b200.model as M
+
+    tape = {"replay": False, "choices": []}    # the kernel path takes the experts the PyTorch path chose: no top-k flips between them
+    monkeypatch.setattr(M, "ROUTING_TAPE", tape)
     for impl in ("torch", "auto"):
+        tape["replay"] = impl == "auto"
         c = replace(cfg, implementation=impl)
         w = ModelWeights.init(1, c, device="cuda")
         leaves = tree_dict(w)
@@ -54,14 +60,8 @@ def test_loss_and_grads_match_torch_path(name):
     for p in g0:
         denom = g0[p].norm().clamp_min(1e-6)
         err = ((g0[p] - g1[p]).norm() / denom).item()
-        # router gradients are sums of many small terms of either sign and flip with near-tie top-k choices,
-        # so they are checked by direction (and exactly, with fixed routing, in test_moe_experts_op)
-        if "router" in p:
-            cos = torch.nn.functional.cosine_similarity(g0[p].reshape(-1), g1[p].reshape(-1), dim=0).item()
-            if cos < 0.8:
-                bad.append((p, err, cos))
-        elif err > (0.25 if (name != "dense" or p.endswith(("xsa_alpha", "sinks"))) else 0.08):  # top-k flips between the two bf16 paths perturb MoE models
-            bad.append((p, err))
+        if err > TOLERANCE:
+            bad.append((p, round(err, 4)))
     assert not bad, bad
 
 

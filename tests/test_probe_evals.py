@@ -46,7 +46,18 @@ def test_scorer_masks_only_the_continuation_and_evaluate_scores():
     scorer = Scorer(ModelWeights.init(0, c), c, batch_size=4)
     docs = [Doc("Question: 1+1?\nAnswer:", ("2", "3", "4"), 0, True), Doc("Question: sky?\nAnswer:", ("blue", "green"), 0, True)]
     reqs = scorer.requests(docs)
-    assert len(reqs) == 5 and all(ids[0] == scorer.tokenizer.eos_token for _, _, ids, _ in reqs)
+    assert len(reqs) == 5 and all(r.ids[0] == scorer.tokenizer.eos_token for r in reqs)
+    assert [(r.doc, r.choice) for r in reqs] == [(0, 0), (0, 1), (0, 2), (1, 0), (1, 1)]
+    tok = scorer.tokenizer
+    assert all(tok.decode(r.ids[r.scored_from:]) == " " + docs[r.doc].choices[r.choice] for r in reqs)   # only the choice is scored
+    # a context that does not fit loses tokens from the left; the continuation is kept whole
+    long_doc = Doc("word " * 200 + "Answer:", ("yes",), 0)
+    (r,) = scorer.requests([long_doc])
+    assert len(r.ids) == c.seq_len and tok.decode(r.ids[r.scored_from:]) == " yes"
+    # the order in which requests are batched does not change a request's score
+    one_by_one = Scorer(scorer.model, c, batch_size=1).score(docs)
+    together = scorer.score(docs)
+    assert all(abs(a - b) < 1e-3 * max(1.0, abs(a)) for x, y in zip(one_by_one, together) for a, b in zip(x, y))
     res = evaluate("toy", docs, scorer)
     assert res.num_docs == 2 and 0.0 <= res.acc <= 1.0 and res.acc_norm is not None
     assert "acc_norm" in str(res)
