@@ -27,6 +27,9 @@ from pathlib import Path
 
 os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 os.environ.setdefault("LYRA_LOG_KERNELS", "0")
+# kernels are loaded when the library is, not at their first launch: a first launch that has to load code can stall the host while
+# this rank's peers already spin in (bounded) waits for it
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))

@@ -52,6 +52,31 @@ def time_ms(fn, iters: int = 10, warmup: int = 3) -> float:
     return statistics.median(times)
 
 
+def time_graph_ms(fn, iters: int = 10) -> float:
+    """Device time of ``fn`` replayed from a CUDA graph (the way the decode loop runs it): no host launch gaps between its kernels."""
+    global _flush
+    if _flush is None:
+        _flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            fn()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        fn()
+    times = []
+    for _ in range(iters + 2):
+        _flush.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        graph.replay()
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+    return statistics.median(times[2:])
+
+
 def report(name: str, ms: float, flops: float = 0.0, bytes_: float = 0.0, ref_ms: float | None = None) -> dict:
     pk = peaks()
     row = {"kernel": name, "ms": round(ms, 4)}
@@ -209,10 +234,17 @@ def bench_decode_gemm():
             os.environ["LYRA_DECODE_PANEL"] = str(panel)
             report(f"decode gemm bf16 {name} G{G} K{K} N{N} rows/group {rows_per} panel{panel}",
                    time_ms(lambda: decode.decode_gemm(x, w, offsets=offsets)), bytes_=2.0 * G * K * N)
+            if panel == 128:
+                report(f"decode gemm bf16 {name} G{G} K{K} N{N} rows/group {rows_per} panel{panel} (CUDA graph replay)",
+                       time_graph_ms(lambda: decode.decode_gemm(x, w, offsets=offsets, max_group_rows=rows_per)), bytes_=2.0 * G * K * N)
         os.environ.pop("LYRA_DECODE_PANEL", None)
         w8 = quantize(w, torch.float8_e4m3fn, block=(64, 64))
-        report(f"decode gemm e4m3 {name} G{G} K{K} N{N} rows/group {rows_per}",
-               time_ms(lambda: decode.decode_gemm(x, w8, offsets=offsets)), bytes_=1.0 * G * K * N)
+        for tc in (False, True):     # mma.sync kernel that dequantises in flight / tcgen05 e4m3 x e4m3 kernel (activation quantisation included)
+            decode.F8_TENSOR_CORES = tc
+            report(f"decode gemm e4m3 {'tcgen05' if tc else 'dequantise + mma.sync'} {name} G{G} K{K} N{N} rows/group {rows_per}",
+                   time_ms(lambda: decode.decode_gemm(x, w8, offsets=offsets, max_group_rows=rows_per)), bytes_=1.0 * G * K * N)
+            report(f"decode gemm e4m3 {'tcgen05' if tc else 'dequantise + mma.sync'} {name} G{G} K{K} N{N} rows/group {rows_per} (CUDA graph replay)",
+                   time_graph_ms(lambda: decode.decode_gemm(x, w8, offsets=offsets, max_group_rows=rows_per)), bytes_=1.0 * G * K * N)
         del w, w8
 
 
@@ -281,7 +313,17 @@ def _one_decode_gemm():
     return lambda: decode.decode_gemm(x, w, offsets=offsets)
 
 
-ONE = {"decode_gemm": _one_decode_gemm, "gemm": _one_gemm, "flash_fwd": lambda: _one_attention(False), "flash_bwd": lambda: _one_attention(True),
+def _one_decode_gemm_f8():
+    from lyra_b200.nn.quant import quantize
+    from lyra_b200.ops import decode
+    G_, K, N, rows = 32, 2880, 5760, 8
+    x = torch.randn(G_ * rows, K, device="cuda").bfloat16()
+    w8 = quantize((torch.randn(G_, K, N, device="cuda") / K ** 0.5).bfloat16(), torch.float8_e4m3fn, block=(64, 64))
+    offsets = torch.arange(G_ + 1, device="cuda", dtype=torch.int32) * rows
+    return lambda: decode.decode_gemm(x, w8, offsets=offsets, max_group_rows=rows)
+
+
+ONE = {"decode_gemm": _one_decode_gemm, "decode_gemm_f8": _one_decode_gemm_f8, "gemm": _one_gemm, "flash_fwd": lambda: _one_attention(False), "flash_bwd": lambda: _one_attention(True),
        "flash_fwd_window": lambda: _one_attention(False, 128), "ce": _one_ce, "rmsnorm": _one_rmsnorm, "moe_up": _one_moe, "decode": lambda: _one_decode()}
 
 

@@ -18,10 +18,12 @@ from __future__ import annotations
 import argparse
 import json
 import os
+
 import sys
 from dataclasses import replace
 from pathlib import Path
 
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")   # load kernels with the library, not at first launch (multi-rank waits)
 import torch
 
 ROOT = Path(__file__).resolve().parents[1]
@@ -46,7 +48,9 @@ def timed(fn) -> tuple[float, object]:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--variant", default="gpt-oss-20b")
-    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--batch", type=int, default=64, help="prompts per rank (expert parallel: every rank serves its own batch)")
+    ap.add_argument("--global-batch", type=int, default=0,
+                    help="prompts served by the whole job, split evenly over the ranks (overrides --batch; the gpt-oss-120b headline is 64 over 8 ranks)")
     ap.add_argument("--prompt", type=int, default=1024)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (0 = all)")
@@ -66,6 +70,10 @@ def main() -> None:
     from lyra_b200.variants import model_variant
 
     world, rank = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0"))
+    if args.global_batch:
+        if args.global_batch % world and not args.tensor_parallel:
+            raise SystemExit(f"--global-batch {args.global_batch} does not split over {world} ranks")
+        args.batch = args.global_batch if args.tensor_parallel else args.global_batch // world
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -150,7 +158,7 @@ def main() -> None:
     bw, kind = hbm_gbs()
     step_ms = results[best]["decode_ms"] / steps
     line = {
-        "bench": "batched serve", "n_gpus": world, "parallelism": (f"tp{world}" if tp else f"ep{world} + data-parallel attention") if world > 1 else "single", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch": args.batch,
+        "bench": "batched serve", "n_gpus": world, "parallelism": (f"tp{world}" if tp else f"ep{world} + data-parallel attention") if world > 1 else "single", "model": mcfg.name, "layers": mcfg.n_layers, "params": param_count(ModelWeights.spec(mcfg)), "batch_per_rank": args.batch, "global_batch": served * args.batch,
         "prompt_len": args.prompt, "new_tokens": args.new, "dtype": "bf16" + (" + e4m3 experts and KV" if args.fp8 else ""), "data": "synthetic tokens, random-init weights",
         "prefill_tokens_per_s": round(served * args.batch * args.prompt / results[best]["prefill_ms"] * 1e3, 1),
         "decode_tokens_per_s": round(served * args.batch * steps / results[best]["decode_ms"] * 1e3, 1),

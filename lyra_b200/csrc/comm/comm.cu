@@ -23,9 +23,10 @@
 namespace lyra {
 
 constexpr int MAX_RANKS = 16;
-constexpr long long PEER_WAIT_NS = 2000000000LL;  // 2 s
+constexpr long long PEER_WAIT_NS = 10000000000LL;  // 10 s: absorbs a peer whose host is busy (first-step allocations); tests pass shorter limits
 constexpr int STATUS_PEER_TIMEOUT = 4;
 constexpr int STATUS_EP_OVERFLOW = 6;
+constexpr int STATUS_RETURN_TIMEOUT = 8;
 
 struct PeerPtrs {
   void* p[MAX_RANKS];
@@ -101,6 +102,69 @@ __global__ void reduce_pull_kernel(void* __restrict__ out, PeerPtrs peers, int w
       reinterpret_cast<float4*>(out)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
       reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
     }
+  }
+}
+
+// The same rank-ordered sum, plus the sum of squares of the result on the way out (the optimizer's global-norm gate and Muon's
+// per-matrix RMS clip need it; computing it here saves two more passes over every reduced gradient). A leaf may interleave
+// `n_seg` (1 or 2) matrices in runs of `seg_len` elements (the gate and linear halves of a `[C, 2, H]` up-projection):
+// partial[block][s] receives the block's sum for matrix s; the caller adds the blocks up in order.
+template <bool IN_BF16, bool OUT_BF16>
+__global__ void reduce_pull_norm_kernel(void* __restrict__ out, PeerPtrs peers, int world, long long n, long long seg_len, int n_seg,
+                                        float* __restrict__ partial) {
+  __shared__ float red[2][32];
+  const long long n8 = n / 8;
+  float sq[2] = {0.f, 0.f};
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int r = 0; r < world; ++r) {
+      if (IN_BF16) {
+        const uint4 v = reinterpret_cast<const uint4*>(peers.p[r])[i];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(h[k]);
+          acc[2 * k] += f.x;
+          acc[2 * k + 1] += f.y;
+        }
+      } else {
+        const float4 a = reinterpret_cast<const float4*>(peers.p[r])[2 * i], b = reinterpret_cast<const float4*>(peers.p[r])[2 * i + 1];
+        acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+        acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+      }
+    }
+    float s = 0.f;
+    if (OUT_BF16) {
+      uint4 o;
+      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        h[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+        const float2 f = __bfloat1622float2(h[k]);   // the norm of what is stored
+        s += f.x * f.x + f.y * f.y;
+      }
+      reinterpret_cast<uint4*>(out)[i] = o;
+    } else {
+#pragma unroll
+      for (int k = 0; k < 8; ++k) s += acc[k] * acc[k];
+      reinterpret_cast<float4*>(out)[2 * i] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+    const int seg = n_seg > 1 ? int(((i * 8) / seg_len) % n_seg) : 0;
+    sq[seg] += s;
+  }
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    float v = sq[t];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    if ((threadIdx.x & 31) == 0) red[t][threadIdx.x >> 5] = v;
+  }
+  __syncthreads();
+  if (threadIdx.x < 2) {
+    float v = 0.f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) v += red[threadIdx.x][w];
+    partial[blockIdx.x * 2 + threadIdx.x] = v;
   }
 }
 
@@ -453,7 +517,7 @@ __global__ void wait_arrivals_kernel(const int* __restrict__ arrived, int* __res
   while (ld_acquire_sys(arrived) - want < 0) {
     if (*reinterpret_cast<volatile int*>(status) != 0) return;   // an earlier kernel already failed (e.g. rows dropped on overflow): do not wait for them
     if (now_ns() - start > limit_ns) {
-      atomicCAS(status, 0, STATUS_PEER_TIMEOUT);
+      atomicCAS(status, 0, STATUS_RETURN_TIMEOUT);
       return;
     }
     __nanosleep(200);
@@ -634,6 +698,24 @@ extern "C" int lyra_wait_arrivals(const int* arrived, int* expect, int add, int*
   long long ns = (long long)limit_ms * 1000000LL;
   if (ns <= 0 || ns > PEER_WAIT_NS) ns = PEER_WAIT_NS;
   wait_arrivals_kernel<<<1, 32, 0, ST(stream)>>>(arrived, expect, add, status, ns);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+// `lyra_reduce_pull` that also writes per-block sums of squares of the result: partial [grid, 2] fp32 where grid is the return
+// value of `lyra_reduce_pull_norm_blocks(n)`; seg_len must be a multiple of 8 when n_seg == 2.
+extern "C" int lyra_reduce_pull_norm_blocks(long long n) { return copy_grid(n / 8); }
+
+extern "C" int lyra_reduce_pull_norm(void* out, const long long* peer_ptrs, int world, long long n, int in_bf16, int out_bf16, long long seg_len, int n_seg,
+                                     float* partial, void* stream) {
+  if (n <= 0) return 0;
+  if (n % 8 || world > MAX_RANKS || n_seg < 1 || n_seg > 2 || (n_seg == 2 && (seg_len <= 0 || seg_len % 8))) return -51;
+  const PeerPtrs p = make_ptrs(peer_ptrs, world);
+  const int grid = copy_grid(n / 8);
+  if (in_bf16 && out_bf16) reduce_pull_norm_kernel<true, true><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
+  else if (in_bf16) reduce_pull_norm_kernel<true, false><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
+  else if (out_bf16) reduce_pull_norm_kernel<false, true><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
+  else reduce_pull_norm_kernel<false, false><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

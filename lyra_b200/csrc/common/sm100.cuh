@@ -15,6 +15,9 @@ namespace lyra {
 
 // ~2 s at 1.9 GHz; intra-CTA waits finish in microseconds.
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;
+// Waits for another GPU absorb the skew between ranks, which in a first step (allocations, handle exchanges, kernel loading on
+// the host side of a peer) can reach seconds: ~10 s. Still bounded: a dead peer costs this once, then the status word is set.
+constexpr long long PEER_WAIT_LIMIT_CYCLES = 20000000000LL;
 
 enum StatusCode : int {
   STATUS_OK = 0,
@@ -23,6 +26,9 @@ enum StatusCode : int {
   STATUS_TIMEOUT_TMEM = 3,    // epilogue / MMA gave up waiting for an accumulator
   STATUS_TIMEOUT_PEER = 4,    // gave up waiting for a flag written by another GPU
   STATUS_BAD_ARGUMENT = 5,
+  STATUS_EP_OVERFLOW_ = 6,    // (set by the exchange layout kernel) receive buffer too small
+  STATUS_TIMEOUT_TILE = 7,    // a grouped GEMM gave up waiting for the rows of a tile that other GPUs store
+  STATUS_TIMEOUT_RETURN = 8,  // gave up waiting for the rows this GPU dispatched to come back
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {

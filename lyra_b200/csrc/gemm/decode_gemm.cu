@@ -19,9 +19,9 @@
 // can. The operand roles are swapped: the accumulator tile is D^T[128 weight columns x NTOK tokens] = W^T x^T, with the
 // e4m3 weight panel as the 128-row A operand (TMA, [K, N] storage = MN-major) and the tokens, quantised to e4m3 with one
 // scale per (row, K block) like the reference's `quantize(lhs, (1, scale_k))`, as the narrow B operand. Scales are applied
-// in software: every K block of `bk` values accumulates into one of two TMEM accumulators (kind::f8f6f4, fp32), the four
-// epilogue warps read it back (tcgen05.ld), multiply by w_scale[k block, column block] * x_scale[token, k block] and add
-// into fp32 registers while the tensor core already works on the next K block in the other accumulator.
+// in software: every K block of `bk` values accumulates into its own TMEM accumulator of a ring of four or eight
+// (kind::f8f6f4, fp32), the four epilogue warps read it back (tcgen05.ld), multiply by w_scale[k block, column block] *
+// x_scale[token, k block] and add into fp32 registers while the tensor core already works on the following K blocks.
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -203,10 +203,16 @@ __global__ void __launch_bounds__(THREADS) decode_gemm_kernel(const DGParams p) 
 
 // out[r, c] = act(sum over splits of part[s, r, c] + bias[group(r), c]); with SwiGLU the N = 2H columns are gate | linear.
 // Without SwiGLU an optional residual is added after scaling: out = residual + alpha * (sum + bias).
-__global__ void decode_gemm_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias, const int* __restrict__ offsets,
-                                          __nv_bfloat16* __restrict__ out, int R, int N, int G, int splits, int swiglu, float beta, float limit,
-                                          const __nv_bfloat16* __restrict__ residual, float alpha) {
+// One CTA per (row, run of 1024 output columns), four columns per thread: the pass is a few megabytes, so it is all latency -
+// every thread has its loads in flight at once instead of walking the row.
+__global__ void __launch_bounds__(256) decode_gemm_finish_kernel(const float* __restrict__ part, const float* __restrict__ bias,
+                                                                 const int* __restrict__ offsets, __nv_bfloat16* __restrict__ out, int R, int N, int G,
+                                                                 int splits, int swiglu, float beta, float limit,
+                                                                 const __nv_bfloat16* __restrict__ residual, float alpha) {
   const int r = blockIdx.x;
+  const int H = swiglu ? N / 2 : N;
+  const int c0 = (blockIdx.y * 256 + threadIdx.x) * 4;
+  if (c0 >= H) return;
   int g = 0;
   if (offsets && bias) {
     int lo = 0, hi = G;                                          // last g with offsets[g] <= r
@@ -216,23 +222,41 @@ __global__ void decode_gemm_finish_kernel(const float* __restrict__ part, const 
     }
     g = lo;
   }
-  const int H = swiglu ? N / 2 : N;
-  for (int c = threadIdx.x; c < H; c += blockDim.x) {
-    float a = bias ? bias[static_cast<size_t>(g) * N + c] : 0.f;
-    float l = (swiglu && bias) ? bias[static_cast<size_t>(g) * N + H + c] : 0.f;
+  float a[4] = {0.f, 0.f, 0.f, 0.f}, l[4] = {0.f, 0.f, 0.f, 0.f};
+  const int n = min(4, H - c0);
+  if (n == 4 && (N & 3) == 0 && (H & 3) == 0) {
     for (int s = 0; s < splits; ++s) {
       const float* row = part + (static_cast<size_t>(s) * R + r) * N;
-      a += row[c];
-      if (swiglu) l += row[H + c];
+      const float4 v = *reinterpret_cast<const float4*>(row + c0);
+      a[0] += v.x; a[1] += v.y; a[2] += v.z; a[3] += v.w;
+      if (swiglu) {
+        const float4 w = *reinterpret_cast<const float4*>(row + H + c0);
+        l[0] += w.x; l[1] += w.y; l[2] += w.z; l[3] += w.w;
+      }
+    }
+  } else {
+    for (int s = 0; s < splits; ++s) {
+      const float* row = part + (static_cast<size_t>(s) * R + r) * N;
+      for (int i = 0; i < n; ++i) {
+        a[i] += row[c0 + i];
+        if (swiglu) l[i] += row[H + c0 + i];
+      }
+    }
+  }
+  for (int i = 0; i < n; ++i) {
+    float av = a[i], lv = l[i];
+    if (bias) {
+      av += bias[static_cast<size_t>(g) * N + c0 + i];
+      if (swiglu) lv += bias[static_cast<size_t>(g) * N + H + c0 + i];
     }
     if (swiglu) {
-      const float gc = fminf(a, limit), lc = fminf(fmaxf(l, -limit), limit);
-      a = (lc + 1.f) * gc / (1.f + __expf(-beta * gc));
+      const float gc = fminf(av, limit), lc = fminf(fmaxf(lv, -limit), limit);
+      av = (lc + 1.f) * gc / (1.f + __expf(-beta * gc));
     } else {
-      a *= alpha;
-      if (residual) a += __bfloat162float(residual[static_cast<size_t>(r) * N + c]);
+      av *= alpha;
+      if (residual) av += __bfloat162float(residual[static_cast<size_t>(r) * N + c0 + i]);
     }
-    out[static_cast<size_t>(r) * H + c] = __float2bfloat16(a);
+    out[static_cast<size_t>(r) * H + c0 + i] = __float2bfloat16(av);
   }
 }
 
@@ -265,6 +289,10 @@ constexpr int F8_THREADS = 192;              // warp 0: TMA, warp 1: MMA issue +
 constexpr int F8_MAX_KBLOCKS = 64;           // K blocks (scale rows) one CTA can hold
 
 constexpr int f8_stages(int ntok) { return ntok >= 64 ? 3 : 4; }   // sized so that two CTAs fit one SM (two weight streams in flight)
+// TMEM accumulators per CTA. One K block's round trip (MMA retires -> commit -> epilogue wakes -> tcgen05.ld -> release -> issuer
+// wakes) measured about 2 us, against 0.2 us of HBM time for the block's weights: the issuer must be able to run several K
+// blocks ahead of the epilogue, so the ring is as deep as the shared-memory stages hold K blocks.
+constexpr int f8_accs(int ntok) { return ntok >= 64 ? 4 : 8; }
 
 struct F8Params {
   const float* xs;          // [R, K / bk] activation scales
@@ -276,6 +304,12 @@ struct F8Params {
   int* status;
 };
 
+// One pass = one (128-column weight panel, group, K split, block of NTOK rows). A CTA walks its passes in a fixed order that all
+// of its roles derive independently; barriers, shared-memory stages and the accumulator ring run on across passes.
+struct F8Pass {
+  int n0, g, split, r0, cnt;
+};
+
 template <int NTOK>
 __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
                                                                    const F8Params p) {
@@ -284,28 +318,26 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
   constexpr int B_BYTES = NTOK * 128;                      // NTOK token rows x 128 k values
   constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   constexpr int F8_STAGES = f8_stages(NTOK);
-  constexpr uint32_t TMEM_COLS = 2 * NTOK < 32 ? 32 : 2 * NTOK;
+  constexpr int NACC = f8_accs(NTOK);
+  constexpr uint32_t TMEM_COLS = NACC * NTOK;              // 128 or 256: a power of two
   constexpr uint32_t IDESC = make_idesc(128, NTOK, 0, 0, 1, 0);   // e4m3 x e4m3, A (weights) MN-major, B (tokens) K-major
 
-  const int n0 = blockIdx.x * 128, g = blockIdx.y;
-  const int split = blockIdx.z % p.splits, zb = blockIdx.z / p.splits;
-  const int gbeg = p.offsets ? p.offsets[g] : 0;
-  const int gend = p.offsets ? (p.counts ? gbeg + p.counts[g] : p.offsets[g + 1]) : p.R;
-  const int r0 = gbeg + zb * NTOK;
-  if (r0 >= gend) return;                                  // group without rows (uniform for the CTA: before any barrier or TMEM use)
-  const int cnt = min(NTOK, gend - r0);
-  const int kbeg = split * p.k_per_split, kend = min(p.K, kbeg + p.k_per_split);
-  const int n_steps = (kend - kbeg) / 32;                  // MMAs (K = 32 each)
-  const int n_kb = (kend - kbeg) / p.bk;                   // K blocks = promotions
+  // Persistent: the grid is a couple of CTAs per SM and each takes work items (panel, group, split) round-robin, panels fastest so
+  // that CTAs running side by side read neighbouring 128-byte pieces of the same weight rows. (One CTA per item spent most of
+  // its life on TMEM allocation, barrier set-up and pipeline fill: 45 us per CTA for 17 us of weight streaming.)
+  const int n_panels = (p.N + 127) / 128;
+  const int n_items = n_panels * p.G * p.splits;
+  const int n_steps = p.k_per_split / 32;                  // MMAs (K = 32 each) per pass
+  const int n_kb = p.k_per_split / p.bk;                   // K blocks = read-backs per pass
   const int steps_per_kb = p.bk / 32;
-  const int kb0 = kbeg / p.bk;
-  const int ws_n = p.bn >= 128 ? 1 : 128 / p.bn;           // weight-scale columns this tile touches (its 128 columns start on a block boundary)
+  const int n_stage_loads = (p.k_per_split + F8_KSTAGE - 1) / F8_KSTAGE;
+  const int ws_n = p.bn >= 128 ? 1 : 128 / p.bn;           // weight-scale columns a panel touches (it starts on a block boundary)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   float* xs_s = reinterpret_cast<float*>(smem + F8_STAGES * STAGE_BYTES);        // [n_kb][NTOK]
   float* ws_s = xs_s + F8_MAX_KBLOCKS * NTOK;                                    // [n_kb][ws_n]
-  __shared__ uint64_t full_bar[F8_STAGES], empty_bar[F8_STAGES], tfull_bar[2], tempty_bar[2];
+  __shared__ uint64_t full_bar[F8_STAGES], empty_bar[F8_STAGES], tfull_bar[NACC], tempty_bar[NACC];
   __shared__ uint32_t tmem_base_holder;
   __shared__ int abort_flag;
 
@@ -315,7 +347,7 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
       mbar_init(smem_u32(&full_bar[s]), 1);
       mbar_init(smem_u32(&empty_bar[s]), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < NACC; ++a) {
       mbar_init(smem_u32(&tfull_bar[a]), 1);
       mbar_init(smem_u32(&tempty_bar[a]), 4);
     }
@@ -326,111 +358,190 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
     tmem_alloc(smem_u32(&tmem_base_holder), TMEM_COLS);
     tmem_relinquish();
   }
-  // scales of this CTA's K range: tokens x K blocks and K blocks x (one or two) column blocks
-  for (int i = threadIdx.x; i < n_kb * NTOK; i += F8_THREADS) {
-    const int kb = i / NTOK, t = i - kb * NTOK;
-    xs_s[i] = t < cnt ? p.xs[static_cast<size_t>(r0 + t) * (p.K / p.bk) + kb0 + kb] : 0.f;
-  }
-  for (int i = threadIdx.x; i < n_kb * ws_n; i += F8_THREADS) {
-    const int kb = i / ws_n, j = i - kb * ws_n;
-    const int nb = n0 / p.bn + j;
-    ws_s[i] = nb < p.N / p.bn ? p.ws[(static_cast<size_t>(g) * (p.K / p.bk) + kb0 + kb) * (p.N / p.bn) + nb] : 0.f;
-  }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_holder;
   volatile int* abortp = &abort_flag;
 
+  // the pass sequence of this CTA: `next` advances (item, row block) and fills `ps`; every role runs the same code
+  int item = int(blockIdx.x) - int(gridDim.x), zb = 0, n_zb = 0, gbeg = 0, gend = 0;
+  F8Pass ps;
+  auto next = [&]() -> bool {
+    for (;;) {
+      if (zb + 1 < n_zb) {
+        ++zb;
+      } else {
+        item += gridDim.x;
+        if (item >= n_items) return false;
+        const int panel = item % n_panels, rest = item / n_panels;
+        ps.g = rest % p.G;
+        ps.split = rest / p.G;
+        ps.n0 = panel * 128;
+        gbeg = p.offsets ? p.offsets[ps.g] : 0;
+        gend = p.offsets ? (p.counts ? gbeg + p.counts[ps.g] : p.offsets[ps.g + 1]) : p.R;
+        n_zb = (gend - gbeg + NTOK - 1) / NTOK;            // 0 for a group without rows
+        zb = 0;
+        if (n_zb <= 0) continue;
+      }
+      ps.r0 = gbeg + zb * NTOK;
+      ps.cnt = min(NTOK, gend - ps.r0);
+      return true;
+    }
+  };
+
   if (warp == 0) {
     if (lane == 0) {
       tma_prefetch_desc(&tma_w);
       tma_prefetch_desc(&tma_x);
-      const int n_stage_loads = (kend - kbeg + F8_KSTAGE - 1) / F8_KSTAGE;
-      for (int it = 0; it < n_stage_loads; ++it) {
-        const int s = it % F8_STAGES;
-        const uint32_t ph = (it / F8_STAGES) & 1;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), ph ^ 1, abortp)) {
-          atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
-          abort_flag = 1;
-          break;
+      uint32_t it = 0;
+      bool ok = true;
+      while (ok && next()) {
+        const int kbeg = ps.split * p.k_per_split;
+        for (int st = 0; st < n_stage_loads; ++st, ++it) {
+          const int s = it % F8_STAGES;
+          if (!mbar_wait(smem_u32(&empty_bar[s]), ((it / F8_STAGES) & 1) ^ 1, abortp)) {
+            atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
+            abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t bar = smem_u32(&full_bar[s]);
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          mbar_expect_tx(bar, STAGE_BYTES);
+          const int k0 = kbeg + st * F8_KSTAGE;            // rows past K (and token rows past R) read as zeros
+          tma_load_3d(sa, &tma_w, bar, ps.n0, k0, ps.g);
+          tma_load_2d(sa + A_BYTES, &tma_x, bar, k0, ps.r0);
         }
-        const uint32_t bar = smem_u32(&full_bar[s]);
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        mbar_expect_tx(bar, STAGE_BYTES);
-        const int k0 = kbeg + it * F8_KSTAGE;              // rows past K (and token rows past R) read as zeros
-        tma_load_3d(sa, &tma_w, bar, n0, k0, g);
-        tma_load_2d(sa + A_BYTES, &tma_x, bar, k0, r0);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
-      for (int q = 0; q < n_steps; ++q) {
-        const int it = q / (F8_KSTAGE / 32), j = q % (F8_KSTAGE / 32);
-        const int s = it % F8_STAGES;
-        const int kb = q / steps_per_kb, first = q % steps_per_kb == 0, last = (q + 1) % steps_per_kb == 0;
-        const int acc = kb & 1;
-        if (j == 0) {
-          if (!mbar_wait(smem_u32(&full_bar[s]), (it / F8_STAGES) & 1, abortp)) {
-            atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
-            abort_flag = 1;
-            break;
+      uint32_t it0 = 0, kc0 = 0;                           // running stage / K-block numbers at the start of the pass
+      bool ok = true;
+      while (ok && next()) {
+        int j = 0, in_kb = 0;                              // position inside the stage / inside the K block
+        uint32_t it = it0, kc = kc0;
+        for (int q = 0; q < n_steps; ++q) {
+          const int s = it % F8_STAGES, acc = kc % NACC;
+          if (j == 0) {
+            if (!mbar_wait(smem_u32(&full_bar[s]), (it / F8_STAGES) & 1, abortp)) {
+              atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after();
           }
-          tc_fence_after();
-        }
-        if (first) {
-          if (!mbar_wait(smem_u32(&tempty_bar[acc]), ((kb >> 1) & 1) ^ 1, abortp)) {
-            atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
-            abort_flag = 1;
-            break;
+          if (in_kb == 0) {
+            if (!mbar_wait(smem_u32(&tempty_bar[acc]), ((kc / NACC) & 1) ^ 1, abortp)) {
+              atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
+              abort_flag = 1;
+              ok = false;
+              break;
+            }
+            tc_fence_after();
           }
-          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
+          const uint64_t da = make_smem_desc(sa + j * 4096, 128 * 128, 1024);          // 32 k rows of 128 bytes, 8-row groups 1024 bytes apart
+          const uint64_t db = make_smem_desc(sa + A_BYTES + j * 32, 16, 1024);         // 32 bytes along each token row
+          tc_mma_ss_f8(tmem_base + acc * NTOK, da, db, IDESC, in_kb == 0 ? 0u : 1u);
+          if (++j == F8_KSTAGE / 32 || q == n_steps - 1) {   // a pass ends its last stage, full or not
+            tc_commit(smem_u32(&empty_bar[s]));
+            j = 0;
+            ++it;
+          }
+          if (++in_kb == steps_per_kb) {
+            tc_commit(smem_u32(&tfull_bar[acc]));
+            in_kb = 0;
+            ++kc;
+          }
         }
-        const uint32_t sa = smem_u32(smem + s * STAGE_BYTES);
-        const uint64_t da = make_smem_desc(sa + j * 4096, 128 * 128, 1024);          // 32 k rows of 128 bytes, 8-row groups 1024 bytes apart
-        const uint64_t db = make_smem_desc(sa + A_BYTES + j * 32, 16, 1024);         // 32 bytes along each token row
-        tc_mma_ss_f8(tmem_base + acc * NTOK, da, db, IDESC, first ? 0u : 1u);
-        if (j == F8_KSTAGE / 32 - 1 || q == n_steps - 1) tc_commit(smem_u32(&empty_bar[s]));
-        if (last) tc_commit(smem_u32(&tfull_bar[acc]));
+        it0 += n_stage_loads;
+        kc0 += n_kb;
       }
     }
   } else {
     const int quarter = warp & 3;
-    const int col = n0 + quarter * 32 + lane;              // this thread's weight column = TMEM lane
-    const int wsel = p.bn >= 128 ? 0 : (quarter * 32 + lane) / p.bn;
-    float racc[NTOK];
-#pragma unroll
-    for (int t = 0; t < NTOK; ++t) racc[t] = 0.f;
+    const int te = threadIdx.x - 64;                        // 0..127 among the four epilogue warps
+    uint32_t kc0 = 0;
     bool ok = true;
-    for (int kb = 0; kb < n_kb && ok; ++kb) {
-      const int acc = kb & 1;
-      if (!mbar_wait(smem_u32(&tfull_bar[acc]), (kb >> 1) & 1, abortp)) {
-        if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
-        abort_flag = 1;
-        ok = false;
-        break;
+    int table_item = -1;
+    while (ok && next()) {
+      const int col = ps.n0 + quarter * 32 + lane;          // this thread's weight column = TMEM lane
+      const int wsel = p.bn >= 128 ? 0 : (quarter * 32 + lane) / p.bn;
+      const int kb0 = ps.split * n_kb;
+      // scale tables of this pass (only these four warps touch them): tokens x K blocks, and - once per item - K blocks x column blocks
+      for (int i = te; i < n_kb * NTOK; i += 128) {
+        const int kb = i / NTOK, t = i - kb * NTOK;
+        xs_s[i] = t < ps.cnt ? p.xs[static_cast<size_t>(ps.r0 + t) * (p.K / p.bk) + kb0 + kb] : 0.f;
       }
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * NTOK + (uint32_t(quarter * 32) << 16);
-      const float wsv = ws_s[kb * ws_n + wsel];
-      const float* xrow = xs_s + kb * NTOK;
+      if (table_item != item) {
+        for (int i = te; i < n_kb * ws_n; i += 128) {
+          const int kb = i / ws_n, jj = i - kb * ws_n;
+          const int nb = ps.n0 / p.bn + jj;
+          ws_s[i] = nb < p.N / p.bn ? p.ws[(static_cast<size_t>(ps.g) * (p.K / p.bk) + kb0 + kb) * (p.N / p.bn) + nb] : 0.f;
+        }
+        table_item = item;
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      float racc[NTOK];
 #pragma unroll
-      for (int c = 0; c < NTOK / 16; ++c) {
-        uint32_t r[16];
-        tmem_ld16(taddr + c * 16, r);
+      for (int t = 0; t < NTOK; ++t) racc[t] = 0.f;
+      // A TMEM read is a long round trip: the accumulators of U consecutive K blocks are read back with one wait.
+      constexpr int U = 64 / NTOK;
+      for (int kb = 0; kb < n_kb && ok; kb += U) {
+        const int nu = min(U, n_kb - kb);
+        uint32_t r[U][NTOK / 16][16];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (u < nu && ok) {
+            const uint32_t kc = kc0 + kb + u;
+            if (!mbar_wait(smem_u32(&tfull_bar[kc % NACC]), (kc / NACC) & 1, abortp)) {
+              if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
+              abort_flag = 1;
+              ok = false;
+            }
+          }
+        }
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (u < nu) {
+            const uint32_t taddr = tmem_base + ((kc0 + kb + u) % NACC) * NTOK + (uint32_t(quarter * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < NTOK / 16; ++c) tmem_ld16(taddr + c * 16, r[u][c]);
+          }
+        }
         tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i) racc[c * 16 + i] = fmaf(__uint_as_float(r[i]), wsv * xrow[c * 16 + i], racc[c * 16 + i]);
+          for (int u = 0; u < U; ++u)
+            if (u < nu) mbar_arrive(smem_u32(&tempty_bar[(kc0 + kb + u) % NACC]));
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (u < nu) {
+            const float wsv = ws_s[(kb + u) * ws_n + wsel];
+            const float* xrow = xs_s + (kb + u) * NTOK;
+#pragma unroll
+            for (int c = 0; c < NTOK / 16; ++c)
+#pragma unroll
+              for (int i = 0; i < 16; ++i) racc[c * 16 + i] = fmaf(__uint_as_float(r[u][c][i]), wsv * xrow[c * 16 + i], racc[c * 16 + i]);
+          }
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[acc]));
-    }
-    if (ok && col < p.N) {
-      float* out = p.part + static_cast<size_t>(split) * p.R * p.N + col;
+      if (ok && col < p.N) {
+        float* out = p.part + static_cast<size_t>(ps.split) * p.R * p.N + col;
 #pragma unroll
-      for (int t = 0; t < NTOK; ++t)
-        if (t < cnt) out[static_cast<size_t>(r0 + t) * p.N] = racc[t];
+        for (int t = 0; t < NTOK; ++t)
+          if (t < ps.cnt) out[static_cast<size_t>(ps.r0 + t) * p.N] = racc[t];
+      }
+      kc0 += n_kb;
+      asm volatile("bar.sync 1, 128;" ::: "memory");       // everyone is done with this pass's scale tables
     }
   }
   __syncthreads();
@@ -454,8 +565,9 @@ int launch_f8(const CUtensorMap& tw, const CUtensorMap& tx, const F8Params& p, c
     if (cudaFuncSetAttribute(decode_gemm_f8_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -91;
     configured[dev] = true;
   }
-  dim3 grid((p.N + 127) / 128, p.G, p.splits * p.zblocks);
-  decode_gemm_f8_kernel<NTOK><<<grid, F8_THREADS, smem, stream>>>(tw, tx, p);
+  const int items = (p.N + 127) / 128 * p.G * p.splits;
+  const int resident = 2 * lyra::sm_count();               // two CTAs per SM: two weight streams in flight
+  decode_gemm_f8_kernel<NTOK><<<items < resident ? items : resident, F8_THREADS, smem, stream>>>(tw, tx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -92;
 }
 
@@ -496,8 +608,9 @@ extern "C" int lyra_decode_gemm(const void* x, const void* w, const float* wscal
   const int rc = quant ? launch_tn<true>(p, panel, stream) : launch_tn<false>(p, panel, stream);
   if (rc) return rc;
   if (swiglu && (residual || alpha != 1.f)) return -90;
-  decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,
-                                                   swiglu_limit, static_cast<const __nv_bfloat16*>(residual), alpha);
+  decode_gemm_finish_kernel<<<dim3(R, ((swiglu ? N / 2 : N) + 1023) / 1024), 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G,
+                                                                                                splits, swiglu, swiglu_beta, swiglu_limit,
+                                                                                                static_cast<const __nv_bfloat16*>(residual), alpha);
   return cudaGetLastError() == cudaSuccess ? 0 : -93;
 }
 
@@ -534,7 +647,8 @@ extern "C" int lyra_decode_gemm_f8(const void* xq, const float* xs, const void* 
   }
   const int rc = ntok == 64 ? launch_f8<64>(tw, tx, p, stream) : ntok == 32 ? launch_f8<32>(tw, tx, p, stream) : launch_f8<16>(tw, tx, p, stream);
   if (rc) return rc;
-  decode_gemm_finish_kernel<<<R, 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G, splits, swiglu, swiglu_beta,
-                                                   swiglu_limit, static_cast<const __nv_bfloat16*>(residual), alpha);
+  decode_gemm_finish_kernel<<<dim3(R, ((swiglu ? N / 2 : N) + 1023) / 1024), 256, 0, stream>>>(part, bias, offsets, static_cast<__nv_bfloat16*>(out), R, N, G,
+                                                                                                splits, swiglu, swiglu_beta, swiglu_limit,
+                                                                                                static_cast<const __nv_bfloat16*>(residual), alpha);
   return cudaGetLastError() == cudaSuccess ? 0 : -93;
 }

@@ -226,8 +226,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant__ C
               // give up after the time limit - or after 2 ms if an earlier kernel has already reported a failure (rows dropped on
               // overflow never arrive; a healthy exchange delivers a tile within microseconds of its neighbours)
               const long long waited = clock64() - t0;
-              if (v - want < 0 && (waited > WAIT_LIMIT_CYCLES || *abortp || (waited > 4000000 && *reinterpret_cast<volatile int*>(p.status) != 0))) {
-                atomicCAS(p.status, 0, STATUS_TIMEOUT_PEER);
+              if (v - want < 0 && (waited > PEER_WAIT_LIMIT_CYCLES || *abortp || (waited > 4000000 && *reinterpret_cast<volatile int*>(p.status) != 0))) {
+                atomicCAS(p.status, 0, STATUS_TIMEOUT_TILE);
                 abort_flag = 1;
                 ok = false;
                 break;

@@ -332,11 +332,30 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
     with score 1 (lyra/model.py:451-480). Returns ``(scores [F, K], indices [F, K], aux_loss)``."""
     c = config
     W = (lambda p: rt.materialize(p) if rt is not None else p)
+    k = c.n_active_routed_experts
     with scope("router"):
         logits = t.float() @ W(w.router).float()
+        if (ROUTING_TAPE is None and not probe.enabled and ops.use_kernels(t, c.implementation) and (rt is None or rt.tp_size == 1)):
+            from lyra_b200.ops import routing
+
+            if routing.supported(c.n_routed_experts, k):
+                # one kernel chain: top-k, scores, both auxiliary terms, counts and the expert-sorted permutation
+                scores, idx, aux, plan = routing.route(logits, W(w.router_bias) if w.router_bias is not None else None, k,
+                                                       c.load_balance_weight, c.router_z_loss_weight)
+                meter = getattr(rt, "load_meter", None)
+                if meter is not None and (meter.always or torch.is_grad_enabled()):
+                    meter.add(rt._layer, idx)
+                if rt is not None:
+                    rt.routing_plan = plan                   # picked up by the expert exchange of this layer call
+                if c.n_shared_experts:
+                    shared = torch.arange(c.n_routed_experts, c.n_experts, device=idx.device, dtype=idx.dtype)
+                    idx = torch.cat([idx, shared[None].expand(t.shape[0], -1)], dim=-1)
+                    scores = torch.cat([scores, scores.new_ones(t.shape[0], c.n_shared_experts)], dim=-1)
+                return scores, idx, aux
         if w.router_bias is not None:
             logits = logits + W(w.router_bias).float()
-    k = c.n_active_routed_experts
+    if rt is not None:
+        rt.routing_plan = None
     if ROUTING_TAPE is not None and ROUTING_TAPE["replay"]:
         idx = ROUTING_TAPE["choices"].pop(0)
         vals = torch.gather(logits, -1, idx)

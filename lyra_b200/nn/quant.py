@@ -121,9 +121,11 @@ def _quantize_kernel(x: torch.Tensor, dtype, block: tuple[int, ...], scale_dtype
     q = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
     scale = torch.empty(*x.shape[:-2], R // br, C // bc, dtype=torch.float32, device=x.device)
     is_bf16 = ctypes.c_int(int(x.dtype == torch.bfloat16))
-    if br == 1 and bc == C and C % 32 == 0 and C <= 1024:
-        rc = lib.lyra_fp8_quantize_rows(native.ptr(x), is_bf16, native.ptr(q), native.ptr(scale), ctypes.c_longlong(L * R), ctypes.c_int(C),
-                                        ctypes.c_longlong(C), ctypes.c_longlong(C), native.stream_ptr())
+    if br == 1 and bc % 32 == 0 and bc <= 1024:
+        # one scale per (row, run of bc values): the runs are contiguous, so the array is a list of L * R * C / bc rows of bc values
+        # (KV-cache rows with bc == C; activations of the e4m3 products with bc = the K block of the weights' scales)
+        rc = lib.lyra_fp8_quantize_rows(native.ptr(x), is_bf16, native.ptr(q), native.ptr(scale), ctypes.c_longlong(L * R * (C // bc)), ctypes.c_int(bc),
+                                        ctypes.c_longlong(bc), ctypes.c_longlong(bc), native.stream_ptr())
     elif L <= 65535 and R // br <= 65535:
         rc = lib.lyra_fp8_quantize_2d(native.ptr(x), is_bf16, native.ptr(q), native.ptr(scale), ctypes.c_int(L), ctypes.c_int(R), ctypes.c_int(C),
                                       ctypes.c_int(br), ctypes.c_int(bc), native.stream_ptr())

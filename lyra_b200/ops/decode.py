@@ -100,7 +100,8 @@ def _gemm_splits(n_cols: int, panel: int, groups_with_rows: int, k_chunks: int) 
 def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, counts: torch.Tensor | None = None, bias: torch.Tensor | None = None,
                 swiglu: bool = False,
                 swiglu_beta: float = 1.702, swiglu_limit: float = 7.0, active_groups: int | None = None,
-                max_group_rows: int | None = None, residual: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:
+                max_group_rows: int | None = None, residual: torch.Tensor | None = None, alpha: float = 1.0,
+                typical_group_rows: int | None = None) -> torch.Tensor:
     """``x [R, K]`` (rows sorted by group) times ``w [G, K, N]`` (bf16 tensor, or QArray of e4m3 values with 2-D block
     scales) -> bf16 ``[R, N]`` (``[R, N/2]`` with SwiGLU). ``offsets [G+1]`` int32 row offsets on the device; ``None``
     means one group (a dense layer, ``w [K, N]`` or ``[1, K, N]``). ``counts [G]`` int32 gives the real rows per group when
@@ -123,7 +124,7 @@ def decode_gemm(x: torch.Tensor, w, *, offsets: torch.Tensor | None = None, coun
         scale = w.scale.float().contiguous()
         if F8_TENSOR_CORES and f8_gemm_supported(K, N, bk, bn) and hasattr(lib, "lyra_decode_gemm_f8"):
             return _decode_gemm_f8(lib, x, wq, scale, bk, bn, offsets, counts, bias, swiglu, swiglu_beta, swiglu_limit, active_groups,
-                                   max_group_rows, residual, alpha)
+                                   max_group_rows, residual, alpha, typical_group_rows)
     panel = _gemm_panel(N)
     splits = _gemm_splits(N, panel, min(G, R) if active_groups is None else active_groups, K // 64)
     part = torch.empty(splits, R, N, dtype=torch.float32, device=x.device)
@@ -148,7 +149,8 @@ def f8_gemm_supported(K: int, N: int, bk: int, bn: int) -> bool:
             and N % 16 == 0 and K % 16 == 0 and K // bk <= 64)
 
 
-def _decode_gemm_f8(lib, x, wq, wscale, bk, bn, offsets, counts, bias, swiglu, swiglu_beta, swiglu_limit, active_groups, max_group_rows, residual, alpha):
+def _decode_gemm_f8(lib, x, wq, wscale, bk, bn, offsets, counts, bias, swiglu, swiglu_beta, swiglu_limit, active_groups, max_group_rows, residual, alpha,
+                    typical_group_rows=None):
     """e4m3 weights x e4m3 activations on the tensor cores (``decode_gemm_f8_kernel``). The activations are quantised here with
     one scale per (row, K block of ``bk``), the (1 x scale_k) block of the reference's quantised grouped GEMM
     (lyra/kernels/gemm.py:1551-1556); the weights stream once, as stored."""
@@ -158,7 +160,10 @@ def _decode_gemm_f8(lib, x, wq, wscale, bk, bn, offsets, counts, bias, swiglu, s
     R = x.shape[0]
     xq = quantize(x, torch.float8_e4m3fn, (1, bk))
     most = min(R, max_group_rows) if max_group_rows else R
-    ntok = 16 if most <= 16 else 32 if most <= 32 else 64
+    # token columns per tile: sized for the rows a group usually has, not for the worst case - a CTA takes a larger group in
+    # several passes, and the narrow tiles read their accumulators back four at a time
+    usual = min(most, typical_group_rows) if typical_group_rows else most
+    ntok = 16 if usual <= 16 else 32 if usual <= 32 else 64
     groups = min(G, R) if active_groups is None else active_groups
     ctas = max(1, (N + 127) // 128 * max(1, groups))
     splits = 1
@@ -226,8 +231,10 @@ def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limi
         x_sorted = xn.to(BF16)[order // K].contiguous()
         ub = up_bias.reshape(E, N_up) if up_bias is not None else None
         db = down_bias.reshape(E, C) if down_bias is not None else None
-        act = decode_gemm(x_sorted, wu, offsets=offsets, bias=ub, swiglu=True, swiglu_beta=beta, swiglu_limit=limit, active_groups=min(E, F_ * K))
-        down = decode_gemm(act, wd, offsets=offsets, bias=db, active_groups=min(E, F_ * K))
+        usual = -(-2 * F_ * K // E)                            # twice the balanced rows per expert
+        act = decode_gemm(x_sorted, wu, offsets=offsets, bias=ub, swiglu=True, swiglu_beta=beta, swiglu_limit=limit, active_groups=min(E, F_ * K),
+                          typical_group_rows=usual)
+        down = decode_gemm(act, wd, offsets=offsets, bias=db, active_groups=min(E, F_ * K), typical_group_rows=usual)
         return ew.combine_rows(down, dest, scores.float().contiguous(), F_, K)
     if up_q:
         w_up = dequantize(w_up, BF16).reshape(E, C, 2, -1)

@@ -90,6 +90,8 @@ STATUS_NAMES = {
     4: "timeout waiting for a peer flag",
     5: "bad argument",
     6: "expert-parallel receive buffer overflow (raise LYRA_EP_CAPACITY)",
+    7: "timeout waiting for the rows of a tile that other GPUs store (expert dispatch)",
+    8: "timeout waiting for dispatched rows to come back from the experts' GPUs",
 }
 
 

@@ -86,6 +86,8 @@ class Comm:
         self.ag_calls: dict[str, int] = {}
         self._grad_views: dict[int, torch.Tensor] = {}
         self._reduced: dict[str, torch.Tensor] = {}
+        self._sq_partial: torch.Tensor | None = None
+        self.grad_sumsq: dict[str, torch.Tensor] = {}            # owned leaf -> sum of squares of its reduced gradient, per matrix
         for name, shape, owner in entries:
             if owner == self.rank:
                 self._reduced[name] = torch.empty((self.numel[name] + 7) // 8 * 8, dtype=torch.float32 if grad_dtype == torch.float32 else BF16, device=self.device)
@@ -201,17 +203,30 @@ class Comm:
         self.barrier()                                           # every rank finished accumulating
         stream = nat.stream_ptr()
         in_bf16 = int(self.grad_dtype == BF16)
-        for name, shape, owner in self.entries:
-            if owner != self.rank:
-                continue
+        owned = [(name, shape) for name, shape, owner in self.entries if owner == self.rank]
+        if owned and self._sq_partial is None:
+            # per-block sums of squares of every owned leaf's reduced gradient, written by the pull-reduce itself; a leaf's block
+            # count never changes, so the unused tail of its row stays zero and one sum over the block axis finishes all leaves
+            self.lib.lyra_reduce_pull_norm_blocks.restype = ctypes.c_int
+            blocks = [int(self.lib.lyra_reduce_pull_norm_blocks(ctypes.c_longlong((self.numel[n] + 7) // 8 * 8))) for n, _ in owned]
+            self._sq_partial = torch.zeros(len(owned), max(blocks), 2, dtype=torch.float32, device=self.device)
+        for i, (name, shape) in enumerate(owned):
             n = self.numel[name]
             n8 = (n + 7) // 8 * 8                                # every leaf's region is 256-byte aligned and its padding stays zero
             dst = self._reduced[name]                            # (padded to n8 elements)
-            nat.check(self.lib.lyra_reduce_pull(nat.ptr(dst), _ptr_array(self.g_slab.peers_at(self.g_off[name])), self.world,
-                                                ctypes.c_longlong(n8), in_bf16, in_bf16, stream), "reduce_pull")
+            # a [C, 2, H] up-projection interleaves two matrices (gate and linear halves) in runs of H elements
+            halves = name.split("#")[0].endswith("mlp_up") and len(shape) == 3 and shape[1] == 2 and shape[2] % 8 == 0
+            nat.check(self.lib.lyra_reduce_pull_norm(nat.ptr(dst), _ptr_array(self.g_slab.peers_at(self.g_off[name])), self.world,
+                                                     ctypes.c_longlong(n8), in_bf16, in_bf16, ctypes.c_longlong(shape[2] if halves else 0),
+                                                     2 if halves else 1, nat.ptr(self._sq_partial[i]), stream), "reduce_pull_norm")
             nat.count_launch()
-            dst = dst[:n]
-            out[name] = dst
+            out[name] = dst[:n]
+        self.grad_sumsq = {}
+        if owned:
+            sums = self._sq_partial.sum(1)                       # [leaves, 2], fixed summation order
+            for i, (name, shape) in enumerate(owned):
+                halves = name.split("#")[0].endswith("mlp_up") and len(shape) == 3 and shape[1] == 2 and shape[2] % 8 == 0
+                self.grad_sumsq[name] = sums[i, : 2 if halves else 1]
         self.barrier()                                           # buffers may be zeroed for the next step after this
         return out
 

@@ -82,9 +82,10 @@ def _ep_moe_decode(rt, xn, scores, indices, w, c: ModelConfig):
     if small:
         valid = ex.counts_mat.view(ex.W, ex.E)[:, ex.rank * El:(ex.rank + 1) * El].sum(0).to(torch.int32)
         most = ex.W * F_ * K                                     # an expert can receive at most every assignment of every rank
+        usual = -(-2 * most // ex.E)                             # twice the balanced load
         act = dec.decode_gemm(x_recv, wu, offsets=ex.offsets, counts=valid, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta,
-                              swiglu_limit=c.swiglu_limit, active_groups=El, max_group_rows=most)
-        rows = dec.decode_gemm(act, wd, offsets=ex.offsets, counts=valid, bias=db, active_groups=El, max_group_rows=most)
+                              swiglu_limit=c.swiglu_limit, active_groups=El, max_group_rows=most, typical_group_rows=usual)
+        rows = dec.decode_gemm(act, wd, offsets=ex.offsets, counts=valid, bias=db, active_groups=El, max_group_rows=most, typical_group_rows=usual)
     else:
         wu_t = dequantize(wu, BF16) if isinstance(wu, QArray) else wu
         wd_t = dequantize(wd, BF16) if isinstance(wd, QArray) else wd
@@ -172,7 +173,7 @@ FWD, BWD = 0, 1
 class EPBuffers:
     """Peer-mapped buffers of the exchange, created on first use (the same order on every rank)."""
 
-    def __init__(self, rt, F_: int, K: int, C: int):
+    def __init__(self, rt, F_: int, K: int, C: int, layers: list[int] | None = None):
         from lyra_b200.parallel.comm import SymmetricSlab
 
         self.rt = rt
@@ -192,6 +193,16 @@ class EPBuffers:
         self._sync = SymmetricSlab((2 * self.n_tiles + 64) * 4, dev, name)
         self.expect = torch.zeros(2 * self.n_tiles, dtype=torch.int32, device=dev)
         self.ret_expect = torch.zeros(2, dtype=torch.int32, device=dev)
+        if layers is not None:
+            # Everything a step will need, now, in one place: creating a peer-mapped buffer stalls the host (handle exchange), and a
+            # rank stalled in the middle of a step keeps its peers' GPUs spinning in their bounded waits. After this, steps allocate
+            # no peer-mapped memory.
+            for idx in layers:
+                self.for_layer(idx)
+            if any(i >= 0 for i in layers):                      # training: the backward pass's scratch as well
+                self.scratch_recv, self.scratch_ret
+            torch.cuda.synchronize(dev)
+            dist.barrier()
 
     def arrive_view(self, direction: int) -> torch.Tensor:
         return self._sync.view(direction * self.n_tiles * 4, self.n_tiles, torch.int32)
@@ -259,7 +270,8 @@ class _Exchange:
         key = (F_, K, C)
         sets = rt._ep_state.setdefault("sets", {})               # one buffer set per problem size (prefill and decode alternate)
         if key not in sets:
-            sets[key] = EPBuffers(rt, F_, K, C)
+            moe_layers = [i for i, kind in enumerate(rt.mcfg.mlp_map) if kind == "moe"]
+            sets[key] = EPBuffers(rt, F_, K, C, layers=(moe_layers + [-1]) if torch.is_grad_enabled() else [-1])
         rt._ep_state["key"], rt._ep_state["buf"] = key, sets[key]
         self.buf: EPBuffers = sets[key]
         self.F, self.K, self.C = F_, K, C
@@ -270,15 +282,22 @@ class _Exchange:
         dev = indices.device
         flat = indices.reshape(-1)
         self.expert_of = flat.to(torch.int32).contiguous()
-        counts = ref.count_ids(flat, self.E).to(torch.int32)
-        order = torch.argsort(flat, stable=True)
-        if tiles:
-            self.order = order.to(torch.int32)
+        plan = getattr(rt, "routing_plan", None)                 # counts and permutation already made by the routing kernels of this layer call
+        rt.routing_plan = None
+        if plan is not None and plan.order.numel() == flat.numel() and plan.counts.numel() <= self.E:
+            counts = torch.zeros(self.E, dtype=torch.int32, device=dev)
+            counts[: plan.counts.numel()] = plan.counts
+            self.order, self.rank_in_expert = plan.order, plan.rank_in_expert
         else:
-            starts = torch.cumsum(counts, 0) - counts
-            rie = torch.empty_like(order)
-            rie[order] = torch.arange(flat.numel(), device=dev) - starts[flat[order]].long()
-            self.rank_in_expert = rie.to(torch.int32).contiguous()
+            counts = ref.count_ids(flat, self.E).to(torch.int32)
+            order = torch.argsort(flat, stable=True)
+            if tiles:
+                self.order = order.to(torch.int32)
+            else:
+                starts = torch.cumsum(counts, 0) - counts
+                rie = torch.empty_like(order)
+                rie[order] = torch.arange(flat.numel(), device=dev) - starts[flat[order]].long()
+                self.rank_in_expert = rie.to(torch.int32).contiguous()
         # counts exchange
         self.buf.calls += 1
         par = self.buf.calls & 1

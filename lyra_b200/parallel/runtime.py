@@ -112,6 +112,8 @@ class Runtime:
         self._ep_state: dict = {}
         self._layer = 0
         self.load_meter = None                                   # ExpertLoadMeter once expert re-placement is switched on
+        self.grad_sumsq: dict[str, torch.Tensor] = {}
+        self.routing_plan = None                                 # counts / permutation of the current MoE layer call, when the routing kernels made them
 
     @classmethod
     def create(cls, *, world_size: int, rank: int, device, implementation: str = "b200", mcfg: ModelConfig | None = None) -> "Runtime":
@@ -287,12 +289,16 @@ class Runtime:
             if p not in out and p in self._masters and p.endswith(("mlp_up", "mlp_down")):
                 # an expert leaf that saw no routed token still needs a (zero) gradient slot for the shared expert
                 out[p] = torch.zeros_like(self._masters[p], dtype=next(iter(grads.values())).dtype if grads else torch.float32)
+        self.grad_sumsq = {}                                     # leaves whose norms the pull-reduce already produced (the optimizer reads this)
         for name, g in reduced.items():
             if name in self._shared:
                 path, e = self._shared[name]
                 out[path][e - self.rank * self.e_local].copy_(g.view(out[path].shape[1:]))
             else:
                 out[name] = g.view(self.plan.specs[name].shape)
+                sq = getattr(self._comm, "grad_sumsq", {}).get(name)
+                if sq is not None:
+                    self.grad_sumsq[name] = sq
         return out
 
     def after_optimizer(self, params: dict[str, torch.Tensor]) -> None:

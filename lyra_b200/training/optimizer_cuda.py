@@ -77,8 +77,11 @@ def optimizer_step_cuda(params: dict[str, torch.Tensor], grads: dict[str, torch.
     # ---- global norm, finite gate, per-matrix RMS clip factors
     zero = torch.zeros((), dtype=torch.float32, device=dev)
     once = (lambda p: rt.counts_once(p)) if rt is not None else (lambda p: True)
-    muon_sq = sum((_sumsq(grads[p]) for p in muon_paths if once(p)), zero)
-    adam_sq = sum((_sumsq(grads[p]) for p in adam_paths if once(p)), zero)
+    # leaves that arrived through the fused pull-reduce bring their sums of squares (per matrix) with them
+    known = getattr(rt, "grad_sumsq", None) or {}
+    leaf_sq = lambda p: known[p].sum() if p in known else _sumsq(grads[p])
+    muon_sq = sum((leaf_sq(p) for p in muon_paths if once(p)), zero)
+    adam_sq = sum((leaf_sq(p) for p in adam_paths if once(p)), zero)
     if rt is not None:
         muon_sq, adam_sq = rt.sum_over_ranks(muon_sq, adam_sq)
     grad_norm = (muon_sq + adam_sq).sqrt()
@@ -89,7 +92,11 @@ def optimizer_step_cuda(params: dict[str, torch.Tensor], grads: dict[str, torch.
     all_rms = []
     for p in muon_paths:
         gm, _ = as_matrices(p, grads[p])
-        norm = torch.linalg.vector_norm(gm, 2, dim=(-2, -1), dtype=torch.float32)
+        n_mats = gm.numel() // (gm.shape[-2] * gm.shape[-1])
+        if p in known and known[p].numel() == n_mats:
+            norm = known[p].sqrt()
+        else:
+            norm = torch.linalg.vector_norm(gm, 2, dim=(-2, -1), dtype=torch.float32)
         r = (norm / math.sqrt(gm.shape[-2] * gm.shape[-1])).reshape(-1)
         all_rms.append(r)
         clips[p] = torch.where(torch.isfinite(r), torch.clamp(tcfg.muon_grad_clip / (r + 1e-8), max=1.0), torch.ones_like(r)).contiguous()

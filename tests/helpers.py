@@ -20,9 +20,18 @@ def token_file(path, n=6000, vocab=500, seed=0):
 
 
 def free_port() -> int:
-    """A port the OS hands out as free right now (fixed ports can collide with a socket of an earlier test in TIME_WAIT)."""
+    """A port that is free right now, drawn from below the kernel's ephemeral range: ports the OS hands out itself (bind to 0)
+    come from the range that the collectives library's own sockets use, and a spawned rank has then found its rendezvous port
+    taken."""
+    import random
     import socket
 
-    with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
-        sock.bind(("127.0.0.1", 0))
-        return sock.getsockname()[1]
+    for _ in range(200):
+        port = random.randint(12000, 29999)
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as sock:
+            try:
+                sock.bind(("127.0.0.1", port))
+            except OSError:
+                continue
+            return port
+    raise RuntimeError("no free port found")

@@ -34,6 +34,7 @@ def _worker(rank, world, port, tmp):
     device = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
     try:
+        import lyra_b200.model as M
         from lyra_b200.model import ModelWeights
         from lyra_b200.nn.params import tree_dict
         from lyra_b200.ops import native
@@ -48,7 +49,11 @@ def _worker(rank, world, port, tmp):
         xs = rng.integers(0, c.vocab_size, size=(2, 2, c.seq_len)).astype(np.int32)
         ys = np.roll(xs, -1, axis=-1)
         results = {}
+        # the second runtime takes the experts the first one chose (per layer call), so the comparison is between two ways of moving
+        # the same tokens, gradients and weights, not between two sets of near-tie routing decisions
+        M.ROUTING_TAPE = {"replay": False, "choices": []}
         for mode in ("nccl", "b200"):
+            M.ROUTING_TAPE["replay"] = mode == "b200"
             rt = Runtime.create(world_size=world, rank=rank, device=device, implementation=mode, mcfg=c)
             w = ModelWeights.init(0, c, device=device, shard_fn=rt.shard_info)
             st = Stepper(init_train_state(w, c, tcfg), c, tcfg, device=device, rt=rt)
@@ -57,30 +62,34 @@ def _worker(rank, world, port, tmp):
             for step in range(2):
                 out = st.train_step(xs, ys, step)
                 losses.append(float(out["loss"]))
+                if step == 0:
+                    first = (float(out["grad_norm"]), {p: t.detach().float().cpu() - init[p] for p, t in tree_dict(w).items() if t.numel()})
             torch.cuda.synchronize()
             native.check_status()
-            results[mode] = (losses, float(out["grad_norm"]), {p: t.detach().float().cpu() - init[p] for p, t in tree_dict(w).items() if t.numel()})
+            results[mode] = (losses, first)
+        M.ROUTING_TAPE = None
         torch.save(results, f"{tmp}/rank{rank}.pt")
     finally:
         dist.destroy_process_group()
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_peer_memory_runtime_matches_collective_runtime(tmp_path):
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_peer_memory_runtime_matches_collective_runtime(tmp_path, world):
     import torch.multiprocessing as mp
 
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     port = free_port()
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
-    init = None
-    for r in range(2):
+    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
         res = torch.load(tmp_path / f"rank{r}.pt", weights_only=False)
-        (l0, g0, p0), (l1, g1, p1) = res["nccl"], res["b200"]
-        assert all(abs(a - b) < 3e-2 for a, b in zip(l0, l1)), (l0, l1)
-        assert abs(g0 - g1) < 0.1 * g0, (g0, g1)
+        (l0, (g0, p0)), (l1, (g1, p1)) = res["nccl"], res["b200"]
+        assert abs(l0[0] - l1[0]) < 2e-3 and abs(l0[1] - l1[1]) < 2e-2, (l0, l1)
+        assert abs(g0 - g1) < 0.02 * g0, (g0, g1)
         assert p0.keys() == p1.keys()
-        # compare the two-step updates by direction; small zero-initialised leaves take +-lr Adam steps whose sign is noise
+        # the first update, leaf by leaf (small zero-initialised leaves take +-lr Adam steps whose sign is noise: skipped)
         cos = {k: torch.nn.functional.cosine_similarity(p0[k].reshape(-1), p1[k].reshape(-1), dim=0).item() for k in p0 if p0[k].numel() >= 4096}
-        bad = {k: v for k, v in cos.items() if v < 0.9}
+        bad = {k: round(v, 4) for k, v in cos.items() if v < 0.98}
         assert cos and not bad, bad
 
 
