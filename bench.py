@@ -46,8 +46,10 @@ def parse_args():
     ap.add_argument("--variant", default="lyra-medium")
     ap.add_argument("--micro-batch", type=int, default=2)
     ap.add_argument("--accumulation", type=int, default=None)
-    ap.add_argument("--rebalance-experts", action="store_true",
-                    help="several GPUs: meter the experts' token counts during warm-up, re-place the experts on the ranks once (untimed), keep metering in the timed steps")
+    ap.add_argument("--rebalance-experts", action=argparse.BooleanOptionalAction, default=True,
+                    help="several GPUs: meter the experts' token counts during warm-up and re-place the experts on the ranks once before the "
+                         "timed steps (what `scripts/train.py --rebalance-experts-every N` does periodically; a relabelling of the experts, "
+                         "the model is unchanged). --no-rebalance-experts keeps the static placement")
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (the result is then labelled invalid)")
     return ap.parse_args()
 

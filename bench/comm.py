@@ -62,6 +62,13 @@ def main():
         return float(t)
 
     peak = peaks()
+    only_ep = len(sys.argv) > 1 and sys.argv[1] == "ep"      # `bench/comm.py ep`: just the MoE-layer and gradient-reduce rows
+    if only_ep:
+        bench_ep_layer(world, rank, dev, peak, timed)
+        bench_reduce(world, rank, dev, timed)
+        native.check_status()
+        dist.destroy_process_group()
+        return
     owner = (rank + 1) % world  # every rank pulls from its neighbour
     for (M, K, N) in [(8192, 4096, 4096), (8192, 4096, 12288), (8192, 6144, 4096), (2048, 4096, 4096)]:
         slab = SymmetricSlab(K * N * 2, dev, dist.group.WORLD.group_name)

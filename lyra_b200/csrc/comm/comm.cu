@@ -375,15 +375,18 @@ __device__ __forceinline__ int block_rank_of_flag(bool flag, int* warp_sums, int
 // Layout of one exchange, one block. Everything `ep_layout_kernel` computes, plus what the tile-granular path needs:
 //   starts[E + 1]      : exclusive prefix of this rank's own per-expert counts (position of expert e's run in the sender's
 //                        expert-sorted assignment list); starts[E] = number of assignments
-//   send_rot           : starts[my_rank * e_local] - the sorted position where this rank's own experts begin. A sender walks
-//                        its sorted list cyclically from there, i.e. destination my_rank first, then my_rank + 1, ...
+//   send_starts[E + 1] : the order in which this rank SENDS its runs: by local expert index j first, then by destination
+//                        starting with itself (k = j * world + t  ->  expert ((my_rank + t) % world) * e_local + j); entry k is
+//                        the number of assignments sent before run k. Every receiver thus gets all of its expert 0's rows
+//                        first, then expert 1's, ... (it consumes tiles expert by expert, which keeps one expert's weights in L2),
+//                        while at any moment the senders target different destinations (no incast).
 //   tile_valid[t]      : real (non-padding) rows in 128-row tile t of the receive buffer, 0 for unused tiles
-//   tile_perm[i]       : the used tiles in the order in which they complete under that sending order: by the step
-//                        (my_rank - source) mod world of the last source that contributes rows to the tile, then by row;
-//                        -1 after the last used tile. The grouped GEMM enumerates its row tiles through this list.
+//   tile_perm[i]       : the used tiles in the order in which they complete under that sending order: by expert, inside an expert
+//                        by the step (my_rank - source) mod world of the last source that contributes rows to the tile, then by
+//                        row; -1 after the last used tile. The grouped GEMM enumerates its row tiles through this list.
 __global__ void ep_layout_tiles_kernel(const int* __restrict__ counts, int world, int my_rank, int n_experts, int e_local, int cap_rows,
                                        int* __restrict__ send_base, int* __restrict__ recv_offsets, int* __restrict__ tile_group,
-                                       int* __restrict__ recv_total, int* __restrict__ starts, int* __restrict__ send_rot,
+                                       int* __restrict__ recv_total, int* __restrict__ starts, int* __restrict__ send_starts,
                                        int* __restrict__ tile_valid, int* __restrict__ tile_perm, int* status) {
   extern __shared__ int sh[];  // totals [E], padded bases [E], warp sums [32], step of each tile [cap_rows / 128]
   int* total = sh;
@@ -421,7 +424,13 @@ __global__ void ep_layout_tiles_kernel(const int* __restrict__ counts, int world
       run += counts[my_rank * n_experts + e];
     }
     starts[n_experts] = run;
-    *send_rot = starts[my_rank * e_local];
+    run = 0;
+    for (int k = 0; k < n_experts; ++k) {
+      const int j = k / world, t = k - j * world;
+      send_starts[k] = run;
+      run += counts[my_rank * n_experts + ((my_rank + t) % world) * e_local + j];
+    }
+    send_starts[n_experts] = run;
     filled = 0;
   }
   __syncthreads();
@@ -452,10 +461,10 @@ __global__ void ep_layout_tiles_kernel(const int* __restrict__ counts, int world
     }
     tile_group[t] = g;
     tile_valid[t] = valid;
-    step_of[t] = valid > 0 ? step : -1;
+    step_of[t] = valid > 0 ? g * world + step : -1;   // sort key: expert, then arrival step
   }
   __syncthreads();
-  for (int k = 0; k < world; ++k) {
+  for (int k = 0; k < e_local * world; ++k) {
     for (int t0 = 0; t0 < n_tiles; t0 += blockDim.x) {
       const int t = t0 + threadIdx.x;
       const bool mine = t < n_tiles && step_of[t] == k;
@@ -477,20 +486,27 @@ __global__ void ep_expect_bump_kernel(int* __restrict__ expect, const int* __res
   if (t < n_tiles) expect[t] += tile_valid[t];
 }
 
-// One block per assignment, taken in the sender's cyclic expert-sorted order (see ep_layout_tiles_kernel): copies the source
-// row into the owner's receive buffer, records (rank, slot) and optionally the routing score beside it, then adds one to the
-// arrival counter of the row's 128-row tile on the owner (release at system scope: the row is visible before the count).
-__global__ void ep_dispatch_sorted_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ order, const int* __restrict__ expert_of,
-                                          const int* __restrict__ starts, const int* __restrict__ send_base, const int* __restrict__ send_rot,
+// One block per assignment, taken in the sender's order (see ep_layout_tiles_kernel): copies the source row into the owner's
+// receive buffer, records (rank, slot) and optionally the routing score beside it, then adds one to the arrival counter of the
+// row's 128-row tile on the owner (release at system scope: the row is visible before the count).
+__global__ void ep_dispatch_sorted_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ order, const int* __restrict__ starts,
+                                          const int* __restrict__ send_base, const int* __restrict__ send_starts,
                                           const float* __restrict__ scores, PeerPtrs recv_bufs, PeerPtrs recv_meta, PeerPtrs recv_score,
-                                          PeerPtrs arrive, int my_rank, int e_local, int cap_rows, int n_assign, int src_div, int C) {
-  int j = blockIdx.x + *send_rot;
-  if (j >= n_assign) j -= n_assign;
-  if (j < 0 || j >= n_assign) return;
-  const int a = order[j];
-  const int e = expert_of[a];
-  const int d = e / e_local;
-  const int row = send_base[e] + (j - starts[e]);
+                                          PeerPtrs arrive, int world, int my_rank, int n_experts, int e_local, int cap_rows, int n_assign, int src_div,
+                                          int C) {
+  const int i = blockIdx.x;
+  if (i >= n_assign || i >= send_starts[n_experts]) return;
+  int lo = 0, hi = n_experts;                    // last run k with send_starts[k] <= i
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (send_starts[mid] <= i) lo = mid; else hi = mid;
+  }
+  const int j = lo / world, t = lo - j * world;
+  const int d = (my_rank + t) % world;
+  const int e = d * e_local + j;
+  const int pos = i - send_starts[lo];           // position inside expert e's run (token order)
+  const int a = order[starts[e] + pos];
+  const int row = send_base[e] + pos;
   if (row >= cap_rows) return;  // overflow was flagged by the layout kernel
   const uint4* s = reinterpret_cast<const uint4*>(src + (long long)(a / src_div) * C);
   uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(recv_bufs.p[d]) + (long long)row * C);
@@ -656,7 +672,7 @@ extern "C" int lyra_ep_zero_pad(void* rows, const int* recv_offsets, const int* 
 }
 
 extern "C" int lyra_ep_layout_tiles(const int* counts, int world, int my_rank, int n_experts, int e_local, int cap_rows, int* send_base,
-                                    int* recv_offsets, int* tile_group, int* recv_total, int* starts, int* send_rot, int* tile_valid,
+                                    int* recv_offsets, int* tile_group, int* recv_total, int* starts, int* send_starts, int* tile_valid,
                                     int* tile_perm, int* status, void* stream) {
   if (world > MAX_RANKS || cap_rows % 128) return -53;
   const size_t smem = (2 * (size_t)n_experts + 32 + cap_rows / 128) * sizeof(int);
@@ -667,7 +683,7 @@ extern "C" int lyra_ep_layout_tiles(const int* counts, int world, int my_rank, i
     configured = true;
   }
   ep_layout_tiles_kernel<<<1, 1024, smem, ST(stream)>>>(counts, world, my_rank, n_experts, e_local, cap_rows, send_base, recv_offsets, tile_group,
-                                                          recv_total, starts, send_rot, tile_valid, tile_perm, status);
+                                                          recv_total, starts, send_starts, tile_valid, tile_perm, status);
   LYRA_CHECK_LAUNCH();
   return 0;
 }
@@ -679,17 +695,17 @@ extern "C" int lyra_ep_expect_bump(int* expect, const int* tile_valid, int n_til
   return 0;
 }
 
-extern "C" int lyra_ep_dispatch_sorted(const void* src, const int* order, const int* expert_of, const int* starts, const int* send_base,
-                                       const int* send_rot, const float* scores, const long long* recv_bufs, const long long* recv_meta,
-                                       const long long* recv_score, const long long* arrive, int world, int my_rank, int e_local, int cap_rows,
-                                       int n_assign, int src_div, int C, void* stream) {
+extern "C" int lyra_ep_dispatch_sorted(const void* src, const int* order, const int* starts, const int* send_base, const int* send_starts,
+                                       const float* scores, const long long* recv_bufs, const long long* recv_meta, const long long* recv_score,
+                                       const long long* arrive, int world, int my_rank, int n_experts, int e_local, int cap_rows, int n_assign,
+                                       int src_div, int C, void* stream) {
   if (n_assign <= 0) return 0;
-  if (C % 8 || world > MAX_RANKS || !arrive) return -52;
+  if (C % 8 || world > MAX_RANKS || !arrive || n_experts != world * e_local) return -52;
   const PeerPtrs none = make_ptrs(recv_bufs, 0);
-  ep_dispatch_sorted_kernel<<<n_assign, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(src), order, expert_of, starts, send_base, send_rot,
-                                                              scores, make_ptrs(recv_bufs, world), recv_meta ? make_ptrs(recv_meta, world) : none,
-                                                              recv_score ? make_ptrs(recv_score, world) : none, make_ptrs(arrive, world), my_rank,
-                                                              e_local, cap_rows, n_assign, src_div, C);
+  ep_dispatch_sorted_kernel<<<n_assign, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(src), order, starts, send_base, send_starts, scores,
+                                                              make_ptrs(recv_bufs, world), recv_meta ? make_ptrs(recv_meta, world) : none,
+                                                              recv_score ? make_ptrs(recv_score, world) : none, make_ptrs(arrive, world), world,
+                                                              my_rank, n_experts, e_local, cap_rows, n_assign, src_div, C);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

@@ -344,7 +344,7 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
                                                        c.load_balance_weight, c.router_z_loss_weight)
                 meter = getattr(rt, "load_meter", None)
                 if meter is not None and (meter.always or torch.is_grad_enabled()):
-                    meter.add(rt._layer, idx)
+                    meter.add_counts(rt._layer, plan.counts)
                 if rt is not None:
                     rt.routing_plan = plan                   # picked up by the expert exchange of this layer call
                 if c.n_shared_experts:

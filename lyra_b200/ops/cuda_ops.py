@@ -218,6 +218,14 @@ class _LinearSwiglu(torch.autograd.Function):
 
 
 def linear_swiglu(x, w_up, bias, beta, limit):
+    C, _, H = w_up.shape
+    if H % 8 or C % 8:
+        # widths the tile kernels do not take (TMA rows must be multiples of 16 bytes), e.g. 1080 / 2 hidden units per rank under
+        # tensor parallelism: the PyTorch statement of the same op, differentiable
+        pre = x @ w_up.reshape(C, 2 * H).to(x.dtype)
+        if bias is not None:
+            pre = pre + bias.reshape(2 * H).to(pre.dtype)
+        return ref.swiglu(pre.float().reshape(*pre.shape[:-1], 2, H), beta, limit).to(x.dtype)
     return _LinearSwiglu.apply(x, w_up, bias, beta, limit)
 
 

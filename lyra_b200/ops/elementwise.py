@@ -331,12 +331,13 @@ def combine_rows(rows: torch.Tensor, dest: torch.Tensor, scores: torch.Tensor, F
     return (g * scores.float()[..., None]).sum(1).to(rows.dtype)
 
 
-def combine_rows_bwd(rows, dout, dest, scores, R: int):
-    """Returns ``(d_rows [R, C] with pad rows zero, dscores [F, K])``."""
+def combine_rows_bwd(rows, dout, dest, scores, R: int, dense: bool = False):
+    """Returns ``(d_rows [R, C] with pad rows zero, dscores [F, K])``. ``dense``: ``dest`` covers every one of the ``R`` rows
+    (no padding rows), so the output needs no zero fill."""
     F_, K = scores.shape
     C = rows.shape[1]
     if _has("lyra_combine_rows_bwd") and rows.dtype == BF16:
-        d_rows = torch.zeros(R, C, dtype=BF16, device=rows.device)
+        d_rows = (torch.empty if dense and R == F_ * K else torch.zeros)(R, C, dtype=BF16, device=rows.device)
         dscores = torch.empty(F_, K, dtype=torch.float32, device=rows.device)
         native.check(_lib().lyra_combine_rows_bwd(ptr(rows), ptr(dout), ptr(dest), ptr(scores), ptr(d_rows), ptr(dscores), c_int(F_), c_int(K),
                                                   c_int(C), native.stream_ptr()), "combine_rows_bwd")

@@ -315,15 +315,15 @@ class _Exchange:
                                                 native.ptr(native.status_word()), stream), "wait")
         self.counts_mat = self.counts_slab.view(0, self.W * self.E, torch.int32).clone()   # private copy: the slab is reused by later calls
         nt = self.buf.n_tiles
-        ints = torch.empty(self.E + (self.El + 1) + nt + 1 + ((self.E + 1) + 1 + 2 * nt if tiles else 0), dtype=torch.int32, device=dev)
-        parts = [self.E, self.El + 1, nt, 1] + ([self.E + 1, 1, nt, nt] if tiles else [])
+        ints = torch.empty(self.E + (self.El + 1) + nt + 1 + (2 * (self.E + 1) + 2 * nt if tiles else 0), dtype=torch.int32, device=dev)
+        parts = [self.E, self.El + 1, nt, 1] + ([self.E + 1, self.E + 1, nt, nt] if tiles else [])
         views = torch.split(ints, parts)
         self.send_base, self.offsets, self.tile_group, self.total = views[:4]
         if tiles:
-            self.starts, self.send_rot, self.tile_valid, self.tile_perm = views[4:]
+            self.starts, self.send_starts, self.tile_valid, self.tile_perm = views[4:]
             native.check(self.lib.lyra_ep_layout_tiles(native.ptr(self.counts_mat), self.W, self.rank, self.E, self.El, self.buf.cap,
                                                        native.ptr(self.send_base), native.ptr(self.offsets), native.ptr(self.tile_group),
-                                                       native.ptr(self.total), native.ptr(self.starts), native.ptr(self.send_rot),
+                                                       native.ptr(self.total), native.ptr(self.starts), native.ptr(self.send_starts),
                                                        native.ptr(self.tile_valid), native.ptr(self.tile_perm), native.ptr(native.status_word()),
                                                        stream), "ep_layout_tiles")
         else:
@@ -406,11 +406,11 @@ class _Exchange:
         stream = nat.stream_ptr()
         nat.check(self.lib.lyra_ep_expect_bump(nat.ptr(buf.expect_view(direction)), nat.ptr(self.tile_valid), buf.n_tiles, stream), "ep_expect_bump")
         recv = self._zero_pad(recv_slab)     # padding rows are never written by a sender, so this may run beside the incoming stores
-        nat.check(self.lib.lyra_ep_dispatch_sorted(nat.ptr(src), nat.ptr(self.order), nat.ptr(self.expert_of), nat.ptr(self.starts), nat.ptr(self.send_base),
-                                                   nat.ptr(self.send_rot), nat.ptr(scores) if scores is not None else None, _arr(recv_slab.peer_ptrs),
+        nat.check(self.lib.lyra_ep_dispatch_sorted(nat.ptr(src), nat.ptr(self.order), nat.ptr(self.starts), nat.ptr(self.send_base),
+                                                   nat.ptr(self.send_starts), nat.ptr(scores) if scores is not None else None, _arr(recv_slab.peer_ptrs),
                                                    _arr(meta_slab.peer_ptrs) if meta_slab is not None else None,
                                                    _arr(score_slab.peer_ptrs) if score_slab is not None else None, _arr(buf.arrive_peers(direction)),
-                                                   self.W, self.rank, self.El, buf.cap, self.F * self.K, src_div, self.C, stream), "ep_dispatch_sorted")
+                                                   self.W, self.rank, self.E, self.El, buf.cap, self.F * self.K, src_div, self.C, stream), "ep_dispatch_sorted")
         nat.count_launch(2)
         return recv
 
@@ -553,7 +553,7 @@ class _EPMoEKernel(torch.autograd.Function):
         tiles = ex.tiles
         dout = dout.contiguous()
         ret = bufs["ret"].view(0, F_ * K * C, BF16).view(F_ * K, C)
-        d_ret, dscores = ew.combine_rows_bwd(ret, dout, ident, scores, F_ * K)
+        d_ret, dscores = ew.combine_rows_bwd(ret, dout, ident, scores, F_ * K, dense=True)
         if ctx.scaled:
             # the buffer holds score x row, so <row, dout> = <score x row, dout> / score. A score that underflowed to zero in the
             # softmax (logit gap beyond ~100) has lost its row; its gradient is then taken as zero.

@@ -46,6 +46,12 @@ class ExpertLoadMeter:
         flat = indices.reshape(-1)
         self.counts[row].index_add_(0, flat, torch.ones_like(flat, dtype=torch.int64))   # no state of its own: safe inside a CUDA graph
 
+    def add_counts(self, layer: int, counts: torch.Tensor) -> None:
+        """The same with the per-expert counts already made (the routing kernels produce them)."""
+        row = self._row.get(layer)
+        if row is not None:
+            self.counts[row] += counts[: self.counts.shape[1]]
+
     def reset(self) -> None:
         self.counts.zero_()
 

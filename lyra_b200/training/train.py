@@ -156,6 +156,14 @@ class TrainHooks:
         pass
 
 
+def check_device_status(device: torch.device) -> None:
+    """Raises ``NativeError`` if a kernel on ``device`` has recorded a failure since the last check (CUDA devices only)."""
+    if device.type == "cuda":
+        from lyra_b200.ops import native
+
+        native.check_status()
+
+
 class _Periodic:
     """Decides which of the loop's side jobs fall on a step: a job is due on its own cadence and always on the last step."""
 
@@ -316,10 +324,7 @@ class TrainingRun:
         """Kernels report a wait that ran out (a peer flag, a TMA stage) or an overflowing expert receive buffer through a
         status word instead of trapping; reading it synchronises, so it is read where the loop synchronises anyway. A bad
         status raises: the step's results are garbage and must reach neither the log nor a checkpoint."""
-        if self.device.type == "cuda":
-            from lyra_b200.ops import native
-
-            native.check_status()
+        check_device_status(self.device)
 
     # ------------------------------------------------------------------ side jobs
     def evaluate(self, step: int) -> None:

@@ -24,11 +24,11 @@ def _rank(rank, world, path, leave_at, silent_at, q):
                 q.put((rank, "left", step))
                 return
             if rank == 1 and step == silent_at:
-                time.sleep(3.0)            # alive but stuck: never announces the step
+                time.sleep(9.0)            # alive but stuck: never announces the step
                 q.put((rank, "stuck", step))
                 return
             hb.beat(step)
-            hb.check(step, timeout=1.0)
+            hb.check(step, timeout=4.0)       # generous: on a loaded machine a healthy peer can be a second late
             time.sleep(0.01)               # the "training step"
         hb.leave()
         q.put((rank, "done", 6))

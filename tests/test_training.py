@@ -221,3 +221,28 @@ def test_resume_auto_restarts_an_interrupted_run_with_the_same_command_line(tmp_
     assert main(argv) == 0
     rows = [json.loads(l) for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
     assert [p.name for p in checkpoint_steps(tmp_path / "run")][-1] == "step_00000004" and rows[-1]["step"] == 4
+
+
+def test_a_kernel_failure_stops_the_run_before_it_is_logged_or_checkpointed(tmp_path, monkeypatch):
+    """Kernels report a failed wait or an overflowing buffer through a status word; the loop reads it before every log line and
+    checkpoint. Here the read is faked: from the fourth check on it reports a peer timeout. The run must stop there, and neither
+    the log nor the checkpoint directory may contain the step whose results are suspect."""
+    import lyra_b200.training.train as T
+    from lyra_b200.ops.native import NativeError
+
+    checks = []
+
+    def fake_status(device):
+        checks.append(device)
+        if len(checks) >= 4:
+            raise NativeError("device 0: kernel reported 'timeout waiting for a peer flag'")
+
+    monkeypatch.setattr(T, "check_device_status", fake_status)
+    c = small_config()
+    tcfg = replace(_tcfg(tmp_path), steps=8, log_every=1, checkpoint_every=2, eval_every=None, eval_data_path=None, numerics_every=None)
+    with pytest.raises(NativeError, match="peer flag"):
+        train(ModelWeights.init(0, c), c, tcfg, device="cpu")
+    # checks: log step 1, log step 2, save step 2, log step 3 (raises)
+    rows = [json.loads(l)["step"] for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
+    assert rows == [1, 2]
+    assert [p.name for p in checkpoint_steps(tmp_path / "run")] == ["step_00000002"]
