@@ -50,6 +50,10 @@ def parse_args():
                     help="several GPUs: meter the experts' token counts during warm-up and re-place the experts on the ranks once before the "
                          "timed steps (what `scripts/train.py --rebalance-experts-every N` does periodically; a relabelling of the experts, "
                          "the model is unchanged). --no-rebalance-experts keeps the static placement")
+    ap.add_argument("--memory-mode", default="auto", choices=["auto", "tight", "roomy"],
+                    help="tight: bf16 gradients, no resident bf16 weight copies, SwiGLU pre-activations recomputed (what one GPU needs to hold all "
+                         "17.7 B parameters); roomy: fp32 gradients, bf16 copies, pre-activations kept; auto: tight only when the state would not fit. "
+                         "Running several GPUs in tight mode gives a like-for-like curve against the one-GPU point")
     ap.add_argument("--layers", type=int, default=None, help="debug only: truncate the model (the result is then labelled invalid)")
     return ap.parse_args()
 
@@ -177,7 +181,7 @@ def main() -> None:
 
     n_params = param_count(ModelWeights.spec(mcfg))
     local_params = n_params / world if rt is not None else n_params
-    tight = local_params * 14 > 150e9
+    tight = local_params * 14 > 150e9 if args.memory_mode == "auto" else args.memory_mode == "tight"
     cuda_ops.set_memory_mode(keep_shadows=not tight, grad_dtype=torch.bfloat16 if tight else torch.float32, save_preact=not tight)
 
     if args.impl == "torch":
@@ -294,6 +298,7 @@ def main() -> None:
             "config": {"model": args.variant, "global_batch": B * world * acc, "seq_len": T, "per_gpu_microbatch": f"{B}x{T}",
                        "accumulation_steps": acc, "parallelism": ("single" if world == 1 else f"fsdp+ep{world}"),
                        "optimizer": "muon+adam in timed region", "l2": "per-step working set (weights, activations) far exceeds the 126 MB L2",
+                       "memory_mode": "tight" if tight else "roomy",
                        "grad_dtype": str(cuda_ops.GRAD_DTYPE).replace("torch.", ""), "bf16_weight_copies": cuda_ops.KEEP_SHADOWS,
                        "params": n_params, "valid": valid, **({"expert_placement": placement} if placement is not None else {})},
             "mfu_of_measured_sustained_bf16": round(value * fpt / world / (peak * 1e12), 4),

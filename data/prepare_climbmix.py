@@ -71,17 +71,17 @@ def local_texts(files: Iterable[Path]) -> Iterator[list[str]]:
         yield pending
 
 
-def tokenize_corpus(texts: Iterable[list[str]], tokenizer: LyraTokenizer, writer: ShardWriter, budget: int, num_threads: int) -> int:
-    """Writes documents until ``budget`` tokens are on disk (the last document is cut to fit); returns the tokens written."""
+def tokenize_corpus(texts: Iterable[list[str]], tokenizer: LyraTokenizer, writer: ShardWriter, limit: int, num_threads: int) -> int:
+    """Writes documents until ``limit`` tokens are on disk (the last document is cut to fit); returns the tokens written."""
     written = 0
     for group in texts:
         for ids in tokenizer.encode_ordinary_batch(group, num_threads=num_threads):
             ids.append(tokenizer.eos_token)
-            if written + len(ids) > budget:
-                del ids[budget - written:]
+            if written + len(ids) > limit:
+                del ids[limit - written:]
             writer.write(ids)
             written += len(ids)
-            if written >= budget:
+            if written >= limit:
                 return written
     return written
 

@@ -6,6 +6,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
 
 namespace lyra {
 
@@ -48,6 +52,54 @@ inline int make_tmap(CUtensorMap* out, const void* base, CUtensorMapDataType dt,
     return -2;
   }
   return 0;
+}
+
+// The same, remembered: a training step encodes the same few hundred (address, shape, stride, box) combinations thousands of
+// times (the caching allocator hands the activations of every microbatch the same blocks), and a map depends on nothing else,
+// so a hit can never be stale. Encoding costs a driver call per operand of every GEMM launch; a hit costs a hash lookup.
+struct TmapKey {
+  const void* base;
+  uint64_t dims[5], strides[4];
+  uint32_t box[5];
+  int dt, rank, swz;
+  bool operator==(const TmapKey& o) const { return memcmp(this, &o, sizeof(TmapKey)) == 0; }
+};
+struct TmapKeyHash {
+  size_t operator()(const TmapKey& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    uint64_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(TmapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+    return static_cast<size_t>(h);
+  }
+};
+
+inline int make_tmap_cached(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int rank, const uint64_t* dims,
+                            const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swz) {
+  static std::unordered_map<TmapKey, CUtensorMap, TmapKeyHash> cache;
+  static std::mutex lock;
+  TmapKey key;
+  memset(&key, 0, sizeof(key));                  // padding bytes take part in the comparison
+  key.base = base;
+  key.dt = int(dt);
+  key.rank = rank;
+  key.swz = int(swz);
+  for (int i = 0; i < rank; ++i) {
+    key.dims[i] = dims[i];
+    key.box[i] = box[i];
+  }
+  for (int i = 0; i + 1 < rank; ++i) key.strides[i] = strides_bytes[i];
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = cache.find(key);
+  if (it != cache.end()) {
+    *out = it->second;
+    return 0;
+  }
+  const int rc = make_tmap(out, base, dt, rank, dims, strides_bytes, box, swz);
+  if (rc == 0) {
+    if (cache.size() > (1u << 16)) cache.clear();
+    cache.emplace(key, *out);
+  }
+  return rc;
 }
 
 inline int sm_count() {

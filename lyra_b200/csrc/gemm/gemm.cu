@@ -786,7 +786,7 @@ extern "C" int lyra_gemm_bf16(
     dims[2] = a_grouped ? G : 1; box[2] = 1;
     strides[0] = (uint64_t)lda * 2;
     strides[1] = a_grouped ? (uint64_t)a_group_stride * 2 : dims[1] * strides[0];
-    if (make_tmap(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
+    if (make_tmap_cached(&ta, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
   }
   {
     uint64_t dims[3], strides[2];
@@ -796,7 +796,7 @@ extern "C" int lyra_gemm_bf16(
     dims[2] = b_grouped ? G : 1; box[2] = 1;
     strides[0] = (uint64_t)ldb * 2;
     strides[1] = b_grouped ? (uint64_t)b_group_stride * 2 : dims[1] * strides[0];
-    if (make_tmap(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
+    if (make_tmap_cached(&tb, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   const int code = (a_mn ? 2 : 0) | (b_mn ? 1 : 0);
@@ -871,12 +871,12 @@ extern "C" int lyra_ce_gemm(const void* x, long long ldx, const void* w, long lo
   {
     uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, 1}, strides[2] = {(uint64_t)ldx * 2, (uint64_t)M * ldx * 2};
     uint32_t box[3] = {64, BM, 1};
-    if (make_tmap(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
+    if (make_tmap_cached(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
   }
   {
     uint64_t dims[3] = {(uint64_t)K, (uint64_t)vocab, 1}, strides[2] = {(uint64_t)ldw * 2, (uint64_t)vocab * ldw * 2};
     uint32_t box[3] = {64, 128, 1};
-    if (make_tmap(&tb, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
+    if (make_tmap_cached(&tb, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
   }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   return mode == 0 ? launch_gemm<BN, false, false, EPI_CE_FWD>(ta, tb, p, s) : launch_gemm<BN, false, false, EPI_CE_DZ>(ta, tb, p, s);
@@ -954,12 +954,12 @@ extern "C" int lyra_gemm_allgather_bf16(const void* x, long long ldx, void* w_lo
   {
     uint64_t dims[3] = {(uint64_t)K, (uint64_t)M, 1}, strides[2] = {(uint64_t)ldx * 2, (uint64_t)M * ldx * 2};
     uint32_t box[3] = {64, BM, 1};
-    if (make_tmap(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
+    if (make_tmap_cached(&ta, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -11;
   }
   {
     uint64_t dims[3] = {(uint64_t)N, (uint64_t)K, 1}, strides[2] = {(uint64_t)ldw * 2, (uint64_t)K * ldw * 2};
     uint32_t box[3] = {64, BK, 1};
-    if (make_tmap(&tb, w_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
+    if (make_tmap_cached(&tb, w_local, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return -12;
   }
   return launch_gemm<BN, false, true, EPI_STORE>(ta, tb, p, reinterpret_cast<cudaStream_t>(stream));
 }

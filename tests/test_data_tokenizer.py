@@ -78,7 +78,7 @@ def test_special_tokens_and_batch(tokenizer):
     assert b"".join(tokenizer.decode_single_token_bytes(i) for i in ids).decode() == "tokenization"
 
 
-def test_prepare_script_tokenizes_local_files_up_to_the_budget(tmp_path):
+def test_prepare_script_tokenizes_local_files_up_to_the_limit(tmp_path):
     import importlib.util
     import json
     import sys
