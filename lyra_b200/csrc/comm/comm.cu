@@ -168,6 +168,25 @@ __global__ void reduce_pull_norm_kernel(void* __restrict__ out, PeerPtrs peers, 
   }
 }
 
+// In-switch all-reduce (NVLS) of a small buffer that every rank holds at the same offset of a symmetric allocation bound to an
+// NVLink multicast object: `mc` is the multicast address of that buffer. Rank r owns the r-th slice: one `multimem.ld_reduce`
+// returns the sum over all ranks' copies (added inside the switch: one load instead of `world` peer loads), one `multimem.st`
+// writes the sum back into every rank's copy. The caller brackets the kernel with the flag barrier: every rank's copy written
+// before, every slice stored before anyone reads its own copy.
+__global__ void multimem_all_reduce_kernel(float* mc, long long n4, int world, int my_rank) {
+  const long long per = (n4 + world - 1) / world;
+  const long long lo = per * my_rank, hi = lo + per < n4 ? lo + per : n4;
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi; i += (long long)gridDim.x * blockDim.x) {
+    float4 v;
+    float* a = mc + 4 * i;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "l"(a)
+                 : "memory");
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(a), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ flags
 // Thread r writes `value` into slot [my_rank] of rank r's flag array (after all earlier writes of this stream).
 __global__ void signal_kernel(PeerPtrs flag_arrays, int world, int my_rank, int value) {
@@ -732,6 +751,17 @@ extern "C" int lyra_reduce_pull_norm(void* out, const long long* peer_ptrs, int 
   else if (in_bf16) reduce_pull_norm_kernel<true, false><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
   else if (out_bf16) reduce_pull_norm_kernel<false, true><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
   else reduce_pull_norm_kernel<false, false><<<grid, 256, 0, ST(stream)>>>(out, p, world, n, seg_len, n_seg, partial);
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+// `mc`: multicast address of an fp32 buffer of n elements (n a multiple of 4) present on every rank; see the kernel's comment for
+// the barriers the caller owes.
+extern "C" int lyra_multimem_all_reduce(void* mc, long long n, int world, int my_rank, void* stream) {
+  if (n <= 0) return 0;
+  if (!mc || n % 4 || world < 1 || world > MAX_RANKS || my_rank < 0 || my_rank >= world) return -55;
+  const long long n4 = n / 4, per = (n4 + world - 1) / world;
+  multimem_all_reduce_kernel<<<copy_grid(per), 256, 0, ST(stream)>>>(static_cast<float*>(mc), n4, world, my_rank);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

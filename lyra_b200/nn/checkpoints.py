@@ -45,8 +45,48 @@ _TORCH_DTYPES = {v: k for k, v in _ZARR_DTYPES.items()}
 
 
 # --------------------------------------------------------------------------- paths
+_REMOTES: dict[Path, str] = {}          # local staging directory -> the gs:// location it mirrors
+
+
+def _sync_command() -> list[str]:
+    """The external tool that mirrors a directory to / from object storage: ``LYRA_GS_SYNC`` or ``gsutil -m rsync -r``."""
+    return os.environ.get("LYRA_GS_SYNC", "gsutil -m rsync -r").split()
+
+
 def checkpoint_path(source) -> Path:
-    return Path(os.path.abspath(os.path.expanduser(str(source))))
+    """Local absolute path of a checkpoint or run directory. A ``gs://bucket/dir`` location (the reference accepts those through
+    etils, lyra/nn/checkpoints.py:12-14) is mirrored: it maps to a staging directory under ``LYRA_GS_CACHE`` (default
+    ``~/.cache/lyra_b200/gs``), filled from the bucket the first time it is named in this process (so a resume finds its
+    checkpoints), and pushed back by ``sync_remote`` after every checkpoint and at the end of a run - the run itself reads and
+    writes local files only, as the reference does for its logs."""
+    text = str(source)
+    if not text.startswith("gs://"):
+        return Path(os.path.abspath(os.path.expanduser(text)))
+    cache = Path(os.path.expanduser(os.environ.get("LYRA_GS_CACHE", "~/.cache/lyra_b200/gs")))
+    local = (cache / text.removeprefix("gs://").strip("/")).resolve()
+    if local not in _REMOTES:
+        import subprocess
+
+        local.mkdir(parents=True, exist_ok=True)
+        _REMOTES[local] = text.rstrip("/")
+        done = subprocess.run([*_sync_command(), _REMOTES[local], str(local)], capture_output=True, text=True)
+        if done.returncode != 0 and any(local.iterdir()):
+            raise OSError(f"could not mirror {text} into {local}: {done.stderr.strip()[-300:]}")
+    return local
+
+
+def sync_remote(path) -> bool:
+    """Pushes ``path``'s mirrored root (if it lies in one) back to its ``gs://`` location. Returns whether anything was mirrored."""
+    import subprocess
+
+    path = Path(path).resolve()
+    for local, remote in _REMOTES.items():
+        if path == local or local in path.parents:
+            done = subprocess.run([*_sync_command(), str(local), remote], capture_output=True, text=True)
+            if done.returncode != 0:
+                raise OSError(f"could not push {local} to {remote}: {done.stderr.strip()[-300:]}")
+            return True
+    return False
 
 
 def is_checkpoint(path: Path) -> bool:

@@ -13,6 +13,7 @@ import torch
 import torch.distributed as dist
 
 BF16 = torch.bfloat16
+NVLS = os.environ.get("LYRA_NVLS", "0") == "1"   # replicated-leaf gradients: in-switch all-reduce (multimem) where the allocation has a multicast address
 ALIGN = 256  # bytes; every sub-buffer starts on this boundary so 16-byte vector accesses and TMA bases stay aligned
 
 
@@ -35,6 +36,8 @@ class SymmetricSlab:
         torch.cuda.synchronize(device)
         self.handle = symm_mem.rendezvous(self.buffer, group_name)
         self.peer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        # address through which NVSwitch reduces / broadcasts over every rank's copy (0 where multicast is not available)
+        self.multicast_ptr = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
     def view(self, offset: int, numel: int, dtype: torch.dtype) -> torch.Tensor:
         nbytes = numel * torch.empty((), dtype=dtype).element_size()
@@ -239,6 +242,21 @@ class Comm:
         flat = torch.cat([grads[n].reshape(-1).float() for n in names])
         if not self.p2p or flat.numel() * 4 > self.small_cap:
             dist.all_reduce(flat)
+        elif NVLS and self.small_slab.multicast_ptr:
+            # in-switch reduction: one multimem.ld_reduce per element of this rank's slice instead of `world` peer loads per element
+            nat = self.native
+            n = flat.numel()
+            pad = 4 * self.world
+            npad = (n + pad - 1) // pad * pad
+            stage = self.small_slab.view(0, npad, torch.float32)
+            stage.zero_()
+            stage[:n] = flat
+            self.barrier()
+            nat.check(self.lib.lyra_multimem_all_reduce(ctypes.c_void_p(self.small_slab.multicast_ptr), ctypes.c_longlong(npad), self.world, self.rank,
+                                                        nat.stream_ptr()), "multimem_all_reduce")
+            nat.count_launch()
+            self.barrier()
+            flat = stage[:n].clone()
         else:
             nat = self.native
             n = flat.numel()

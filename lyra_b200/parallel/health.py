@@ -13,7 +13,7 @@ Usage (one ``Heartbeat`` per rank, any ``torch.distributed`` store: ``TCPStore``
         hb.beat(step)                 # "I am about to run step `step`"
         hb.check(step, timeout=30.0)  # raises PeerLost if some rank has not announced `step` in time or announced that it leaves
         train_step(...)
-    hb.leave()                        # tell the others this rank is done
+    hb.done()                         # ran every step: the others' remaining checks pass; hb.leave() = gone early, they stop
 """
 
 from __future__ import annotations
@@ -29,6 +29,7 @@ class PeerLost(RuntimeError):
 
 class Heartbeat:
     LEFT = -1
+    DONE = 1 << 62                    # "past every step": a rank that finished never holds up, or alarms, a slower one
 
     def __init__(self, store, rank: int, world: int, prefix: str = "lyra/hb"):
         self.store, self.rank, self.world, self.prefix = store, rank, world, prefix
@@ -41,6 +42,9 @@ class Heartbeat:
 
     def leave(self) -> None:
         self.store.set(self._key(self.rank), str(self.LEFT))
+
+    def done(self) -> None:
+        self.store.set(self._key(self.rank), str(self.DONE))
 
     def _read(self, rank: int) -> int | None:
         try:

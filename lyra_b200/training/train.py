@@ -18,7 +18,7 @@ import torch
 from lyra_b200.config import ModelConfig
 from lyra_b200.data import DataLoader, DataLoaderConfig
 from lyra_b200.model import ModelWeights
-from lyra_b200.nn.checkpoints import checkpoint_path, checkpoint_run_config, checkpoint_steps, resolve_checkpoint
+from lyra_b200.nn.checkpoints import checkpoint_path, checkpoint_run_config, checkpoint_steps, resolve_checkpoint, sync_remote
 from lyra_b200.training.metrics import RULE, MetricsLogger, format_duration
 from lyra_b200.training.plotting import plot_run
 from lyra_b200.training.probe import Probe, to_floats
@@ -339,6 +339,8 @@ class TrainingRun:
         artifacts = {name: (self.out / name).read_text() for name in RUN_ARTIFACTS if (self.out / name).exists()}
         save_checkpoint(self.out, step, self.state, self.loader.get_state(), self.run_config | {"run_artifacts": artifacts},
                         keep=self.tcfg.checkpoint_keep, rt=self.rt)
+        if self.primary:
+            sync_remote(self.out)                              # a gs:// run directory is a local mirror: push the new checkpoint
         self.hooks.on_checkpoint(step, self.out, self.out)
 
     def replace_experts(self, step: int) -> None:
@@ -390,10 +392,10 @@ class TrainingRun:
                 if sampling:
                     self._sampler(step)
 
-    def close(self) -> None:
+    def close(self, finished: bool = False) -> None:
         if self.heartbeat is not None:   # finished or failed: tell the others now, so that none of them waits out its time limit
             try:
-                self.heartbeat.leave()
+                self.heartbeat.done() if finished else self.heartbeat.leave()
             except Exception:
                 pass
         if self.metrics is not None:
@@ -408,13 +410,16 @@ def train(model: ModelWeights | None, mcfg: ModelConfig, tcfg: TrainingConfig, *
     """Runs (or resumes) training to ``tcfg.steps`` and returns the final state."""
     run = TrainingRun(model, mcfg, tcfg, hooks or TrainHooks(), rt, device)
     began = time.perf_counter()
+    finished = False
     try:
         run.before_first_step()
         for step in range(run.start_step + 1, tcfg.steps + 1):
             run.advance(step)
+        finished = True
     finally:
-        run.close()
+        run.close(finished)
     if run.primary:
         plot_run(run.out)
+        sync_remote(run.out)                                   # logs, plot and the last checkpoint of a gs:// run
         print(f"{RULE}\nTraining finished in {format_duration(time.perf_counter() - began)}\n{RULE}")
     return run.state

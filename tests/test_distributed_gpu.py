@@ -149,3 +149,54 @@ def test_allgather_fused_gemm(tmp_path):
         res = torch.load(tmp_path / f"ag{r}.pt", weights_only=False)
         assert res["rows"] < 1e-2 and res["owner"] < 1e-2, res
         assert res["rows_filled"] and res["owner_filled"], res
+
+
+def _nvls_worker(rank, world, port, tmp):
+    import ctypes
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    device = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=device)
+    try:
+        from lyra_b200.ops import native
+        from lyra_b200.parallel.comm import SymmetricSlab
+
+        lib = native.kernels()
+        n = 4 * world * 1000 + 4 * world          # a multiple of 4 x world
+        slab = SymmetricSlab(n * 4, device, dist.group.WORLD.group_name)
+        result = {"multicast": bool(slab.multicast_ptr)}
+        if slab.multicast_ptr:
+            mine = torch.randn(n, device=device, generator=torch.Generator(device="cuda").manual_seed(10 + rank))
+            slab.view(0, n, torch.float32).copy_(mine)
+            want = mine.clone()
+            dist.all_reduce(want)                 # library sum as the oracle (same addends, possibly another order)
+            torch.cuda.synchronize()
+            dist.barrier()                        # every rank's copy is in place
+            native.check(lib.lyra_multimem_all_reduce(ctypes.c_void_p(slab.multicast_ptr), ctypes.c_longlong(n), world, rank, native.stream_ptr()),
+                         "multimem_all_reduce")
+            torch.cuda.synchronize()
+            dist.barrier()                        # every slice has been stored everywhere
+            got = slab.view(0, n, torch.float32).clone()
+            result["err"] = float((got - want).abs().max())
+            result["scale"] = float(want.abs().max())
+        torch.save(result, f"{tmp}/nvls{rank}.pt")
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_in_switch_all_reduce_of_a_small_buffer(tmp_path):
+    """``multimem.ld_reduce`` / ``multimem.st`` over a symmetric allocation's multicast address against the library all-reduce.
+    No rank leaves while the allocation is bound (the ranks exit together after the last barrier)."""
+    import torch.multiprocessing as mp
+
+    world = 2
+    mp.spawn(_nvls_worker, args=(world, free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        res = torch.load(tmp_path / f"nvls{r}.pt", weights_only=False)
+        if not res["multicast"]:
+            pytest.skip("no NVLink multicast support for symmetric allocations on this machine")
+        assert res["err"] <= 1e-5 * max(1.0, res["scale"]), res

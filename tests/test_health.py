@@ -30,7 +30,7 @@ def _rank(rank, world, path, leave_at, silent_at, q):
             hb.beat(step)
             hb.check(step, timeout=4.0)       # generous: on a loaded machine a healthy peer can be a second late
             time.sleep(0.01)               # the "training step"
-        hb.leave()
+        hb.done()
         q.put((rank, "done", 6))
     except PeerLost as e:
         q.put((rank, f"lost:{e.rank}", step))

@@ -90,3 +90,97 @@ def test_allgather_pieces_cover_b_once_and_in_panel_order(K, N, ctas):
             piece += ctas
     assert per_panel == [n_slabs] * n_panels               # the producer waits for exactly this count (times the epoch)
     assert first_round_panels == set(range(max(first_round_panels) + 1))   # the first wave of pieces fills the leading panels
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Layout arithmetic of the tile-granular expert exchange (csrc/comm/comm.cu: ep_layout_tiles_kernel,
+# ep_dispatch_sorted_kernel), restated for every rank of a small world and checked against each other: what the senders
+# compute as destination rows must tile the receivers' buffers exactly, and the receivers' expectations must equal what arrives.
+def ep_layout(counts, world, rank, e_local, cap_rows):
+    """The receiver / sender side tables of one rank. ``counts[s][e]``: rows rank ``s`` routes to expert ``e``."""
+    E = world * e_local
+    total = [sum(counts[s][e] for s in range(world)) for e in range(E)]
+    base, offsets = [0] * E, []
+    for d in range(world):
+        off = 0
+        for j in range(e_local):
+            e = d * e_local + j
+            base[e] = off
+            if d == rank:
+                offsets.append(min(off, cap_rows))
+            off += (total[e] + 127) // 128 * 128
+        if d == rank:
+            offsets.append(min(off, cap_rows))
+    send_base = [base[e] + sum(counts[s][e] for s in range(rank)) for e in range(E)]
+    starts = [sum(counts[rank][:e]) for e in range(E + 1)]
+    send_starts, run = [], 0
+    for k in range(E):
+        j, t = divmod(k, world)
+        send_starts.append(run)
+        run += counts[rank][((rank + t) % world) * e_local + j]
+    send_starts.append(run)
+    n_tiles = cap_rows // 128
+    group, valid, key = [-1] * n_tiles, [0] * n_tiles, [-1] * n_tiles
+    for t in range(n_tiles):
+        row = t * 128
+        g = next((j for j in range(e_local) if offsets[j] <= row < offsets[j + 1]), -1) if row < offsets[e_local] else -1
+        if g >= 0:
+            e = rank * e_local + g
+            r0 = row - offsets[g]
+            r1 = min(r0 + 128, total[e])
+            lo, step = 0, -1
+            for s in range(world):
+                c = counts[s][e]
+                if c > 0 and lo < r1 and lo + c > r0:
+                    step = max(step, (rank - s + world) % world)
+                lo += c
+            group[t], valid[t], key[t] = g, max(r1 - r0, 0), g * world + step
+    perm = [t for k in range(e_local * world) for t in range(n_tiles) if valid[t] > 0 and key[t] == k]
+    return dict(offsets=offsets, send_base=send_base, starts=starts, send_starts=send_starts, group=group, valid=valid, perm=perm)
+
+
+def ep_send_sequence(lay, world, rank, e_local):
+    """(destination rank, destination row) of every block of ep_dispatch_sorted_kernel, in launch order."""
+    E = world * e_local
+    out = []
+    for i in range(lay["send_starts"][E]):
+        k = max(k for k in range(E) if lay["send_starts"][k] <= i)
+        j, t = divmod(k, world)
+        d = (rank + t) % world
+        e = d * e_local + j
+        out.append((d, lay["send_base"][e] + i - lay["send_starts"][k], j))
+    return out
+
+
+@pytest.mark.parametrize("world, e_local, seed", [(2, 2, 0), (4, 2, 1), (4, 4, 2), (8, 1, 3), (8, 4, 4), (3, 2, 5)])
+def test_exchange_layout_senders_and_receivers_agree(world, e_local, seed):
+    import random
+
+    rng = random.Random(seed)
+    E = world * e_local
+    counts = [[rng.choice([0, 0, 1, 5, 130, 260, 77]) for _ in range(E)] for _ in range(world)]
+    cap = (max(sum(counts[s][e] for s in range(world)) for e in range(E)) // 128 + 2) * 128 * e_local
+    lays = [ep_layout(counts, world, r, e_local, cap) for r in range(world)]
+    landed = [dict() for _ in range(world)]                 # per destination: row -> (source, local expert)
+    for s in range(world):
+        seq = ep_send_sequence(lays[s], world, s, e_local)
+        assert len(seq) == sum(counts[s])
+        assert [j for _, _, j in seq] == sorted(j for _, _, j in seq)          # all of local expert 0 first, then 1, ...
+        for d, row, j in seq:
+            assert row not in landed[d], "two assignments were given the same row"
+            landed[d][row] = (s, j)
+    for d in range(world):
+        lay = lays[d]
+        per_tile = [0] * len(lay["valid"])
+        for row, (s, j) in landed[d].items():
+            assert lay["offsets"][j] <= row < lay["offsets"][j + 1]            # inside its expert's (padded) range
+            per_tile[row // 128] += 1
+        assert per_tile == lay["valid"]                                        # the receiver expects exactly what arrives, tile by tile
+        used = [t for t, v in enumerate(lay["valid"]) if v > 0]
+        assert sorted(lay["perm"]) == used
+        assert [lay["group"][t] for t in lay["perm"]] == sorted(lay["group"][t] for t in lay["perm"])   # visited expert by expert
+        # inside an expert: rows are source-major, every source's rows contiguous and in source order
+        for j in range(e_local):
+            rows = sorted(r for r, (s, jj) in landed[d].items() if jj == j)
+            assert [landed[d][r][0] for r in rows] == sorted(landed[d][r][0] for r in rows)
+            assert rows == list(range(lay["offsets"][j], lay["offsets"][j] + len(rows)))

@@ -246,3 +246,37 @@ def test_a_kernel_failure_stops_the_run_before_it_is_logged_or_checkpointed(tmp_
     rows = [json.loads(l)["step"] for l in (tmp_path / "run" / "metrics.jsonl").read_text().splitlines() if json.loads(l)["kind"] == "train"]
     assert rows == [1, 2]
     assert [p.name for p in checkpoint_steps(tmp_path / "run")] == ["step_00000002"]
+
+
+def test_gs_locations_are_mirrored_through_the_sync_tool(tmp_path, monkeypatch):
+    """``gs://`` run directories: staged locally, pulled once when first named, pushed after a save. The sync tool is replaced by
+    a script that copies between a fake bucket directory and the staging directory."""
+    import stat
+    import sys
+
+    from lyra_b200.nn import checkpoints as C
+
+    bucket = tmp_path / "bucket"
+    (bucket / "runs" / "a" / "step_00000002").mkdir(parents=True)
+    (bucket / "runs" / "a" / "step_00000002" / "_CHECKPOINT_METADATA").write_text("{}")
+    tool = tmp_path / "fake_rsync.py"
+    tool.write_text(
+        "import shutil, sys\n"
+        f"root = {str(bucket)!r}\n"
+        "conv = lambda p: root + '/' + p.removeprefix('gs://fake/') if p.startswith('gs://fake/') else p\n"
+        "src, dst = conv(sys.argv[-2]), conv(sys.argv[-1])\n"
+        "import os\n"
+        "if os.path.isdir(src): shutil.copytree(src, dst, dirs_exist_ok=True)\n")
+    tool.chmod(tool.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("LYRA_GS_SYNC", f"{sys.executable} {tool}")
+    monkeypatch.setenv("LYRA_GS_CACHE", str(tmp_path / "cache"))
+    monkeypatch.setattr(C, "_REMOTES", {})
+    local = C.checkpoint_path("gs://fake/runs/a")
+    assert local == (tmp_path / "cache" / "fake" / "runs" / "a").resolve()
+    assert [p.name for p in C.checkpoint_steps(local)] == ["step_00000002"]          # pulled from the bucket
+    (local / "step_00000004").mkdir()
+    (local / "step_00000004" / "_CHECKPOINT_METADATA").write_text("{}")
+    assert C.sync_remote(local / "step_00000004") is True
+    assert (bucket / "runs" / "a" / "step_00000004" / "_CHECKPOINT_METADATA").is_file()   # pushed back
+    assert C.sync_remote(tmp_path / "elsewhere") is False
+    assert C.checkpoint_path("~/x") == C.checkpoint_path(str(C.Path.home() / "x"))
