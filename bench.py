@@ -309,6 +309,8 @@ def main() -> None:
             "phases": phases,
             "gpu_launches": launches,
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
+            "max_reserved_gb": round(torch.cuda.max_memory_reserved() / 1e9, 1),
+            "allocator_retries": int(torch.cuda.memory_stats().get("num_alloc_retries", 0)),   # > 0: the step ran at the memory limit
             "baseline_note": "the reference's only published end-to-end figure is lyra-small, 34,150 tok/s on one TPU v6e (README.md:33); vs_baseline is that ratio for --variant lyra-small and null for variants without a published number",
         }
         print(json.dumps(line))

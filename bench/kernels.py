@@ -246,6 +246,19 @@ def bench_decode_gemm():
             report(f"decode gemm e4m3 {'tcgen05' if tc else 'dequantise + mma.sync'} {name} G{G} K{K} N{N} rows/group {rows_per} (CUDA graph replay)",
                    time_graph_ms(lambda: decode.decode_gemm(x, w8, offsets=offsets, max_group_rows=rows_per)), bytes_=1.0 * G * K * N)
         del w, w8
+    # one decode step of a 128-expert layer on one rank: 8 tokens x top-4 land on about 28 experts, one or two rows each
+    G, K, N = 128, 2880, 5760
+    torch.manual_seed(0)
+    ids, _ = torch.sort(torch.randint(0, G, (32,), device="cuda"))
+    counts = torch.bincount(ids, minlength=G)
+    offsets = torch.zeros(G + 1, dtype=torch.int32, device="cuda")
+    offsets[1:] = torch.cumsum(counts, 0)
+    active, most = int((counts > 0).sum()), int(counts.max())
+    x = torch.randn(32, K, device="cuda").bfloat16()
+    w8 = quantize((torch.randn(G, K, N, device="cuda") / K ** 0.5).bfloat16(), torch.float8_e4m3fn, block=(64, 64))
+    decode.F8_TENSOR_CORES = True
+    report(f"decode gemm e4m3 tcgen05 gpt-oss-120b up G{G} K{K} N{N} 32 rows on {active} experts (CUDA graph replay)",
+           time_graph_ms(lambda: decode.decode_gemm(x, w8, offsets=offsets, max_group_rows=most)), bytes_=1.0 * active * K * N)
 
 
 BENCHES["decode_gemm"] = bench_decode_gemm

@@ -56,6 +56,9 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="truncate the model to this many layers (0 = all)")
     ap.add_argument("--fp8", action="store_true", help="block-scaled e4m3 expert weights and an e4m3 KV cache")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile-decode", action="store_true",
+                    help="bracket the timed decode with cudaProfilerStart / Stop, so that a profiler started with "
+                         "--profile-from-start off sees the decode steps only (not initialisation or prefill)")
     ap.add_argument("--rebalance", action="store_true",
                     help="expert parallel: one metered warm-up request, then the experts are re-placed on the ranks by its token counts")
     ap.add_argument("--tensor-parallel", action="store_true",
@@ -130,7 +133,11 @@ def main() -> None:
         gen.decode(first, min(args.new, 4))
         t_pre, first = timed(lambda: gen.prefill(prompts))
         l0 = native.launches()
+        if args.profile_decode:
+            torch.cuda.profiler.start()
         t_dec, toks = timed(lambda: gen.decode(first, args.new))
+        if args.profile_decode:
+            torch.cuda.profiler.stop()
         native.check_status()
         if world > 1:   # the job's time is the slowest rank's
             t = torch.tensor([t_pre, t_dec], device=dev)

@@ -4,18 +4,28 @@
 // The running max starts at the sink logit and the normaliser at 1, so the sink is an extra softmax column
 // without a value. Only key tiles that intersect the causal / window band are visited.
 //
-// One CTA per (128-query tile, query head, batch). Tensors are token-major [B, T, N, D] (the layout the
-// projection GEMMs produce), addressed by 4-D TMA maps, so no transposes are needed around the kernel.
+// A work item is a (128-query tile, query head, batch); one persistent CTA per SM walks its share of the items.
+// Tensors are token-major [B, T, N, D] (the layout the projection GEMMs produce), addressed by 4-D TMA maps,
+// so no transposes are needed around the kernel.
+//
+// The key tiles of a query tile are dealt alternately to two softmax groups that never talk to each other
+// until the end: each group has its own score buffer, its own running (max, sum) per row and its own output
+// accumulator in TMEM (2 x 128 score columns + 2 x D output columns), as if the keys were split in two
+// interleaved sequences; the two partial results are merged once, in the epilogue. While one group
+// exponentiates tile j, the tensor core runs the other group's P V and Q K^T, so the two pipes overlap
+// without any per-tile exchange between the groups.
 //   warp 0      : TMA producer (Q once; K and V tiles double-buffered)
-//   warp 1      : tcgen05 issuer:  S = Q K^T (fp32 in TMEM, two buffers)  and  O += P V (TMEM)
-//   warps 2..5  : softmax - one query row per thread via tcgen05.ld, exp2-domain online softmax with lazy
-//                 rescaling of O, P written as bf16 into 128B-swizzled shared memory for the second MMA
+//   warp 1      : tcgen05 issuer:  S_g = Q K_j^T  and  O_g += P_g V_j   (g = j mod 2)
+//   warps 2..5  : softmax group 0, warps 6..9 : softmax group 1 - one query row per thread: the row's 128 scores
+//                 come out of TMEM once, exp2-domain online softmax with lazy rescaling of O_g, and P goes back
+//                 as packed bf16 into the first 64 columns of the same score buffer, from where the second MMA
+//                 takes it as its TMEM operand (no shared-memory staging of P)
 #include "../common/sm100.cuh"
 #include "../common/tmap.h"
 
 namespace lyra {
 
-constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, two groups of four softmax warps (64 of a tile's 128 key columns each)
+constexpr int FA_THREADS = 320;   // TMA warp, MMA warp, two groups of four softmax warps (alternate key tiles)
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr float LN2 = 0.6931471805599453f;
 
@@ -28,6 +38,11 @@ struct FwdParams {
   int* status;
 };
 
+// One work item: a 128-query tile of one (batch, head) and the key tiles inside its band.
+struct FwdItem {
+  int q0, head, b, kvh, jt_begin, n_tiles, qlo;
+};
+
 template <int D>
 __global__ void __launch_bounds__(FA_THREADS, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -35,51 +50,60 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   constexpr int BQ = 128, BKV = 128;
   constexpr int TILE = BQ * D * 2;         // bytes of a 128 x D bf16 tile
   constexpr int HALF = BQ * 128;           // bytes of one 64-column swizzle atom column block (128 rows x 128 B)
-  constexpr int P_BYTES = BQ * BKV * 2;
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t S_COL0 = 0, O_COL = 256;
+  constexpr uint32_t S_COL = 0, O_COL = 256, GROUP_COLS = 128;    // group g: scores at S_COL + 128 g, output at O_COL + 128 g
   constexpr uint32_t IDESC_S = make_idesc(BQ, BKV, 1, 1, 0, 0);   // Q K-major, K K-major
-  constexpr uint32_t IDESC_O = make_idesc(BQ, D, 1, 1, 0, 1);     // P K-major, V MN-major
+  constexpr uint32_t IDESC_O = make_idesc(BQ, D, 1, 1, 0, 1);     // P K-major (TMEM), V MN-major
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + TILE;           // 2 stages
   uint8_t* sV = sK + 2 * TILE;       // 2 stages
-  uint8_t* sP = sV + 2 * TILE;
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full;
-  __shared__ uint64_t x_full[2], l_full;          // row-maximum / row-sum exchange between the two softmax groups
-  __shared__ float xmax[2][2][BQ], xl[2][BQ];
+  __shared__ uint64_t q_full, q_empty, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full[2], o_full, o_empty, l_full;
+  __shared__ float xm[2][2][BQ], xl[2][2][BQ];      // [item parity][group][row]: the groups' row maxima and sums, merged in the epilogue
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * BQ, head = blockIdx.y, b = blockIdx.z;
-  const int kvh = head / (p.Nq / p.Nkv);
 
-  // key tiles that intersect the band of this query tile
-  const int qlo = p.q_start + q0;
-  const int qhi = min(p.q_start + min(q0 + BQ, p.T) - 1, p.S - 1);
-  int klo = p.window > 0 ? max(0, qlo - p.window + 1) : 0;
-  const int jt_begin = klo / BKV;
-  const int jt_end = qhi < 0 ? jt_begin : qhi / BKV + 1;
-  const int n_tiles = max(jt_end - jt_begin, 0);
+  // Persistent: one CTA per SM walks the work items, so TMEM allocation, barrier set-up and the first loads are paid once and
+  // the output pass of one item overlaps the first products of the next. Items are ordered by falling key-tile count (late
+  // query tiles first) and dealt to the CTAs in a serpentine, which evens out the sums without a shared counter.
+  const int n_qt = (p.T + BQ - 1) / BQ;
+  const int per_qt = p.Nq * p.B;
+  const int n_items = n_qt * per_qt;
+  auto item_at = [&](int round, FwdItem& it) -> bool {
+    const int idx = round * int(gridDim.x) + ((round & 1) ? int(gridDim.x) - 1 - int(blockIdx.x) : int(blockIdx.x));
+    if (idx >= n_items) return false;
+    const int rest = idx % per_qt;
+    it.q0 = (n_qt - 1 - idx / per_qt) * BQ;
+    it.head = rest % p.Nq;
+    it.b = rest / p.Nq;
+    it.kvh = it.head / (p.Nq / p.Nkv);
+    it.qlo = p.q_start + it.q0;
+    const int qhi = min(p.q_start + min(it.q0 + BQ, p.T) - 1, p.S - 1);
+    const int klo = p.window > 0 ? max(0, it.qlo - p.window + 1) : 0;
+    it.jt_begin = klo / BKV;
+    const int jt_end = qhi < 0 ? it.jt_begin : qhi / BKV + 1;
+    it.n_tiles = max(jt_end - it.jt_begin, 0);
+    return true;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&q_full), 1);
+    mbar_init(smem_u32(&q_empty), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(smem_u32(&k_full[s]), 1);
       mbar_init(smem_u32(&k_empty[s]), 1);
       mbar_init(smem_u32(&v_full[s]), 1);
       mbar_init(smem_u32(&v_empty[s]), 1);
       mbar_init(smem_u32(&s_full[s]), 1);
-      mbar_init(smem_u32(&s_empty[s]), 256);
-      mbar_init(smem_u32(&x_full[s]), 256);
+      mbar_init(smem_u32(&p_full[s]), 128);
     }
     mbar_init(smem_u32(&l_full), 256);
-    mbar_init(smem_u32(&p_full), 256);
-    mbar_init(smem_u32(&p_empty), 1);
     mbar_init(smem_u32(&o_full), 1);
+    mbar_init(smem_u32(&o_empty), 256);
     abort_flag = 0;
     fence_mbar_init();
   }
@@ -92,73 +116,92 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
   tc_fence_after();
   const uint32_t tmem = tmem_holder;
   volatile int* abortp = &abort_flag;
-#define FA_FAIL(code)                      \
-  {                                        \
-    atomicExch(p.status, code);            \
-    abort_flag = 1;                        \
-    break;                                 \
-  }
+  FwdItem w;
 
+  // Counters that run across the items of this CTA (every role keeps its own copies and advances them the same way):
+  //   t    key tiles so far: stage t & 1 of the K and V rings, parity (t >> 1) & 1
+  //   n    items with at least one key tile so far: parity of q_full / q_empty / o_full / o_empty / l_full
+  //   c_g  tiles given to softmax group g so far: parity of s_full[g] / p_full[g]
   if (warp == 0) {
-    if (lane == 0 && n_tiles > 0) {
+    if (lane == 0) {
       tma_prefetch_desc(&tq);
       tma_prefetch_desc(&tk);
       tma_prefetch_desc(&tv);
-      mbar_expect_tx(smem_u32(&q_full), TILE);
-      for (int h = 0; h < D / 64; ++h) tma_load_4d(smem_u32(sQ + h * HALF), &tq, smem_u32(&q_full), h * 64, q0, head, b);
-      for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int k0 = (jt_begin + j) * BKV;
-        if (!mbar_wait(smem_u32(&k_empty[s]), ph ^ 1, abortp)) FA_FAIL(STATUS_TIMEOUT_EMPTY);
-        mbar_expect_tx(smem_u32(&k_full[s]), TILE);
-        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem_u32(sK + s * TILE + h * HALF), &tk, smem_u32(&k_full[s]), h * 64, k0, kvh, b);
-        if (!mbar_wait(smem_u32(&v_empty[s]), ph ^ 1, abortp)) FA_FAIL(STATUS_TIMEOUT_EMPTY);
-        mbar_expect_tx(smem_u32(&v_full[s]), TILE);
-        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem_u32(sV + s * TILE + h * HALF), &tv, smem_u32(&v_full[s]), h * 64, k0, kvh, b);
+      uint32_t t = 0, n = 0;
+      bool ok = true;
+      for (int round = 0; ok && item_at(round, w); ++round) {
+        if (w.n_tiles == 0) continue;
+        if (!mbar_wait(smem_u32(&q_empty), (n & 1) ^ 1, abortp)) { ok = false; break; }   // the last Q K^T of the previous item retired
+        mbar_expect_tx(smem_u32(&q_full), TILE);
+        for (int h = 0; h < D / 64; ++h) tma_load_4d(smem_u32(sQ + h * HALF), &tq, smem_u32(&q_full), h * 64, w.q0, w.head, w.b);
+        ++n;
+        for (int j = 0; j < w.n_tiles; ++j, ++t) {
+          const int s = t & 1;
+          const uint32_t ph = (t >> 1) & 1;
+          const int k0 = (w.jt_begin + j) * BKV;
+          if (!mbar_wait(smem_u32(&k_empty[s]), ph ^ 1, abortp)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(&k_full[s]), TILE);
+          for (int h = 0; h < D / 64; ++h) tma_load_4d(smem_u32(sK + s * TILE + h * HALF), &tk, smem_u32(&k_full[s]), h * 64, k0, w.kvh, w.b);
+          if (!mbar_wait(smem_u32(&v_empty[s]), ph ^ 1, abortp)) { ok = false; break; }
+          mbar_expect_tx(smem_u32(&v_full[s]), TILE);
+          for (int h = 0; h < D / 64; ++h) tma_load_4d(smem_u32(sV + s * TILE + h * HALF), &tv, smem_u32(&v_full[s]), h * 64, k0, w.kvh, w.b);
+        }
+      }
+      if (!ok) {
+        atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
+        abort_flag = 1;
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && n_tiles > 0) {
-      auto issue_s = [&](int j) -> bool {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&k_full[s]), ph, abortp)) return false;
-        if (!mbar_wait(smem_u32(&s_empty[s]), ph ^ 1, abortp)) return false;
-        tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * TILE);
+    if (lane == 0) {
+      // Tile j of an item belongs to group g = j & 1. MMAs of one thread retire in issue order, so S_g(j + 2) (issued after
+      // P_g(j) V_j) can never overwrite P_g(j) before it was read, and s_full[g] of tile j + 2 tells the group that O_g is quiet
+      // (P_g(j) V_j retired) until the group itself releases the next P.
+      uint32_t t = 0, n = 0, c[2] = {0, 0};
+      bool ok = true;
+      for (int round = 0; ok && item_at(round, w); ++round) {
+        if (w.n_tiles == 0) continue;
+        const uint32_t t0 = t;
+        auto issue_s = [&](int j) -> bool {
+          const int g = j & 1, s = (t0 + j) & 1;
+          if (!mbar_wait(smem_u32(&k_full[s]), ((t0 + j) >> 1) & 1, abortp)) return false;
+          tc_fence_after();
+          const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * TILE);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * HALF + (k % 4) * 32;
-          tc_mma_ss(tmem + S_COL0 + s * BKV, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), IDESC_S, k > 0);
-        }
-        tc_commit(smem_u32(&s_full[s]));
-        tc_commit(smem_u32(&k_empty[s]));
-        return true;
-      };
-      bool ok = mbar_wait(smem_u32(&q_full), 0, abortp);
-      if (ok) ok = issue_s(0);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        if (j + 1 < n_tiles) ok = issue_s(j + 1);
-        if (!ok) break;
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&v_full[s]), ph, abortp)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&p_full), j & 1, abortp)) { ok = false; break; }
-        tc_fence_after();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + s * TILE);
+          for (int k = 0; k < D / 16; ++k) {
+            const uint32_t off = (k / 4) * HALF + (k % 4) * 32;
+            tc_mma_ss(tmem + S_COL + g * GROUP_COLS, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), IDESC_S, k > 0);
+          }
+          tc_commit(smem_u32(&s_full[g]));
+          tc_commit(smem_u32(&k_empty[s]));
+          if (j == w.n_tiles - 1) tc_commit(smem_u32(&q_empty));
+          return true;
+        };
+        ok = mbar_wait(smem_u32(&q_full), n & 1, abortp);
+        if (ok) ok = issue_s(0);
+        if (ok && w.n_tiles > 1) ok = issue_s(1);
+        // the previous item's output must have been read before the first P V of this one overwrites the accumulators
+        if (ok) ok = mbar_wait(smem_u32(&o_empty), (n & 1) ^ 1, abortp);
+        for (int j = 0; j < w.n_tiles && ok; ++j) {
+          const int g = j & 1, s = (t0 + j) & 1;
+          if (!mbar_wait(smem_u32(&v_full[s]), ((t0 + j) >> 1) & 1, abortp)) { ok = false; break; }
+          if (!mbar_wait(smem_u32(&p_full[g]), c[g] & 1, abortp)) { ok = false; break; }
+          ++c[g];
+          tc_fence_after();
+          const uint32_t va = smem_u32(sV + s * TILE);
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          const uint64_t da = make_smem_desc(pa + (k / 4) * HALF + (k % 4) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(va + k * 2048, HALF, 1024);
-          tc_mma_ss(tmem + O_COL, da, db, IDESC_O, (j > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < BKV / 16; ++k)      // 16 keys of P = 8 TMEM columns of packed bf16 pairs
+            tc_mma_ts(tmem + O_COL + g * GROUP_COLS, tmem + S_COL + g * GROUP_COLS + k * 8, make_smem_desc(va + k * 2048, HALF, 1024), IDESC_O,
+                      (j >= 2 || k > 0) ? 1u : 0u);
+          tc_commit(smem_u32(&v_empty[s]));
+          if (j + 2 < w.n_tiles) ok = issue_s(j + 2);
         }
-        tc_commit(smem_u32(&v_empty[s]));
-        tc_commit(smem_u32(&p_empty));
-        if (j == n_tiles - 1) tc_commit(smem_u32(&o_full));
+        if (ok) tc_commit(smem_u32(&o_full));
+        t += w.n_tiles;
+        ++n;
       }
       if (!ok) {
-        atomicExch(p.status, STATUS_TIMEOUT_FULL);
+        atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
         abort_flag = 1;
       }
     }
@@ -167,156 +210,167 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;                  // row of the query tile == TMEM lane
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    const int qpos = p.q_start + q0 + row;                // absolute position of this query
-    const bool row_valid = (q0 + row) < p.T;
-    const int wg = (warp - 2) >> 2;                       // group 0: key columns 0..63 of every tile, group 1: 64..127
-    const float sink2 = p.sinks[head] * LOG2E;
-    float m = sink2, l = wg == 0 ? 1.0f : 0.0f;           // the sink's unit weight is counted once; the groups' sums are added at the end
+    const int g = (warp - 2) >> 2;                        // group 0: key tiles 0, 2, 4, ... of an item; group 1: 1, 3, 5, ...
+    const uint32_t s_addr = tmem + lane_addr + S_COL + g * GROUP_COLS;
+    const uint32_t o_addr = tmem + lane_addr + O_COL + g * GROUP_COLS;
+    const float sc = p.scale_log2;
+    uint32_t n = 0, cg = 0;
     bool failed = false;
 
-    for (int j = 0; j < n_tiles; ++j) {
-      const int s = j & 1;
-      const uint32_t ph = (j >> 1) & 1;
-      const int k0 = (jt_begin + j) * BKV;
-      if (!mbar_wait(smem_u32(&s_full[s]), ph, abortp)) { failed = true; break; }
-      tc_fence_after();
-      const uint32_t s_addr = tmem + lane_addr + S_COL0 + s * BKV;
-      const bool need_mask = (k0 + BKV - 1 > qlo) || (p.window > 0 && k0 < qlo + BQ - p.window + 1) || (k0 + BKV > p.S);
-      const int hi = min(qpos, p.S - 1);                               // last visible key
-      const int lo = p.window > 0 ? qpos - p.window + 1 : 0;           // first visible key
+    for (int round = 0; !failed && item_at(round, w); ++round) {
+      const int qpos = p.q_start + w.q0 + row;              // absolute position of this query
+      const bool row_valid = (w.q0 + row) < p.T;
+      const float sink2 = p.sinks[w.head] * LOG2E;
+      float m = sink2, l = g == 0 ? 1.0f : 0.0f;            // the sink's unit weight is counted once, by group 0
+      const int hi = min(qpos, p.S - 1);                    // last visible key
+      const int lo = p.window > 0 ? qpos - p.window + 1 : 0;   // first visible key
 
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = wg * (BKV / 64); c < (wg + 1) * (BKV / 64); ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        if (!need_mask) {   // interior tile: the maximum of the raw scores, scaled once below (the scale is positive)
+      for (int j = g; j < w.n_tiles; j += 2, ++cg) {
+        const int k0 = (w.jt_begin + j) * BKV;
+        if (!mbar_wait(smem_u32(&s_full[g]), cg & 1, abortp)) { failed = true; break; }
+        tc_fence_after();
+        const bool need_mask = (k0 + BKV - 1 > w.qlo) || (p.window > 0 && k0 < w.qlo + BQ - p.window + 1) || (k0 + BKV > p.S);
+        auto mask = [&](uint32_t (&r)[32], int c) {
+          if (need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
-        } else {
+            for (int i = 0; i < 32; ++i) {
+              const int kk = k0 + c * 32 + i;
+              if (kk > hi || kk < lo) r[i] = 0xff800000u;        // -inf: never the maximum, weight 0
+            }
+          }
+        };
+        // pass 1: the row maximum (the scores are read again below rather than kept: 128 live values per thread do not fit)
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+        {
+          uint32_t ra[32], rb[32];
+          tmem_ld32(s_addr, ra);
+          tmem_ld32(s_addr + 32, rb);
+          tmem_ld_wait();
+          mask(ra, 0);
+          mask(rb, 1);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kk = k0 + c * 32 + i;
-            if (kk <= hi && kk >= lo) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; i += 2) {
+            mx4[0] = fmaxf(mx4[0], fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
+            mx4[1] = fmaxf(mx4[1], fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
+          }
+          tmem_ld32(s_addr + 64, ra);
+          tmem_ld32(s_addr + 96, rb);
+          tmem_ld_wait();
+          mask(ra, 2);
+          mask(rb, 3);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            mx4[2] = fmaxf(mx4[2], fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
+            mx4[3] = fmaxf(mx4[3], fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
           }
         }
-      }
-      mx *= p.scale_log2;
-      // the row maximum over all 128 columns: exchange the two halves (bounded wait, like every other wait here)
-      xmax[s][wg][row] = mx;
-      mbar_arrive(smem_u32(&x_full[s]));
-      if (!mbar_wait(smem_u32(&x_full[s]), ph, abortp)) { failed = true; break; }
-      mx = fmaxf(mx, xmax[s][wg ^ 1][row]);
-      // lazy rescale: keep the old reference max unless the new one exceeds it by more than 2^8
-      float factor = 1.0f;
-      if (mx > m + 8.0f) {
-        factor = exp2f(m - mx);
-        m = mx;
-      }
-      l *= factor;
-      // P(j-1) and the O accumulator must be retired before P is overwritten / O is rescaled
-      if (j > 0) {
-        if (!mbar_wait(smem_u32(&p_empty), (j - 1) & 1, abortp)) { failed = true; break; }
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, factor != 1.0f)) {
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;    // the scale is positive
+        // lazy rescale: keep the old reference max unless the new one exceeds it by more than 2^8
+        float factor = 1.0f;
+        if (mx > m + 8.0f) {
+          factor = exp2f(m - mx);
+          m = mx;
+        }
+        l *= factor;
+        if (j >= 2 && __any_sync(0xffffffffu, factor != 1.0f)) {   // O_g holds tiles j-2, j-4, ...: all retired (see the issuer)
 #pragma unroll 1
-          for (int c = wg; c < D / 32; c += 2) {           // each group rescales half of the accumulator's columns
-            uint32_t r[32];
-            tmem_ld32(tmem + lane_addr + O_COL + c * 32, r);
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t o[32];
+            tmem_ld32(o_addr + c * 32, o);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-            tmem_st32(tmem + lane_addr + O_COL + c * 32, r);
-          }
-          tmem_st_wait();
-        }
-      }
-      // pass 2: probabilities -> shared memory (bf16, K-major 128B swizzle), row sum
-      float sum = 0.0f;
-#pragma unroll 1
-      for (int c = wg * (BKV / 64); c < (wg + 1) * (BKV / 64); ++c) {
-        uint32_t r[32];
-        tmem_ld32(s_addr + c * 32, r);
-        tmem_ld_wait();
-        float pv[32];
-        if (!need_mask) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            pv[i] = exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m));
-            sum += pv[i];
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int kk = k0 + c * 32 + i;
-            pv[i] = (kk > hi || kk < lo) ? 0.f : exp2f(fmaf(__uint_as_float(r[i]), p.scale_log2, -m));
-            sum += pv[i];
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+            tmem_st32(o_addr + c * 32, o);
           }
         }
+        // pass 2: probabilities, as bf16 pairs back into columns 0..63 of the same buffer (column c holds keys 2c and 2c+1;
+        // a column is overwritten only after both scores it replaces were read). The next 64 scores are in flight while 64 are
+        // exponentiated.
+        float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int c16 = c * 4 + q;
-          uint4 o;
-          o.x = pack_bf16(pv[q * 8 + 0], pv[q * 8 + 1]);
-          o.y = pack_bf16(pv[q * 8 + 2], pv[q * 8 + 3]);
-          o.z = pack_bf16(pv[q * 8 + 4], pv[q * 8 + 5]);
-          o.w = pack_bf16(pv[q * 8 + 6], pv[q * 8 + 7]);
-          *reinterpret_cast<uint4*>(sP + (c16 >> 3) * HALF + swz128(row, c16 & 7)) = o;
-        }
-      }
-      l += sum;
-      tc_fence_before();
-      mbar_arrive(smem_u32(&s_empty[s]));
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&p_full));
-    }
-
-    // epilogue: O / l -> bf16, LSE
-    if (!failed && n_tiles > 0) {
-      if (!mbar_wait(smem_u32(&o_full), 0, abortp)) failed = true;
-    }
-    if (failed) {
-      if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
-      abort_flag = 1;
-    } else {
-      tc_fence_after();
-      xl[wg][row] = l;                                      // add the two groups' partial row sums
-      mbar_arrive(smem_u32(&l_full));
-      if (!mbar_wait(smem_u32(&l_full), 0, abortp)) {
-        if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
-        abort_flag = 1;
-      }
-      l = xl[0][row] + xl[1][row];
-      const float inv = 1.0f / l;
-      __nv_bfloat16* orow = p.out + (((long long)b * p.T + (q0 + row)) * p.Nq + head) * D;
-#pragma unroll 1
-      for (int c = wg; c < D / 32; c += 2) {
-        uint32_t r[32];
-        if (n_tiles > 0) {
-          tmem_ld32(tmem + lane_addr + O_COL + c * 32, r);
+        for (int h = 0; h < 2; ++h) {
+          uint32_t ra[32], rb[32], pk[32];
+          tmem_ld32(s_addr + h * 64, ra);
+          tmem_ld32(s_addr + h * 64 + 32, rb);
           tmem_ld_wait();
-        } else {
+          mask(ra, 2 * h);
+          mask(rb, 2 * h + 1);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(ra[i]), sc, -m));
+            const float p1 = exp2f(fmaf(__uint_as_float(ra[i + 1]), sc, -m));
+            const float p2 = exp2f(fmaf(__uint_as_float(rb[i]), sc, -m));
+            const float p3 = exp2f(fmaf(__uint_as_float(rb[i + 1]), sc, -m));
+            sum4[2 * h] += p0 + p1;
+            sum4[2 * h + 1] += p2 + p3;
+            pk[i >> 1] = pack_bf16(p0, p1);
+            pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+          }
+          tmem_st32(s_addr + h * 32, pk);
+        }
+        tmem_st_wait();
+        l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        tc_fence_before();
+        mbar_arrive(smem_u32(&p_full[g]));
+      }
+      if (failed) break;
+
+      // epilogue of the item: merge the two groups, O / l -> bf16, LSE
+      __nv_bfloat16* orow = p.out + (((long long)w.b * p.T + (w.q0 + row)) * p.Nq + w.head) * D;
+      if (w.n_tiles == 0) {                                   // no visible key at all: the sink takes all the weight
+        if (row_valid) {
+          for (int c = g * (D / 2); c < (g + 1) * (D / 2); c += 8) *reinterpret_cast<uint4*>(orow + c) = make_uint4(0u, 0u, 0u, 0u);
+          if (g == 0) p.lse[((long long)w.b * p.Nq + w.head) * p.T + w.q0 + row] = sink2 * LN2;
+        }
+        continue;
+      }
+      const int par = n & 1;
+      xm[par][g][row] = m;
+      xl[par][g][row] = l;
+      mbar_arrive(smem_u32(&l_full));
+      if (!mbar_wait(smem_u32(&o_full), par, abortp)) { failed = true; break; }
+      if (!mbar_wait(smem_u32(&l_full), par, abortp)) { failed = true; break; }
+      tc_fence_after();
+      const bool two = w.n_tiles > 1;                         // group 1 saw at least one tile
+      const float m0 = xm[par][0][row], m1 = xm[par][1][row];
+      const float mt = two ? fmaxf(m0, m1) : m0;
+      const float a0 = exp2f(m0 - mt), a1 = two ? exp2f(m1 - mt) : 0.0f;
+      const float lt = a0 * xl[par][0][row] + a1 * xl[par][1][row];
+      const float w0 = a0 / lt, w1 = a1 / lt;
+#pragma unroll 1
+      for (int c = g; c < D / 32; c += 2) {                   // each group writes half of the columns
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tmem + lane_addr + O_COL + c * 32, r0);
+        if (two) tmem_ld32(tmem + lane_addr + O_COL + GROUP_COLS + c * 32, r1);
+        tmem_ld_wait();
+        float o[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          o[i] = __uint_as_float(r0[i]) * w0;
+          if (two) o[i] = fmaf(__uint_as_float(r1[i]), w1, o[i]);
         }
         if (row_valid) {
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            o.x = pack_bf16(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv);
-            o.y = pack_bf16(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv);
-            o.z = pack_bf16(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv);
-            o.w = pack_bf16(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv);
-            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = o;
+            uint4 v;
+            v.x = pack_bf16(o[q * 8 + 0], o[q * 8 + 1]);
+            v.y = pack_bf16(o[q * 8 + 2], o[q * 8 + 3]);
+            v.z = pack_bf16(o[q * 8 + 4], o[q * 8 + 5]);
+            v.w = pack_bf16(o[q * 8 + 6], o[q * 8 + 7]);
+            *reinterpret_cast<uint4*>(orow + c * 32 + q * 8) = v;
           }
         }
       }
-      if (row_valid && wg == 0) p.lse[((long long)b * p.Nq + head) * p.T + q0 + row] = (m + log2f(l)) * LN2;
+      tc_fence_before();
+      mbar_arrive(smem_u32(&o_empty));                        // the accumulators may be overwritten by the next item
+      if (row_valid && g == 0) p.lse[((long long)w.b * p.Nq + w.head) * p.T + w.q0 + row] = (mt + log2f(lt)) * LN2;
+      ++n;
+    }
+    if (failed) {
+      if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
+      abort_flag = 1;
     }
   }
-#undef FA_FAIL
 
   tc_fence_before();
   __syncthreads();
@@ -357,15 +411,17 @@ extern "C" int lyra_flash_fwd(const void* q, long long q_sb, long long q_st, lon
   FwdParams p;
   p.B = B; p.T = T; p.S = S; p.Nq = Nq; p.Nkv = Nkv; p.window = window; p.q_start = q_start;
   p.scale_log2 = scale * LOG2E; p.sinks = sinks; p.out = reinterpret_cast<__nv_bfloat16*>(out); p.lse = lse; p.status = status;
-  dim3 grid((T + 127) / 128, Nq, B);
+  const long long n_items = (long long)((T + 127) / 128) * Nq * B;
+  const int sms = lyra::sm_count();
+  dim3 grid(n_items < sms ? (unsigned)n_items : (unsigned)sms);          // persistent: one CTA per SM
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   if (D == 128) {
-    constexpr int smem = 6 * 128 * 128 * 2 + 1024;  // Q + 2K + 2V + P
+    constexpr int smem = 5 * 128 * 128 * 2 + 1024;  // Q + 2K + 2V
     static bool once = false;
     if (!once) { if (cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -24; once = true; }
     flash_fwd_kernel<128><<<grid, FA_THREADS, smem, s>>>(tq, tk, tv, p);
   } else {
-    constexpr int smem = 5 * 128 * 64 * 2 + 128 * 128 * 2 + 1024;
+    constexpr int smem = 5 * 128 * 64 * 2 + 1024;
     static bool once = false;
     if (!once) { if (cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -24; once = true; }
     flash_fwd_kernel<64><<<grid, FA_THREADS, smem, s>>>(tq, tk, tv, p);

@@ -287,6 +287,7 @@ int launch_tn(const DGParams& p, int tn, cudaStream_t stream) {
 constexpr int F8_KSTAGE = 128;               // K values per shared-memory stage: 128 rows of 128 weight bytes, 128 bytes per token row
 constexpr int F8_THREADS = 192;              // warp 0: TMA, warp 1: MMA issue + TMEM, warps 2..5: scale-and-accumulate
 constexpr int F8_MAX_KBLOCKS = 64;           // K blocks (scale rows) one CTA can hold
+constexpr int F8_MAX_UNITS = 1024;           // (group, block of token rows) pairs with at least one row that one launch can hold
 
 constexpr int f8_stages(int ntok) { return ntok >= 64 ? 3 : 4; }   // sized so that two CTAs fit one SM (two weight streams in flight)
 // TMEM accumulators per CTA. One K block's round trip (MMA retires -> commit -> epilogue wakes -> tcgen05.ld -> release -> issuer
@@ -309,6 +310,10 @@ struct F8Params {
 struct F8Pass {
   int n0, g, split, r0, cnt;
 };
+struct F8Unit {    // a group's block of token rows
+  int r0;
+  short g, cnt;
+};
 
 template <int NTOK>
 __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x,
@@ -322,11 +327,13 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
   constexpr uint32_t TMEM_COLS = NACC * NTOK;              // 128 or 256: a power of two
   constexpr uint32_t IDESC = make_idesc(128, NTOK, 0, 0, 1, 0);   // e4m3 x e4m3, A (weights) MN-major, B (tokens) K-major
 
-  // Persistent: the grid is a couple of CTAs per SM and each takes work items (panel, group, split) round-robin, panels fastest so
-  // that CTAs running side by side read neighbouring 128-byte pieces of the same weight rows. (One CTA per item spent most of
-  // its life on TMEM allocation, barrier set-up and pipeline fill: 45 us per CTA for 17 us of weight streaming.)
+  // Persistent: the grid is a couple of CTAs per SM and each takes passes round-robin. A pass is one 128-column weight panel
+  // times one unit (a group's block of up to NTOK token rows) times one K split; every pass streams the same number of weight
+  // bytes, and units exist only for groups that received rows, so the CTAs finish together however the rows are spread over the
+  // groups (with a static walk over all groups, a decode step that touches 28 of 128 experts left most CTAs idle while a few
+  // streamed ten panels). Panels run fastest, so CTAs working side by side read neighbouring 128-byte pieces of the same rows.
+  // (One CTA per pass spent most of its life on TMEM allocation, barrier set-up and pipeline fill.)
   const int n_panels = (p.N + 127) / 128;
-  const int n_items = n_panels * p.G * p.splits;
   const int n_steps = p.k_per_split / 32;                  // MMAs (K = 32 each) per pass
   const int n_kb = p.k_per_split / p.bk;                   // K blocks = read-backs per pass
   const int steps_per_kb = p.bk / 32;
@@ -339,7 +346,8 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
   float* ws_s = xs_s + F8_MAX_KBLOCKS * NTOK;                                    // [n_kb][ws_n]
   __shared__ uint64_t full_bar[F8_STAGES], empty_bar[F8_STAGES], tfull_bar[NACC], tempty_bar[NACC];
   __shared__ uint32_t tmem_base_holder;
-  __shared__ int abort_flag;
+  __shared__ int abort_flag, n_units_s;
+  __shared__ F8Unit units[F8_MAX_UNITS];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -364,30 +372,51 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
   const uint32_t tmem_base = tmem_base_holder;
   volatile int* abortp = &abort_flag;
 
-  // the pass sequence of this CTA: `next` advances (item, row block) and fills `ps`; every role runs the same code
-  int item = int(blockIdx.x) - int(gridDim.x), zb = 0, n_zb = 0, gbeg = 0, gend = 0;
+  // the units of this launch, built by every CTA for itself: warp 2 scans the groups' row counts
+  if (warp == 2) {
+    const int per = (p.G + 31) / 32;                       // consecutive groups per lane
+    int mine = 0;
+    for (int g = lane * per; g < min(p.G, (lane + 1) * per); ++g) {
+      const int beg = p.offsets ? p.offsets[g] : 0;
+      const int end = p.offsets ? (p.counts ? beg + p.counts[g] : p.offsets[g + 1]) : p.R;
+      mine += (max(end - beg, 0) + NTOK - 1) / NTOK;
+    }
+    int at = mine;                                          // inclusive scan over the lanes
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, at, d);
+      if (lane >= d) at += up;
+    }
+    if (lane == 31) n_units_s = min(at, F8_MAX_UNITS);
+    at -= mine;
+    for (int g = lane * per; g < min(p.G, (lane + 1) * per); ++g) {
+      const int beg = p.offsets ? p.offsets[g] : 0;
+      const int end = p.offsets ? (p.counts ? beg + p.counts[g] : p.offsets[g + 1]) : p.R;
+      for (int r0 = beg; r0 < end && at < F8_MAX_UNITS; r0 += NTOK, ++at) {
+        units[at].r0 = r0;
+        units[at].g = static_cast<short>(g);
+        units[at].cnt = static_cast<short>(min(NTOK, end - r0));
+      }
+    }
+  }
+  __syncthreads();
+  const int n_units = n_units_s;
+  const int n_passes = n_panels * n_units * p.splits;
+
+  // the pass sequence of this CTA: `next` fills `ps`; every role runs the same code
+  int pass = int(blockIdx.x) - int(gridDim.x);
   F8Pass ps;
   auto next = [&]() -> bool {
-    for (;;) {
-      if (zb + 1 < n_zb) {
-        ++zb;
-      } else {
-        item += gridDim.x;
-        if (item >= n_items) return false;
-        const int panel = item % n_panels, rest = item / n_panels;
-        ps.g = rest % p.G;
-        ps.split = rest / p.G;
-        ps.n0 = panel * 128;
-        gbeg = p.offsets ? p.offsets[ps.g] : 0;
-        gend = p.offsets ? (p.counts ? gbeg + p.counts[ps.g] : p.offsets[ps.g + 1]) : p.R;
-        n_zb = (gend - gbeg + NTOK - 1) / NTOK;            // 0 for a group without rows
-        zb = 0;
-        if (n_zb <= 0) continue;
-      }
-      ps.r0 = gbeg + zb * NTOK;
-      ps.cnt = min(NTOK, gend - ps.r0);
-      return true;
-    }
+    pass += gridDim.x;
+    if (pass >= n_passes) return false;
+    const int panel = pass % n_panels, rest = pass / n_panels;
+    const F8Unit u = units[rest % n_units];
+    ps.split = rest / n_units;
+    ps.n0 = panel * 128;
+    ps.g = u.g;
+    ps.r0 = u.r0;
+    ps.cnt = u.cnt;
+    return true;
   };
 
   if (warp == 0) {
@@ -466,23 +495,25 @@ __global__ void __launch_bounds__(F8_THREADS) decode_gemm_f8_kernel(const __grid
     const int te = threadIdx.x - 64;                        // 0..127 among the four epilogue warps
     uint32_t kc0 = 0;
     bool ok = true;
-    int table_item = -1;
+    int table_g = -1, table_n0 = -1, table_split = -1;
     while (ok && next()) {
       const int col = ps.n0 + quarter * 32 + lane;          // this thread's weight column = TMEM lane
       const int wsel = p.bn >= 128 ? 0 : (quarter * 32 + lane) / p.bn;
       const int kb0 = ps.split * n_kb;
-      // scale tables of this pass (only these four warps touch them): tokens x K blocks, and - once per item - K blocks x column blocks
+      // scale tables of this pass (only these four warps touch them): tokens x K blocks, and K blocks x column blocks
       for (int i = te; i < n_kb * NTOK; i += 128) {
         const int kb = i / NTOK, t = i - kb * NTOK;
         xs_s[i] = t < ps.cnt ? p.xs[static_cast<size_t>(ps.r0 + t) * (p.K / p.bk) + kb0 + kb] : 0.f;
       }
-      if (table_item != item) {
+      if (table_g != ps.g || table_n0 != ps.n0 || table_split != ps.split) {
         for (int i = te; i < n_kb * ws_n; i += 128) {
           const int kb = i / ws_n, jj = i - kb * ws_n;
           const int nb = ps.n0 / p.bn + jj;
           ws_s[i] = nb < p.N / p.bn ? p.ws[(static_cast<size_t>(ps.g) * (p.K / p.bk) + kb0 + kb) * (p.N / p.bn) + nb] : 0.f;
         }
-        table_item = item;
+        table_g = ps.g;
+        table_n0 = ps.n0;
+        table_split = ps.split;
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       float racc[NTOK];
@@ -565,9 +596,10 @@ int launch_f8(const CUtensorMap& tw, const CUtensorMap& tx, const F8Params& p, c
     if (cudaFuncSetAttribute(decode_gemm_f8_kernel<NTOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -91;
     configured[dev] = true;
   }
-  const int items = (p.N + 127) / 128 * p.G * p.splits;
+  if (p.G + (p.R + NTOK - 1) / NTOK > F8_MAX_UNITS) return -93;   // more (group, row block) units than a CTA's table holds
+  const long long most = (long long)((p.N + 127) / 128) * p.splits * (p.G + (p.R + NTOK - 1) / NTOK);   // upper bound of the passes
   const int resident = 2 * lyra::sm_count();               // two CTAs per SM: two weight streams in flight
-  decode_gemm_f8_kernel<NTOK><<<items < resident ? items : resident, F8_THREADS, smem, stream>>>(tw, tx, p);
+  decode_gemm_f8_kernel<NTOK><<<most < resident ? int(most) : resident, F8_THREADS, smem, stream>>>(tw, tx, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -92;
 }
 

@@ -33,6 +33,23 @@ def test_flash_fwd(D, window, T):
     assert torch.equal(out, out2)
 
 
+def test_flash_fwd_rescales_and_merges_the_two_key_streams():
+    """Large score ranges over many key tiles: the running maxima of the even and the odd key tiles drift apart by far more
+    than the lazy-rescale threshold, so both the accumulator rescale and the final merge of the two streams are exercised."""
+    from lyra_b200.ops import attention as A, native
+    from lyra_b200.ops import reference as ref
+
+    q, k, v, sinks = _inputs(1, 4, 2, 1664, 1664, 128, seed=5)
+    q = (q.float() * 6.0).bfloat16()
+    k = k.clone()
+    k[:, :, 1200:1210] *= 3.0                    # a late burst of strong keys, in an odd and an even tile
+    out, lse = A.flash_fwd(q, k, v, sinks, 128 ** -0.5, 0)
+    native.check_status()
+    ro, rl = ref.attention(q.float(), k.float(), v.float(), sinks, 128 ** -0.5, 0)
+    assert (out.float() - ro).abs().max().item() < 4e-2
+    assert (lse - rl).abs().max().item() < 3e-2
+
+
 def test_flash_fwd_offset_queries():
     """T != S: queries start at position q_start of a longer key sequence (chunked prefill)."""
     from lyra_b200.ops import attention as A

@@ -104,7 +104,7 @@ def _swiglu_ref(pre, beta, limit):
 
 
 @pytest.mark.parametrize("quant", [False, True])
-@pytest.mark.parametrize("shape", [(8, 256, 512, 40), (32, 2880, 5760, 96), (4, 128, 64, 70)])
+@pytest.mark.parametrize("shape", [(8, 256, 512, 40), (32, 2880, 5760, 96), (4, 128, 64, 70), (128, 256, 384, 40)])
 def test_decode_gemm_grouped(quant, shape):
     """Small-M grouped product with empty groups, bias and fused SwiGLU against fp32 matmuls of the same (dequantised) weights."""
     from lyra_b200.nn.quant import dequantize, quantize
