@@ -2,11 +2,14 @@
 // and its dsinks reduction, lyra/kernels/flash_attention.py:377-659). Probabilities are recomputed from the
 // stored LSE; dS = P o (dP - delta) with delta = rowsum(O o dO). Two deterministic kernels (no atomics):
 //
-//   dq  kernel: one CTA per (128-query tile, head, batch); per key tile  S = Q K^T, dP = dO V^T (TMEM),
-//               dS -> bf16 shared memory, dQ += dS K (TMEM accumulator across key tiles).
+//   dq  kernel: one CTA per (128-query tile, head, batch); per 64-key tile  S = Q K^T, dP = dO V^T (TMEM),
+//               dS written in place over dP as bf16 and taken from TMEM by dQ += dS K (accumulator across key tiles);
+//               two elementwise groups work on alternate key tiles.
 //   dkv kernel: one CTA per (128-key tile, kv head, batch); loops over the GQA group's query heads and the
 //               64-query tiles inside the band, working in the transposed orientation (keys on TMEM lanes):
-//               S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q. S^T/dP^T are double-buffered in TMEM.
+//               S^T = K Q^T, dP^T = V dO^T, dV += P^T dO, dK += dS^T Q. Two elementwise groups take alternate
+//               iterations, each with its own S^T / dP^T buffers in TMEM, which it turns in place into the bf16
+//               P^T / dS^T operands of the accumulating products (no shared-memory staging).
 // The same shared-memory tile serves as a K-major operand in one product and an MN-major operand in the other
 // (e.g. K in S = Q K^T and in dQ = dS K), so every tile is loaded once per use by TMA.
 #include "../common/sm100.cuh"
@@ -14,8 +17,8 @@
 
 namespace lyra {
 
-constexpr int FB_THREADS = 320;   // dQ kernel: TMA warp, MMA warp and two groups of four elementwise warps (two 32-key chunks of a tile each)
-constexpr int DKV_THREADS = 320;  // dK/dV kernel: the same roles, one 32-query chunk of a tile per group
+constexpr int FB_THREADS = 320;   // dQ kernel: TMA warp, MMA warp and two groups of four elementwise warps (alternate key tiles)
+constexpr int DKV_THREADS = 320;  // dK/dV kernel: the same roles, alternate iterations per group
 constexpr float B_LOG2E = 1.4426950408889634f;
 
 // ---------------------------------------------------------------------------------------------- delta
@@ -54,29 +57,34 @@ struct BwdParams {
 };
 
 // ---------------------------------------------------------------------------------------------- dQ
+constexpr int DQ_STAGES = 4;      // (K, V) tiles of 64 keys in flight
+
 template <int D>
 __global__ void __launch_bounds__(FB_THREADS, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
                     const __grid_constant__ CUtensorMap tv, const __grid_constant__ CUtensorMap tdo, const BwdParams p) {
-  constexpr int BQ = 128, BKV = 128;
-  constexpr int TILE = BQ * D * 2;
-  constexpr int HALF = 128 * 128;
-  constexpr uint32_t TMEM_COLS = 512, S_COL = 0, DP_COL = 128, DQ_COL = 256;
+  constexpr int BQ = 128, BKV = 64;
+  constexpr int TILE = BQ * D * 2;         // Q or dO tile
+  constexpr int KTILE = BKV * D * 2;       // K or V tile of 64 keys
+  constexpr int HALF = 128 * 128;          // one 64-column block of a 128-row tile
+  constexpr int KHALF = 64 * 128;          // one 64-column block of a 64-row tile
+  constexpr uint32_t TMEM_COLS = 512, S_COL = 0, DP_COL = 128, DQ_COL = 256;   // S of group 0 / 1 at 0 / 64, dP at 128 / 192
   constexpr uint32_t IDESC_S = make_idesc(BQ, BKV, 1, 1, 0, 0);
-  constexpr uint32_t IDESC_DQ = make_idesc(BQ, D, 1, 1, 0, 1);
+  constexpr uint32_t IDESC_DQ = make_idesc(BQ, D, 1, 1, 0, 1);                 // dS (TMEM) x K (MN-major)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + TILE;
-  uint8_t* sKV = sDO + TILE;          // 2 stages x (K, V)
-  uint8_t* sDS = sKV + 4 * TILE;
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], sdp_full, sdp_empty, ds_full, ds_empty, dq_full;
+  uint8_t* sKV = sDO + TILE;          // DQ_STAGES x (K, V)
+  __shared__ uint64_t q_full, kv_full[DQ_STAGES], kv_empty[DQ_STAGES], sdp_full[2], ds_full[2], dq_full;
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int q0 = blockIdx.x * BQ, head = blockIdx.y, b = blockIdx.z;
+  // late query tiles see the most keys: they come first in launch order
+  const int per_qt = p.Nq * p.B, n_qt = (p.T + BQ - 1) / BQ;
+  const int q0 = (n_qt - 1 - int(blockIdx.x) / per_qt) * BQ, head = (int(blockIdx.x) % per_qt) % p.Nq, b = (int(blockIdx.x) % per_qt) / p.Nq;
   const int kvh = head / (p.Nq / p.Nkv);
   const int qlo = p.q_start + q0;
   const int qhi = min(p.q_start + min(q0 + BQ, p.T) - 1, p.S - 1);
@@ -86,14 +94,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&q_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < DQ_STAGES; ++s) {
       mbar_init(smem_u32(&kv_full[s]), 1);
       mbar_init(smem_u32(&kv_empty[s]), 1);
     }
-    mbar_init(smem_u32(&sdp_full), 1);
-    mbar_init(smem_u32(&sdp_empty), 256);
-    mbar_init(smem_u32(&ds_full), 256);
-    mbar_init(smem_u32(&ds_empty), 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(smem_u32(&sdp_full[g]), 1);
+      mbar_init(smem_u32(&ds_full[g]), 128);
+    }
     mbar_init(smem_u32(&dq_full), 1);
     abort_flag = 0;
     fence_mbar_init();
@@ -108,6 +116,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   const uint32_t tmem = tmem_holder;
   volatile int* abortp = &abort_flag;
 
+  // Key tile j (64 keys) belongs to elementwise group j & 1; each group has its own S / dP buffers and turns dP in place into the
+  // bf16 dS operand of dQ += dS K, so the groups never wait for each other and the tensor core always has the other group's work.
   if (warp == 0) {
     if (lane == 0 && n_tiles > 0) {
       mbar_expect_tx(smem_u32(&q_full), 2 * TILE);
@@ -116,127 +126,119 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         tma_load_4d(smem_u32(sDO + h * HALF), &tdo, smem_u32(&q_full), h * 64, q0, head, b);
       }
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
+        const int s = j % DQ_STAGES;
+        const uint32_t ph = (j / DQ_STAGES) & 1;
         const int k0 = (jt_begin + j) * BKV;
         if (!mbar_wait(smem_u32(&kv_empty[s]), ph ^ 1, abortp)) {
-          atomicExch(p.status, STATUS_TIMEOUT_EMPTY);
+          atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
           abort_flag = 1;
           break;
         }
-        mbar_expect_tx(smem_u32(&kv_full[s]), 2 * TILE);
+        mbar_expect_tx(smem_u32(&kv_full[s]), 2 * KTILE);
         for (int h = 0; h < D / 64; ++h) {
-          tma_load_4d(smem_u32(sKV + (2 * s) * TILE + h * HALF), &tk, smem_u32(&kv_full[s]), h * 64, k0, kvh, b);
-          tma_load_4d(smem_u32(sKV + (2 * s + 1) * TILE + h * HALF), &tv, smem_u32(&kv_full[s]), h * 64, k0, kvh, b);
+          tma_load_4d(smem_u32(sKV + (2 * s) * KTILE + h * KHALF), &tk, smem_u32(&kv_full[s]), h * 64, k0, kvh, b);
+          tma_load_4d(smem_u32(sKV + (2 * s + 1) * KTILE + h * KHALF), &tv, smem_u32(&kv_full[s]), h * 64, k0, kvh, b);
         }
       }
     }
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
-      bool ok = mbar_wait(smem_u32(&q_full), 0, abortp);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(smem_u32(&kv_full[s]), ph, abortp)) { ok = false; break; }
-        if (!mbar_wait(smem_u32(&sdp_empty), (j & 1) ^ 1, abortp)) { ok = false; break; }
+      // MMAs of one thread retire in issue order: dP_g(j + 2) is issued after dQ += dS_g(j) K_j, so it cannot overwrite dS_g(j) early
+      auto issue_s = [&](int j) -> bool {
+        const int s = j % DQ_STAGES, g = j & 1;
+        if (!mbar_wait(smem_u32(&kv_full[s]), (j / DQ_STAGES) & 1, abortp)) return false;
         tc_fence_after();
         const uint32_t qa = smem_u32(sQ), doa = smem_u32(sDO);
-        const uint32_t ka = smem_u32(sKV + (2 * s) * TILE), va = smem_u32(sKV + (2 * s + 1) * TILE);
+        const uint32_t ka = smem_u32(sKV + (2 * s) * KTILE), va = smem_u32(sKV + (2 * s + 1) * KTILE);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * HALF + (k % 4) * 32;
-          tc_mma_ss(tmem + S_COL, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), IDESC_S, k > 0);
+          const uint32_t off = (k / 4) * HALF + (k % 4) * 32, offk = (k / 4) * KHALF + (k % 4) * 32;
+          tc_mma_ss(tmem + S_COL + g * BKV, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + offk, 16, 1024), IDESC_S, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * HALF + (k % 4) * 32;
-          tc_mma_ss(tmem + DP_COL, make_smem_desc(doa + off, 16, 1024), make_smem_desc(va + off, 16, 1024), IDESC_S, k > 0);
+          const uint32_t off = (k / 4) * HALF + (k % 4) * 32, offk = (k / 4) * KHALF + (k % 4) * 32;
+          tc_mma_ss(tmem + DP_COL + g * BKV, make_smem_desc(doa + off, 16, 1024), make_smem_desc(va + offk, 16, 1024), IDESC_S, k > 0);
         }
-        tc_commit(smem_u32(&sdp_full));
-        // dQ += dS K once the softmax threads have written dS
-        if (!mbar_wait(smem_u32(&ds_full), j & 1, abortp)) { ok = false; break; }
+        tc_commit(smem_u32(&sdp_full[g]));
+        return true;
+      };
+      bool ok = mbar_wait(smem_u32(&q_full), 0, abortp);
+      if (ok) ok = issue_s(0);
+      if (ok && n_tiles > 1) ok = issue_s(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        const int s = j % DQ_STAGES, g = j & 1;
+        if (!mbar_wait(smem_u32(&ds_full[g]), (j >> 1) & 1, abortp)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t dsa = smem_u32(sDS);
+        const uint32_t ka = smem_u32(sKV + (2 * s) * KTILE);
 #pragma unroll
-        for (int k = 0; k < BKV / 16; ++k) {
-          const uint64_t da = make_smem_desc(dsa + (k / 4) * HALF + (k % 4) * 32, 16, 1024);
-          const uint64_t db = make_smem_desc(ka + k * 2048, HALF, 1024);
-          tc_mma_ss(tmem + DQ_COL, da, db, IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < BKV / 16; ++k)     // 16 keys of dS = 8 TMEM columns of packed bf16 pairs
+          tc_mma_ts(tmem + DQ_COL, tmem + DP_COL + g * BKV + k * 8, make_smem_desc(ka + k * 2048, KHALF, 1024), IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(smem_u32(&kv_empty[s]));
-        tc_commit(smem_u32(&ds_empty));
-        if (j == n_tiles - 1) tc_commit(smem_u32(&dq_full));
+        if (j + 2 < n_tiles) ok = issue_s(j + 2);
       }
+      if (ok) tc_commit(smem_u32(&dq_full));
       if (!ok) {
-        atomicExch(p.status, STATUS_TIMEOUT_FULL);
+        atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
         abort_flag = 1;
       }
     }
   } else {
     const int quarter = warp & 3;
-    const int wg = (warp - 2) >> 2;                       // two groups of four warps share each tile's key columns
+    const int g = (warp - 2) >> 2;                        // group 0: key tiles 0, 2, 4, ...; group 1: 1, 3, 5, ...
     const int row = quarter * 32 + lane;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const uint32_t s_addr = tmem + lane_addr + S_COL + g * BKV, dp_addr = tmem + lane_addr + DP_COL + g * BKV;
     const int qpos = p.q_start + q0 + row;
     const bool row_valid = (q0 + row) < p.T;
     const long long stat_idx = ((long long)b * p.Nq + head) * p.T + q0 + row;
     const float lse2 = row_valid ? p.lse[stat_idx] * B_LOG2E : INFINITY;
     const float delta = row_valid ? p.delta[stat_idx] : 0.f;
+    const int hi = min(qpos, p.S - 1);
+    const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
     bool failed = false;
-    for (int j = 0; j < n_tiles; ++j) {
+    for (int j = g; j < n_tiles; j += 2) {
       const int k0 = (jt_begin + j) * BKV;
-      if (!mbar_wait(smem_u32(&sdp_full), j & 1, abortp)) { failed = true; break; }
-      if (j > 0 && !mbar_wait(smem_u32(&ds_empty), (j - 1) & 1, abortp)) { failed = true; break; }
+      if (!mbar_wait(smem_u32(&sdp_full[g]), (j >> 1) & 1, abortp)) { failed = true; break; }
       tc_fence_after();
-      const int hi = min(qpos, p.S - 1);
-      const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
-#pragma unroll 1
-      for (int c = wg * (BKV / 64); c < (wg + 1) * (BKV / 64); ++c) {
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tmem + lane_addr + S_COL + c * 32, rs);
-        tmem_ld32(tmem + lane_addr + DP_COL + c * 32, rp);
+#pragma unroll
+      for (int c = 0; c < BKV / 32; ++c) {
+        uint32_t rs[32], rp[32], pd[16];
+        tmem_ld32(s_addr + c * 32, rs);
+        tmem_ld32(dp_addr + c * 32, rp);
         tmem_ld_wait();
-        float ds[32];
         const int kfirst = k0 + c * 32;
         if (kfirst >= lo && kfirst + 31 <= hi) {           // whole chunk visible (all but the diagonal / band-edge tiles)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float pr = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
-            ds[i] = pr * (__uint_as_float(rp[i]) - delta);
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+            const float p1 = exp2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2));
+            pd[i >> 1] = pack_bf16(p0 * (__uint_as_float(rp[i]) - delta), p1 * (__uint_as_float(rp[i + 1]) - delta));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 32; i += 2) {
             const int kk = kfirst + i;
-            const float pr = (kk > hi || kk < lo) ? 0.f : exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
-            ds[i] = pr * (__uint_as_float(rp[i]) - delta);
+            const float p0 = (kk > hi || kk < lo) ? 0.f : exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse2));
+            const float p1 = (kk + 1 > hi || kk + 1 < lo) ? 0.f : exp2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse2));
+            pd[i >> 1] = pack_bf16(p0 * (__uint_as_float(rp[i]) - delta), p1 * (__uint_as_float(rp[i + 1]) - delta));
           }
         }
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int c16 = c * 4 + q;
-          uint4 o;
-          o.x = pack_bf16(ds[q * 8 + 0], ds[q * 8 + 1]);
-          o.y = pack_bf16(ds[q * 8 + 2], ds[q * 8 + 3]);
-          o.z = pack_bf16(ds[q * 8 + 4], ds[q * 8 + 5]);
-          o.w = pack_bf16(ds[q * 8 + 6], ds[q * 8 + 7]);
-          *reinterpret_cast<uint4*>(sDS + (c16 >> 3) * HALF + swz128(row, c16 & 7)) = o;
-        }
+        tmem_st16(dp_addr + c * 16, pd);                  // in place: column j holds keys 2j and 2j+1, both read above
       }
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&sdp_empty));
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&ds_full));
+      mbar_arrive(smem_u32(&ds_full[g]));
     }
     if (!failed && n_tiles > 0 && !mbar_wait(smem_u32(&dq_full), 0, abortp)) failed = true;
     if (failed) {
-      if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+      if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
       abort_flag = 1;
     } else {
       tc_fence_after();
       __nv_bfloat16* orow = p.dq + (((long long)b * p.T + (q0 + row)) * p.Nq + head) * D;
 #pragma unroll 1
-      for (int c = wg; c < D / 32; c += 2) {
+      for (int c = g; c < D / 32; c += 2) {
         uint32_t r[32];
         if (n_tiles > 0) {
           tmem_ld32(tmem + lane_addr + DQ_COL + c * 32, r);
@@ -273,6 +275,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------------- dK, dV
+constexpr int DKV_STAGES = 4;     // (Q, dO) tiles in flight: the loads run two iterations ahead of the products that free a stage
+
 template <int D>
 __global__ void __launch_bounds__(DKV_THREADS, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__ CUtensorMap tk,
@@ -282,27 +286,26 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   constexpr int QTILE = BQ * D * 2;        // Q or dO tile
   constexpr int KHALF = 128 * 128;         // one 64-column block of a 128-row tile
   constexpr int QHALF = 64 * 128;          // one 64-column block of a 64-row tile
-  constexpr int PT_BYTES = BKV * BQ * 2;   // P^T / dS^T tile: 128 rows x 128 B
   constexpr uint32_t TMEM_COLS = 512;
-  constexpr uint32_t ST_COL = 0;           // S^T buffers at 0, 64; dP^T buffers at 128, 192
+  constexpr uint32_t ST_COL = 0;           // S^T of group 0 / 1 at 0 / 64; dP^T at 128 / 192
   constexpr uint32_t DPT_COL = 128, DK_COL = 256, DV_COL = 384;
   constexpr uint32_t IDESC_ST = make_idesc(BKV, BQ, 1, 1, 0, 0);   // K (K-major) x Q (K-major) -> [keys, q]
-  constexpr uint32_t IDESC_ACC = make_idesc(BKV, D, 1, 1, 0, 1);   // P^T (K-major) x dO/Q (MN-major) -> [keys, d]
+  constexpr uint32_t IDESC_ACC = make_idesc(BKV, D, 1, 1, 0, 1);   // P^T (TMEM) x dO/Q (MN-major) -> [keys, d]
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
   uint8_t* sV = sK + KTILE;
-  uint8_t* sQD = sV + KTILE;               // 2 stages x (Q, dO)
-  uint8_t* sPT = sQD + 4 * QTILE;
-  uint8_t* sDST = sPT + PT_BYTES;
-  __shared__ uint64_t kv_full, qd_full[2], qd_empty[2], st_full[2], st_empty[2], stat_full[2], pt_full, pt_empty, acc_full;
-  __shared__ __align__(16) float s_lse2[2][BQ], s_delta[2][BQ];
+  uint8_t* sQD = sV + KTILE;               // DKV_STAGES x (Q, dO)
+  __shared__ uint64_t kv_full, qd_full[DKV_STAGES], qd_empty[DKV_STAGES], st_full[2], stat_full[2], pt_full[2], acc_full;
+  __shared__ __align__(16) float s_lse2[2][2][BQ], s_delta[2][2][BQ];     // [group][iteration parity][query]
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int k0 = blockIdx.x * BKV, kvh = blockIdx.y, b = blockIdx.z;
+  // early key tiles are seen by the most queries: they come first in launch order, so the long CTAs start first
+  const int per_kt = p.Nkv * p.B;
+  const int k0 = (int(blockIdx.x) / per_kt) * BKV, kvh = (int(blockIdx.x) % per_kt) % p.Nkv, b = (int(blockIdx.x) % per_kt) / p.Nkv;
   const int rep = p.Nq / p.Nkv;
   // queries (indices into T) whose band touches keys [k0, k0 + 127]
   const int khi = min(k0 + BKV, p.S) - 1;
@@ -315,15 +318,15 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
 
   if (threadIdx.x == 0) {
     mbar_init(smem_u32(&kv_full), 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < DKV_STAGES; ++s) {
       mbar_init(smem_u32(&qd_full[s]), 1);
       mbar_init(smem_u32(&qd_empty[s]), 1);
-      mbar_init(smem_u32(&st_full[s]), 1);
-      mbar_init(smem_u32(&st_empty[s]), 256);
-      mbar_init(smem_u32(&stat_full[s]), 256);
     }
-    mbar_init(smem_u32(&pt_full), 256);
-    mbar_init(smem_u32(&pt_empty), 1);
+    for (int g = 0; g < 2; ++g) {
+      mbar_init(smem_u32(&st_full[g]), 1);
+      mbar_init(smem_u32(&stat_full[g]), 128);
+      mbar_init(smem_u32(&pt_full[g]), 128);
+    }
     mbar_init(smem_u32(&acc_full), 1);
     abort_flag = 0;
     fence_mbar_init();
@@ -338,6 +341,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
   const uint32_t tmem = tmem_holder;
   volatile int* abortp = &abort_flag;
 
+  // Iteration `it` (one 64-query tile of one head of the GQA group) belongs to elementwise group it & 1. The groups never meet:
+  // each has its own S^T / dP^T buffers, turns them in place into bf16 P^T / dS^T (two values per 32-bit column), and the two
+  // accumulating products take those as their TMEM operand. While a group exponentiates, the tensor core works for the other one.
   if (warp == 0) {
     if (lane == 0 && n_iter > 0) {
       mbar_expect_tx(smem_u32(&kv_full), 2 * KTILE);
@@ -346,12 +352,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         tma_load_4d(smem_u32(sV + h * KHALF), &tv, smem_u32(&kv_full), h * 64, k0, kvh, b);
       }
       for (int it = 0; it < n_iter; ++it) {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
+        const int s = it % DKV_STAGES;
+        const uint32_t ph = (it / DKV_STAGES) & 1;
         const int head = kvh * rep + it / tiles_per_head;
         const int qi0 = (it_begin + it % tiles_per_head) * BQ;
         if (!mbar_wait(smem_u32(&qd_empty[s]), ph ^ 1, abortp)) {
-          atomicExch(p.status, STATUS_TIMEOUT_EMPTY);
+          atomicCAS(p.status, 0, STATUS_TIMEOUT_EMPTY);
           abort_flag = 1;
           break;
         }
@@ -364,155 +370,128 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     }
   } else if (warp == 1) {
     if (lane == 0 && n_iter > 0) {
+      // MMAs of one thread retire in issue order: S^T_g(it + 2) is issued after the products that read P^T_g(it) / dS^T_g(it),
+      // so the in-place operands cannot be overwritten early.
       auto issue_st = [&](int it) -> bool {
-        const int s = it & 1;
-        const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait(smem_u32(&qd_full[s]), ph, abortp)) return false;
-        if (!mbar_wait(smem_u32(&st_empty[s]), ph ^ 1, abortp)) return false;
+        const int s = it % DKV_STAGES, g = it & 1;
+        if (!mbar_wait(smem_u32(&qd_full[s]), (it / DKV_STAGES) & 1, abortp)) return false;
         tc_fence_after();
         const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
         const uint32_t qa = smem_u32(sQD + (2 * s) * QTILE), doa = smem_u32(sQD + (2 * s + 1) * QTILE);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t offk = (k / 4) * KHALF + (k % 4) * 32, offq = (k / 4) * QHALF + (k % 4) * 32;
-          tc_mma_ss(tmem + ST_COL + s * BQ, make_smem_desc(ka + offk, 16, 1024), make_smem_desc(qa + offq, 16, 1024), IDESC_ST, k > 0);
+          tc_mma_ss(tmem + ST_COL + g * BQ, make_smem_desc(ka + offk, 16, 1024), make_smem_desc(qa + offq, 16, 1024), IDESC_ST, k > 0);
         }
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
           const uint32_t offk = (k / 4) * KHALF + (k % 4) * 32, offq = (k / 4) * QHALF + (k % 4) * 32;
-          tc_mma_ss(tmem + DPT_COL + s * BQ, make_smem_desc(va + offk, 16, 1024), make_smem_desc(doa + offq, 16, 1024), IDESC_ST, k > 0);
+          tc_mma_ss(tmem + DPT_COL + g * BQ, make_smem_desc(va + offk, 16, 1024), make_smem_desc(doa + offq, 16, 1024), IDESC_ST, k > 0);
         }
-        tc_commit(smem_u32(&st_full[s]));
+        tc_commit(smem_u32(&st_full[g]));
         return true;
       };
       bool ok = mbar_wait(smem_u32(&kv_full), 0, abortp);
       if (ok) ok = issue_st(0);
+      if (ok && n_iter > 1) ok = issue_st(1);
       for (int it = 0; it < n_iter && ok; ++it) {
-        if (it + 1 < n_iter) ok = issue_st(it + 1);
-        if (!ok) break;
-        const int s = it & 1;
-        if (!mbar_wait(smem_u32(&pt_full), it & 1, abortp)) { ok = false; break; }
+        const int s = it % DKV_STAGES, g = it & 1;
+        if (!mbar_wait(smem_u32(&pt_full[g]), (it >> 1) & 1, abortp)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t pta = smem_u32(sPT), dsta = smem_u32(sDST);
         const uint32_t qa = smem_u32(sQD + (2 * s) * QTILE), doa = smem_u32(sQD + (2 * s + 1) * QTILE);
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {  // dV += P^T dO
-          tc_mma_ss(tmem + DV_COL, make_smem_desc(pta + k * 32, 16, 1024), make_smem_desc(doa + k * 2048, QHALF, 1024), IDESC_ACC,
-                    (it > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < BQ / 16; ++k)    // dV += P^T dO   (16 queries of P^T = 8 TMEM columns)
+          tc_mma_ts(tmem + DV_COL, tmem + ST_COL + g * BQ + k * 8, make_smem_desc(doa + k * 2048, QHALF, 1024), IDESC_ACC, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
-        for (int k = 0; k < BQ / 16; ++k) {  // dK += dS^T Q
-          tc_mma_ss(tmem + DK_COL, make_smem_desc(dsta + k * 32, 16, 1024), make_smem_desc(qa + k * 2048, QHALF, 1024), IDESC_ACC,
-                    (it > 0 || k > 0) ? 1u : 0u);
-        }
+        for (int k = 0; k < BQ / 16; ++k)    // dK += dS^T Q
+          tc_mma_ts(tmem + DK_COL, tmem + DPT_COL + g * BQ + k * 8, make_smem_desc(qa + k * 2048, QHALF, 1024), IDESC_ACC, (it > 0 || k > 0) ? 1u : 0u);
         tc_commit(smem_u32(&qd_empty[s]));
-        tc_commit(smem_u32(&pt_empty));
-        if (it == n_iter - 1) tc_commit(smem_u32(&acc_full));
+        if (it + 2 < n_iter) ok = issue_st(it + 2);
       }
+      if (ok) tc_commit(smem_u32(&acc_full));
       if (!ok) {
-        atomicExch(p.status, STATUS_TIMEOUT_FULL);
+        atomicCAS(p.status, 0, STATUS_TIMEOUT_FULL);
         abort_flag = 1;
       }
     }
   } else {
     const int quarter = warp & 3;
-    const int row = quarter * 32 + lane;                  // key row
-    const int tid = threadIdx.x - 64;                     // 0..255 among the elementwise threads
-    const int wg = tid >> 7;                              // group 0 takes query columns 0..31 of a tile, group 1 columns 32..63
+    const int row = quarter * 32 + lane;                  // key row == TMEM lane
+    const int g = (warp - 2) >> 2;                        // group 0: iterations 0, 2, 4, ...; group 1: 1, 3, 5, ...
+    const int gt = (threadIdx.x - 64) & 127;              // 0..127 inside the group
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    const uint32_t st_addr = tmem + lane_addr + ST_COL + g * BQ, dpt_addr = tmem + lane_addr + DPT_COL + g * BQ;
     const int kk = k0 + row;
     const bool key_valid = kk < p.S;
     bool failed = false;
-    // per-query statistics (log-sum-exp, delta) of tile `it`, one value per thread of the first group; they are fetched one
-    // iteration ahead so that the global-load latency is off the per-iteration critical path
+    // per-query statistics of iteration `it`: the first 64 threads of the group fetch the log-sum-exp, the others delta, one of
+    // the group's iterations ahead, so that the global-load latency is off the critical path
     auto load_stat = [&](int it) -> float {
       const int head = kvh * rep + it / tiles_per_head;
-      const int qi = (it_begin + it % tiles_per_head) * BQ + (tid & 63);
+      const int qi = (it_begin + it % tiles_per_head) * BQ + (gt & 63);
       const long long idx = ((long long)b * p.Nq + head) * p.T + qi;
-      if (tid < 64) return qi < p.T ? p.lse[idx] * B_LOG2E : INFINITY;
-      if (tid < 128) return qi < p.T ? p.delta[idx] : 0.f;
-      return 0.f;
+      if (gt < 64) return qi < p.T ? p.lse[idx] * B_LOG2E : INFINITY;
+      return qi < p.T ? p.delta[idx] : 0.f;
     };
-    auto publish_stat = [&](int buf, float v) {
-      if (tid < 64) s_lse2[buf][tid] = v;
-      else if (tid < 128) s_delta[buf][tid - 64] = v;
-      mbar_arrive(smem_u32(&stat_full[buf]));
-    };
-    if (n_iter > 0) publish_stat(0, load_stat(0));
-    for (int it = 0; it < n_iter; ++it) {
-      const int s = it & 1;
-      const uint32_t ph = (it >> 1) & 1;
+    float stat = g < n_iter ? load_stat(g) : 0.f;
+    for (int it = g; it < n_iter; it += 2) {
+      const int par = (it >> 1) & 1;
       const int qi0 = (it_begin + it % tiles_per_head) * BQ;
-      const float next_stat = it + 1 < n_iter ? load_stat(it + 1) : 0.f;
-      if (!mbar_wait(smem_u32(&stat_full[s]), ph, abortp)) { failed = true; break; }
-      if (!mbar_wait(smem_u32(&st_full[s]), ph, abortp)) { failed = true; break; }
+      // publish this iteration's statistics (buffer `par`: its readers of two iterations ago passed pt_full since)
+      if (gt < 64) s_lse2[g][par][gt] = stat;
+      else s_delta[g][par][gt - 64] = stat;
+      mbar_arrive(smem_u32(&stat_full[g]));
+      if (it + 2 < n_iter) stat = load_stat(it + 2);
+      if (!mbar_wait(smem_u32(&stat_full[g]), par, abortp)) { failed = true; break; }
+      if (!mbar_wait(smem_u32(&st_full[g]), par, abortp)) { failed = true; break; }
       tc_fence_after();
-      {
-        const int c = wg;                                 // BQ / 32 = 2 column chunks, one per group
-        uint32_t rs[32], rp[32];
-        tmem_ld32(tmem + lane_addr + ST_COL + s * BQ + c * 32, rs);
-        tmem_ld32(tmem + lane_addr + DPT_COL + s * BQ + c * 32, rp);
-        tmem_ld_wait();
-        float pr[32], ds[32];
-        float lse_c[32], del_c[32];                         // this chunk's statistics, fetched 16 bytes at a time
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float4 a = reinterpret_cast<const float4*>(&s_lse2[s][c * 32])[i];
-          const float4 d = reinterpret_cast<const float4*>(&s_delta[s][c * 32])[i];
-          lse_c[4 * i] = a.x; lse_c[4 * i + 1] = a.y; lse_c[4 * i + 2] = a.z; lse_c[4 * i + 3] = a.w;
-          del_c[4 * i] = d.x; del_c[4 * i + 1] = d.y; del_c[4 * i + 2] = d.z; del_c[4 * i + 3] = d.w;
-        }
+      for (int c = 0; c < BQ / 32; ++c) {
+        uint32_t rs[32], rp[32];
+        tmem_ld32(st_addr + c * 32, rs);
+        tmem_ld32(dpt_addr + c * 32, rp);
+        tmem_ld_wait();
+        const float* lse_c = &s_lse2[g][par][c * 32];
+        const float* del_c = &s_delta[g][par][c * 32];
+        uint32_t pp[16], pd[16];
         const int qfirst = p.q_start + qi0 + c * 32;
         if (key_valid && kk <= qfirst && (p.window == 0 || kk > qfirst + 31 - p.window)) {   // whole chunk visible
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            pr[i] = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse_c[i]));
-            ds[i] = pr[i] * (__uint_as_float(rp[i]) - del_c[i]);
+          for (int i = 0; i < 32; i += 2) {
+            const float p0 = exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse_c[i]));
+            const float p1 = exp2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse_c[i + 1]));
+            pp[i >> 1] = pack_bf16(p0, p1);
+            pd[i >> 1] = pack_bf16(p0 * (__uint_as_float(rp[i]) - del_c[i]), p1 * (__uint_as_float(rp[i + 1]) - del_c[i + 1]));
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
+          for (int i = 0; i < 32; i += 2) {
             const int qpos = qfirst + i;
-            const bool vis = key_valid && kk <= qpos && (p.window == 0 || kk > qpos - p.window);
-            pr[i] = vis ? exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse_c[i])) : 0.f;
-            ds[i] = pr[i] * (__uint_as_float(rp[i]) - del_c[i]);
+            const bool v0 = key_valid && kk <= qpos && (p.window == 0 || kk > qpos - p.window);
+            const bool v1 = key_valid && kk <= qpos + 1 && (p.window == 0 || kk > qpos + 1 - p.window);
+            const float p0 = v0 ? exp2f(fmaf(__uint_as_float(rs[i]), p.scale_log2, -lse_c[i])) : 0.f;
+            const float p1 = v1 ? exp2f(fmaf(__uint_as_float(rs[i + 1]), p.scale_log2, -lse_c[i + 1])) : 0.f;
+            pp[i >> 1] = pack_bf16(p0, p1);
+            pd[i >> 1] = pack_bf16(p0 * (__uint_as_float(rp[i]) - del_c[i]), p1 * (__uint_as_float(rp[i + 1]) - del_c[i + 1]));
           }
         }
-        // the previous tile's dV / dK products must have consumed P^T and dS^T before they are overwritten
-        if (it > 0 && !mbar_wait(smem_u32(&pt_empty), (it - 1) & 1, abortp)) failed = true;
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int c16 = c * 4 + q;
-          uint4 o;
-          o.x = pack_bf16(pr[q * 8 + 0], pr[q * 8 + 1]);
-          o.y = pack_bf16(pr[q * 8 + 2], pr[q * 8 + 3]);
-          o.z = pack_bf16(pr[q * 8 + 4], pr[q * 8 + 5]);
-          o.w = pack_bf16(pr[q * 8 + 6], pr[q * 8 + 7]);
-          *reinterpret_cast<uint4*>(sPT + swz128(row, c16)) = o;
-          o.x = pack_bf16(ds[q * 8 + 0], ds[q * 8 + 1]);
-          o.y = pack_bf16(ds[q * 8 + 2], ds[q * 8 + 3]);
-          o.z = pack_bf16(ds[q * 8 + 4], ds[q * 8 + 5]);
-          o.w = pack_bf16(ds[q * 8 + 6], ds[q * 8 + 7]);
-          *reinterpret_cast<uint4*>(sDST + swz128(row, c16)) = o;
-        }
+        // in place: column j of the bf16 operand holds queries 2j and 2j+1, whose fp32 columns were read above
+        tmem_st16(st_addr + c * 16, pp);
+        tmem_st16(dpt_addr + c * 16, pd);
       }
-      if (failed) break;
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(smem_u32(&st_empty[s]));
-      fence_proxy_async_smem();
-      mbar_arrive(smem_u32(&pt_full));
-      // everyone who passed this iteration's stat_full wait has finished iteration it - 1, the last reader of the other buffer
-      if (it + 1 < n_iter) publish_stat(s ^ 1, next_stat);
+      mbar_arrive(smem_u32(&pt_full[g]));
     }
     if (!failed && n_iter > 0 && !mbar_wait(smem_u32(&acc_full), 0, abortp)) failed = true;
     if (failed) {
-      if (lane == 0) atomicExch(p.status, STATUS_TIMEOUT_TMEM);
+      if (lane == 0) atomicCAS(p.status, 0, STATUS_TIMEOUT_TMEM);
       abort_flag = 1;
     } else {
       tc_fence_after();
       const long long o_off = (((long long)b * p.S + kk) * p.Nkv + kvh) * D;
       {
-        const int which = wg;                             // group 0 writes dK, group 1 writes dV
+        const int which = g;                              // group 0 writes dK, group 1 writes dV
         __nv_bfloat16* orow = (which == 0 ? p.dk : p.dv) + o_off;
         const float mul = which == 0 ? p.scale : 1.0f;
         const uint32_t col0 = which == 0 ? DK_COL : DV_COL;
@@ -564,23 +543,25 @@ static int bwd_map(CUtensorMap* m, const void* ptr, int B, int T, int N, int D, 
 template <int D>
 static int launch_bwd(const void* q, const long long* qs, const void* k, const long long* ks, const void* v, const long long* vs,
                       const void* d_o, const long long* dos, const BwdParams& p, cudaStream_t s) {
-  CUtensorMap tq, tk, tv, tdo, tq64, tdo64;
+  CUtensorMap tq, tk, tv, tdo, tq64, tdo64, tk64, tv64;
   if (bwd_map(&tq, q, p.B, p.T, p.Nq, D, qs[0], qs[1], qs[2], 128)) return -31;
   if (bwd_map(&tk, k, p.B, p.S, p.Nkv, D, ks[0], ks[1], ks[2], 128)) return -32;
   if (bwd_map(&tv, v, p.B, p.S, p.Nkv, D, vs[0], vs[1], vs[2], 128)) return -33;
   if (bwd_map(&tdo, d_o, p.B, p.T, p.Nq, D, dos[0], dos[1], dos[2], 128)) return -34;
   if (bwd_map(&tq64, q, p.B, p.T, p.Nq, D, qs[0], qs[1], qs[2], 64)) return -35;
   if (bwd_map(&tdo64, d_o, p.B, p.T, p.Nq, D, dos[0], dos[1], dos[2], 64)) return -36;
-  constexpr int smem_dq = 7 * 128 * D * 2 + 1024 + (D == 64 ? 128 * 128 * 2 - 128 * 64 * 2 : 0);  // Q, dO, 2x(K,V), dS(32 KB)
-  constexpr int smem_dkv = 2 * 128 * D * 2 + 4 * 64 * D * 2 + 2 * 128 * 64 * 2 + 1024;
+  if (bwd_map(&tk64, k, p.B, p.S, p.Nkv, D, ks[0], ks[1], ks[2], 64)) return -32;
+  if (bwd_map(&tv64, v, p.B, p.S, p.Nkv, D, vs[0], vs[1], vs[2], 64)) return -33;
+  constexpr int smem_dq = 2 * 128 * D * 2 + DQ_STAGES * 2 * 64 * D * 2 + 1024;          // Q, dO, stages of (K, V)
+  constexpr int smem_dkv = 2 * 128 * D * 2 + DKV_STAGES * 2 * 64 * D * 2 + 1024;      // K, V, stages of (Q, dO)
   static bool once = false;
   if (!once) {
     if (cudaFuncSetAttribute(flash_bwd_dq_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq) != cudaSuccess) return -37;
     if (cudaFuncSetAttribute(flash_bwd_dkv_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv) != cudaSuccess) return -38;
     once = true;
   }
-  flash_bwd_dq_kernel<D><<<dim3((p.T + 127) / 128, p.Nq, p.B), FB_THREADS, smem_dq, s>>>(tq, tk, tv, tdo, p);
-  flash_bwd_dkv_kernel<D><<<dim3((p.S + 127) / 128, p.Nkv, p.B), DKV_THREADS, smem_dkv, s>>>(tq64, tk, tv, tdo64, p);
+  flash_bwd_dq_kernel<D><<<dim3(((p.T + 127) / 128) * p.Nq * p.B), FB_THREADS, smem_dq, s>>>(tq, tk64, tv64, tdo, p);
+  flash_bwd_dkv_kernel<D><<<dim3(((p.S + 127) / 128) * p.Nkv * p.B), DKV_THREADS, smem_dkv, s>>>(tq64, tk, tv, tdo64, p);
   return 0;
 }
 
