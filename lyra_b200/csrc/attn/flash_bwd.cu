@@ -144,22 +144,20 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       // MMAs of one thread retire in issue order: dP_g(j + 2) is issued after dQ += dS_g(j) K_j, so it cannot overwrite dS_g(j) early
+      const uint64_t dq0 = make_smem_desc(smem_u32(sQ), 16, 1024), ddo0 = make_smem_desc(smem_u32(sDO), 16, 1024);
+      const uint64_t dk0 = make_smem_desc(smem_u32(sKV), 16, 1024);          // K of stage 0 as the K-major operand of S
+      const uint64_t dkmn0 = make_smem_desc(smem_u32(sKV), KHALF, 1024);     // the same tile as the MN-major operand of dQ += dS K
       auto issue_s = [&](int j) -> bool {
         const int s = j % DQ_STAGES, g = j & 1;
         if (!mbar_wait(smem_u32(&kv_full[s]), (j / DQ_STAGES) & 1, abortp)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), doa = smem_u32(sDO);
-        const uint32_t ka = smem_u32(sKV + (2 * s) * KTILE), va = smem_u32(sKV + (2 * s + 1) * KTILE);
+        const uint64_t dk = desc_advance(dk0, (2 * s) * KTILE), dv = desc_advance(dk0, (2 * s + 1) * KTILE);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * HALF + (k % 4) * 32, offk = (k / 4) * KHALF + (k % 4) * 32;
-          tc_mma_ss(tmem + S_COL + g * BKV, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + offk, 16, 1024), IDESC_S, k > 0);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          tc_mma_ss(tmem + S_COL + g * BKV, desc_advance(dq0, (k / 4) * HALF + (k % 4) * 32), desc_advance(dk, (k / 4) * KHALF + (k % 4) * 32), IDESC_S, k > 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t off = (k / 4) * HALF + (k % 4) * 32, offk = (k / 4) * KHALF + (k % 4) * 32;
-          tc_mma_ss(tmem + DP_COL + g * BKV, make_smem_desc(doa + off, 16, 1024), make_smem_desc(va + offk, 16, 1024), IDESC_S, k > 0);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          tc_mma_ss(tmem + DP_COL + g * BKV, desc_advance(ddo0, (k / 4) * HALF + (k % 4) * 32), desc_advance(dv, (k / 4) * KHALF + (k % 4) * 32), IDESC_S, k > 0);
         tc_commit(smem_u32(&sdp_full[g]));
         return true;
       };
@@ -170,10 +168,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         const int s = j % DQ_STAGES, g = j & 1;
         if (!mbar_wait(smem_u32(&ds_full[g]), (j >> 1) & 1, abortp)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t ka = smem_u32(sKV + (2 * s) * KTILE);
+        const uint64_t dkmn = desc_advance(dkmn0, (2 * s) * KTILE);
 #pragma unroll
         for (int k = 0; k < BKV / 16; ++k)     // 16 keys of dS = 8 TMEM columns of packed bf16 pairs
-          tc_mma_ts(tmem + DQ_COL, tmem + DP_COL + g * BKV + k * 8, make_smem_desc(ka + k * 2048, KHALF, 1024), IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(tmem + DQ_COL, tmem + DP_COL + g * BKV + k * 8, desc_advance(dkmn, k * 2048), IDESC_DQ, (j > 0 || k > 0) ? 1u : 0u);
         tc_commit(smem_u32(&kv_empty[s]));
         if (j + 2 < n_tiles) ok = issue_s(j + 2);
       }
@@ -372,22 +370,20 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
     if (lane == 0 && n_iter > 0) {
       // MMAs of one thread retire in issue order: S^T_g(it + 2) is issued after the products that read P^T_g(it) / dS^T_g(it),
       // so the in-place operands cannot be overwritten early.
+      const uint64_t dk0 = make_smem_desc(smem_u32(sK), 16, 1024), dv0 = make_smem_desc(smem_u32(sV), 16, 1024);
+      const uint64_t dq0 = make_smem_desc(smem_u32(sQD), 16, 1024);          // Q of stage 0 as the K-major operand of S^T
+      const uint64_t dqmn0 = make_smem_desc(smem_u32(sQD), QHALF, 1024);     // the same tile as the MN-major operand of dK += dS^T Q
       auto issue_st = [&](int it) -> bool {
         const int s = it % DKV_STAGES, g = it & 1;
         if (!mbar_wait(smem_u32(&qd_full[s]), (it / DKV_STAGES) & 1, abortp)) return false;
         tc_fence_after();
-        const uint32_t ka = smem_u32(sK), va = smem_u32(sV);
-        const uint32_t qa = smem_u32(sQD + (2 * s) * QTILE), doa = smem_u32(sQD + (2 * s + 1) * QTILE);
+        const uint64_t dq = desc_advance(dq0, (2 * s) * QTILE), ddo = desc_advance(dq0, (2 * s + 1) * QTILE);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t offk = (k / 4) * KHALF + (k % 4) * 32, offq = (k / 4) * QHALF + (k % 4) * 32;
-          tc_mma_ss(tmem + ST_COL + g * BQ, make_smem_desc(ka + offk, 16, 1024), make_smem_desc(qa + offq, 16, 1024), IDESC_ST, k > 0);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          tc_mma_ss(tmem + ST_COL + g * BQ, desc_advance(dk0, (k / 4) * KHALF + (k % 4) * 32), desc_advance(dq, (k / 4) * QHALF + (k % 4) * 32), IDESC_ST, k > 0);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint32_t offk = (k / 4) * KHALF + (k % 4) * 32, offq = (k / 4) * QHALF + (k % 4) * 32;
-          tc_mma_ss(tmem + DPT_COL + g * BQ, make_smem_desc(va + offk, 16, 1024), make_smem_desc(doa + offq, 16, 1024), IDESC_ST, k > 0);
-        }
+        for (int k = 0; k < D / 16; ++k)
+          tc_mma_ss(tmem + DPT_COL + g * BQ, desc_advance(dv0, (k / 4) * KHALF + (k % 4) * 32), desc_advance(ddo, (k / 4) * QHALF + (k % 4) * 32), IDESC_ST, k > 0);
         tc_commit(smem_u32(&st_full[g]));
         return true;
       };
@@ -398,13 +394,13 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tq, const __grid_consta
         const int s = it % DKV_STAGES, g = it & 1;
         if (!mbar_wait(smem_u32(&pt_full[g]), (it >> 1) & 1, abortp)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQD + (2 * s) * QTILE), doa = smem_u32(sQD + (2 * s + 1) * QTILE);
+        const uint64_t dqmn = desc_advance(dqmn0, (2 * s) * QTILE), ddomn = desc_advance(dqmn0, (2 * s + 1) * QTILE);
 #pragma unroll
         for (int k = 0; k < BQ / 16; ++k)    // dV += P^T dO   (16 queries of P^T = 8 TMEM columns)
-          tc_mma_ts(tmem + DV_COL, tmem + ST_COL + g * BQ + k * 8, make_smem_desc(doa + k * 2048, QHALF, 1024), IDESC_ACC, (it > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(tmem + DV_COL, tmem + ST_COL + g * BQ + k * 8, desc_advance(ddomn, k * 2048), IDESC_ACC, (it > 0 || k > 0) ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < BQ / 16; ++k)    // dK += dS^T Q
-          tc_mma_ts(tmem + DK_COL, tmem + DPT_COL + g * BQ + k * 8, make_smem_desc(qa + k * 2048, QHALF, 1024), IDESC_ACC, (it > 0 || k > 0) ? 1u : 0u);
+          tc_mma_ts(tmem + DK_COL, tmem + DPT_COL + g * BQ + k * 8, desc_advance(dqmn, k * 2048), IDESC_ACC, (it > 0 || k > 0) ? 1u : 0u);
         tc_commit(smem_u32(&qd_empty[s]));
         if (it + 2 < n_iter) ok = issue_st(it + 2);
       }

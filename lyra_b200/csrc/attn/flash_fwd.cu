@@ -159,6 +159,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
       // (P_g(j) V_j retired) until the group itself releases the next P.
       uint32_t t = 0, n = 0, c[2] = {0, 0};
       bool ok = true;
+      const uint64_t dq0 = make_smem_desc(smem_u32(sQ), 16, 1024), dk0 = make_smem_desc(smem_u32(sK), 16, 1024);
+      const uint64_t dv0 = make_smem_desc(smem_u32(sV), HALF, 1024);         // V as the MN-major operand of O += P V
       for (int round = 0; ok && item_at(round, w); ++round) {
         if (w.n_tiles == 0) continue;
         const uint32_t t0 = t;
@@ -166,12 +168,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           const int g = j & 1, s = (t0 + j) & 1;
           if (!mbar_wait(smem_u32(&k_full[s]), ((t0 + j) >> 1) & 1, abortp)) return false;
           tc_fence_after();
-          const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + s * TILE);
+          const uint64_t dk = desc_advance(dk0, s * TILE);
 #pragma unroll
-          for (int k = 0; k < D / 16; ++k) {
-            const uint32_t off = (k / 4) * HALF + (k % 4) * 32;
-            tc_mma_ss(tmem + S_COL + g * GROUP_COLS, make_smem_desc(qa + off, 16, 1024), make_smem_desc(ka + off, 16, 1024), IDESC_S, k > 0);
-          }
+          for (int k = 0; k < D / 16; ++k)
+            tc_mma_ss(tmem + S_COL + g * GROUP_COLS, desc_advance(dq0, (k / 4) * HALF + (k % 4) * 32), desc_advance(dk, (k / 4) * HALF + (k % 4) * 32), IDESC_S, k > 0);
           tc_commit(smem_u32(&s_full[g]));
           tc_commit(smem_u32(&k_empty[s]));
           if (j == w.n_tiles - 1) tc_commit(smem_u32(&q_empty));
@@ -188,11 +188,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
           if (!mbar_wait(smem_u32(&p_full[g]), c[g] & 1, abortp)) { ok = false; break; }
           ++c[g];
           tc_fence_after();
-          const uint32_t va = smem_u32(sV + s * TILE);
+          const uint64_t dv = desc_advance(dv0, s * TILE);
 #pragma unroll
           for (int k = 0; k < BKV / 16; ++k)      // 16 keys of P = 8 TMEM columns of packed bf16 pairs
-            tc_mma_ts(tmem + O_COL + g * GROUP_COLS, tmem + S_COL + g * GROUP_COLS + k * 8, make_smem_desc(va + k * 2048, HALF, 1024), IDESC_O,
-                      (j >= 2 || k > 0) ? 1u : 0u);
+            tc_mma_ts(tmem + O_COL + g * GROUP_COLS, tmem + S_COL + g * GROUP_COLS + k * 8, desc_advance(dv, k * 2048), IDESC_O, (j >= 2 || k > 0) ? 1u : 0u);
           tc_commit(smem_u32(&v_empty[s]));
           if (j + 2 < w.n_tiles) ok = issue_s(j + 2);
         }

@@ -182,6 +182,11 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
   return d;
 }
 
+// The descriptor of the same layout `byte_off` bytes further on (a multiple of 16; shared-memory addresses stay below 256 KB, so
+// the 14-bit address field cannot carry into the next field). A single thread issues every MMA of a CTA: with short MMAs
+// (N = 64) the address arithmetic of freshly built descriptors, not the tensor core, set the pace; one add per operand does not.
+__device__ __forceinline__ uint64_t desc_advance(uint64_t desc, uint32_t byte_off) { return desc + (byte_off >> 4); }
+
 // Byte offset of element (row, 16-byte chunk) inside a 128B-swizzled tile whose rows are 128 B and
 // whose base is 1024-byte aligned (the layout TMA writes and tcgen05 reads with SWIZZLE_128B).
 __device__ __forceinline__ uint32_t swz128(uint32_t row, uint32_t chunk16) {

@@ -11,6 +11,7 @@
 //                       experts, aux = lb_weight * E * sum_e mean_softmax_e * count_e / (F k) + z_weight * mean(lse^2)
 //   route_scatter_kernel order[start_e + rank] = assignment: the counting-sort permutation (token order kept inside an expert)
 //   route_bwd_kernel    one warp per token: gradient of the logits from the gradients of the scores and of the aux loss
+#include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <math.h>
 #include <stdint.h>
@@ -273,6 +274,29 @@ extern "C" int lyra_route_bwd(const float* logits, const float* bias, const floa
   else if (epl <= 4) LAUNCH_BWD(4);
   else LAUNCH_BWD(8);
 #undef LAUNCH_BWD
+  LYRA_CHECK_LAUNCH();
+  return 0;
+}
+
+// Rows of x in expert order for a handful of tokens: sorted position p takes the row of token order[p] / k, and the inverse
+// permutation dest[order[p]] = p is written on the way (it is what the weighted combine gathers by). One block per position.
+namespace {
+__global__ void gather_by_plan_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ order, int k, int C,
+                                      __nv_bfloat16* __restrict__ out, long long* __restrict__ dest) {
+  const int pos = blockIdx.x;
+  const int a = order[pos];
+  if (threadIdx.x == 0) dest[a] = pos;
+  const uint4* src = reinterpret_cast<const uint4*>(x + static_cast<size_t>(a / k) * C);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(pos) * C);
+  for (int i = threadIdx.x; i < C / 8; i += blockDim.x) dst[i] = src[i];
+}
+}  // namespace
+
+// x [F, C] bf16 (C a multiple of 8), order [A] int32 with A = F k -> out [A, C] bf16, dest [A] int64
+extern "C" int lyra_gather_by_plan(const void* x, const int* order, int A, int k, int C, void* out, long long* dest, void* stream) {
+  if (A <= 0) return 0;
+  if (C % 8 || k < 1) return -61;
+  gather_by_plan_kernel<<<A, 128, 0, ST(stream)>>>(reinterpret_cast<const __nv_bfloat16*>(x), order, k, C, reinterpret_cast<__nv_bfloat16*>(out), dest);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

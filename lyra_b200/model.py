@@ -327,9 +327,10 @@ run (the experts chosen by every MoE layer call are recorded) and flip ``replay`
 experts instead of its own top-k: near-tie choices that flip between two bf16 paths no longer blur the comparison."""
 
 
-def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE, rt=None):
+def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE, rt=None, plan_out: list | None = None):
     """fp32 router, top-k over routed experts, softmax over the selected logits, shared experts appended
-    with score 1 (lyra/model.py:451-480). Returns ``(scores [F, K], indices [F, K], aux_loss)``."""
+    with score 1 (lyra/model.py:451-480). Returns ``(scores [F, K], indices [F, K], aux_loss)``. When the routing kernels
+    ran, their ``RoutingPlan`` (counts, offsets and the expert-sorted order of the routed choices) is appended to ``plan_out``."""
     c = config
     W = (lambda p: rt.materialize(p) if rt is not None else p)
     k = c.n_active_routed_experts
@@ -347,6 +348,8 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
                     meter.add_counts(rt._layer, plan.counts)
                 if rt is not None:
                     rt.routing_plan = plan                   # picked up by the expert exchange of this layer call
+                if plan_out is not None:
+                    plan_out.append(plan)
                 if c.n_shared_experts:
                     shared = torch.arange(c.n_routed_experts, c.n_experts, device=idx.device, dtype=idx.dtype)
                     idx = torch.cat([idx, shared[None].expand(t.shape[0], -1)], dim=-1)
@@ -403,7 +406,8 @@ def moe_apply(x, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE,
         probe.tensor("norm_out", xn)
         xn = xn.reshape(B * T, C)
         with scope("route_tokens"):
-            scores, indices, aux = route_tokens(xn, w, c, probe=probe, rt=rt)
+            plans: list = []
+            scores, indices, aux = route_tokens(xn, w, c, probe=probe, rt=rt, plan_out=plans)
         tp = rt.tp_size if rt is not None else 1
         # tensor parallel: every rank holds a slice of each expert's hidden units; the partial outputs are summed below, so the
         # (replicated) down-projection bias enters as bias / tp on every rank (lyra/model.py:549)
@@ -414,7 +418,7 @@ def moe_apply(x, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PROBE,
             t = rt.ep_moe(xn, scores, indices, w, c)
         elif c.mode == Mode.DECODE and ops.use_kernels(xn, impl) and not xn.requires_grad:
             t = ops._cuda().decode_moe(xn, scores, indices, w.mlp_up, w.mlp_up_bias, w.mlp_down, down_bias,
-                                       c.swiglu_beta, c.swiglu_limit)
+                                       c.swiglu_beta, c.swiglu_limit, plans[0] if plans and not c.n_shared_experts else None)
         else:
             up, down = w.mlp_up, w.mlp_down
             if isinstance(up, QArray):

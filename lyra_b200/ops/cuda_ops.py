@@ -259,10 +259,10 @@ def decode_attention(q, k_cache, v_cache, sinks, scale, window, pos, pos_dev=Non
     return dec.decode_attention(q, k_cache, v_cache, sinks, scale, window, int(pos), pos_dev=pos_dev)
 
 
-def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit):
+def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit, plan=None):
     from lyra_b200.ops import decode as dec
 
-    return dec.decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit)
+    return dec.decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit, plan)
 
 
 # --------------------------------------------------------------------------- fused linear cross-entropy

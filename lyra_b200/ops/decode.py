@@ -200,9 +200,11 @@ F8_TENSOR_CORES = _os.environ.get("LYRA_DECODE_F8_TC", "1") != "0"   # quantised
 DECODE_GEMM_MAX_ROWS = int(_os.environ.get("LYRA_DECODE_GEMM_MAX_ROWS", "512"))   # assignments (tokens x experts per token); above this the 128-row-tile tcgen05 grouped GEMM takes over
 
 
-def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit):
+def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limit, plan=None):
     """Expert MLP for a handful of tokens (role of lyra/kernels/decode_gemm.py): rows sorted by expert without padding,
-    two weight-streaming products (SwiGLU fused into the first one's finishing pass), weighted combine."""
+    two weight-streaming products (SwiGLU fused into the first one's finishing pass), weighted combine. ``plan``: the routing
+    kernels' counts / offsets / expert-sorted order for exactly these ``indices`` (no shared experts appended), which replaces
+    the sort-and-count glue below by one gather launch."""
     from lyra_b200.ops import cuda_ops
     from lyra_b200.ops import elementwise as ew
     from lyra_b200.ops import reference as ref
@@ -221,14 +223,20 @@ def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limi
     force = _os.environ.get("LYRA_DECODE_MOE_SMALL_M", "0") == "1"
     small = F_ * K <= DECODE_GEMM_MAX_ROWS and (up_q or down_q or force)
     if small and decode_gemm_supported(C, N_up, wu) and decode_gemm_supported(H, C, wd):
-        flat = indices.reshape(-1)
-        counts = ref.count_ids(flat, E)
-        offsets = torch.zeros(E + 1, dtype=torch.int32, device=xn.device)
-        offsets[1:] = torch.cumsum(counts, 0)
-        order = torch.argsort(flat, stable=True)
-        dest = torch.empty_like(order)
-        dest[order] = torch.arange(order.numel(), device=order.device)
-        x_sorted = xn.to(BF16)[order // K].contiguous()
+        if plan is not None and plan.counts.numel() == E and plan.order.numel() == F_ * K and C % 8 == 0:
+            from lyra_b200.ops import routing
+
+            offsets = plan.starts
+            x_sorted, dest = routing.gather_by_plan(xn.to(BF16).contiguous(), plan, K)
+        else:
+            flat = indices.reshape(-1)
+            counts = ref.count_ids(flat, E)
+            offsets = torch.zeros(E + 1, dtype=torch.int32, device=xn.device)
+            offsets[1:] = torch.cumsum(counts, 0)
+            order = torch.argsort(flat, stable=True)
+            dest = torch.empty_like(order)
+            dest[order] = torch.arange(order.numel(), device=order.device)
+            x_sorted = xn.to(BF16)[order // K].contiguous()
         ub = up_bias.reshape(E, N_up) if up_bias is not None else None
         db = down_bias.reshape(E, C) if down_bias is not None else None
         usual = -(-2 * F_ * K // E)                            # twice the balanced rows per expert

@@ -74,3 +74,15 @@ def route(logits: torch.Tensor, bias: torch.Tensor | None, k: int, lb_weight: fl
     """``logits [F, Er]`` fp32 (router product without the bias) -> ``(scores [F, k], idx [F, k] int64, aux, RoutingPlan)``."""
     scores, idx, aux, counts, starts, order, rank = _Route.apply(logits.float(), bias, k, lb_weight, z_weight)
     return scores, idx, aux, RoutingPlan(counts, starts, order, rank)
+
+
+def gather_by_plan(x: torch.Tensor, plan: RoutingPlan, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Rows of ``x [F, C]`` (bf16) in the plan's expert order, and ``dest [F k]`` (int64) with ``dest[assignment] = sorted
+    position``: what a small-batch expert product and its weighted combine need, in one launch."""
+    A, C = plan.order.numel(), x.shape[1]
+    out = torch.empty(A, C, dtype=torch.bfloat16, device=x.device)
+    dest = torch.empty(A, dtype=torch.int64, device=x.device)
+    native.check(native.kernels().lyra_gather_by_plan(ptr(x), ptr(plan.order), c_int(A), c_int(k), c_int(C), ptr(out), ptr(dest),
+                                                      native.stream_ptr()), "lyra_gather_by_plan")
+    native.count_launch()
+    return out, dest

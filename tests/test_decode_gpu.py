@@ -209,6 +209,25 @@ def test_decode_moe_matches_grouped_path(monkeypatch):
     assert (a.float() - b.float()).abs().max().item() < 3e-2
 
 
+def test_decode_moe_takes_the_routing_kernels_plan(monkeypatch):
+    """With the plan of the routing kernels (offsets and expert-sorted order) the small-batch expert path skips its own sort and
+    count and gives the same output bit for bit."""
+    from lyra_b200.ops import decode, routing
+
+    F_, K, E, C, H = 12, 4, 32, 256, 128
+    torch.manual_seed(12)
+    xn = torch.randn(F_, C, device="cuda").bfloat16()
+    logits = torch.randn(F_, E, device="cuda")
+    w_up = (torch.randn(E, C, 2, H, device="cuda") / C ** 0.5).bfloat16()
+    w_down = (torch.randn(E, H, C, device="cuda") / H ** 0.5).bfloat16()
+    monkeypatch.setenv("LYRA_DECODE_MOE_SMALL_M", "1")
+    with torch.no_grad():
+        scores, indices, _, plan = routing.route(logits, None, K, 0.0, 0.0)
+        a = decode.decode_moe(xn, scores, indices, w_up, None, w_down, None, 1.702, 7.0, plan=plan)
+        b = decode.decode_moe(xn, scores, indices, w_up, None, w_down, None, 1.702, 7.0)
+    assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("fp8_cache", [False, True])
 def test_cuda_graph_decode_equals_eager(fp8_cache):
     """Greedy decode replayed from a CUDA graph (device-resident position) gives the tokens of the eager loop."""
