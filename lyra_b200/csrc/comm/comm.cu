@@ -259,7 +259,7 @@ __global__ void ep_counts_push_kernel(const int* __restrict__ my_counts, PeerPtr
 // Receive layout is expert-major, then source-rank-major (lyra/kernels/ep_moe.py:9-37), each expert padded to 128 rows.
 __global__ void ep_layout_kernel(const int* __restrict__ counts, int world, int my_rank, int n_experts, int e_local, int cap_rows,
                                  int* __restrict__ send_base, int* __restrict__ recv_offsets, int* __restrict__ tile_group,
-                                 int* __restrict__ recv_total, int* status) {
+                                 int* __restrict__ recv_total, int* __restrict__ valid, int* status) {
   extern __shared__ int sh[];  // per-expert totals [E], padded bases [E]
   int* total = sh;
   int* base = sh + n_experts;
@@ -275,7 +275,10 @@ __global__ void ep_layout_kernel(const int* __restrict__ counts, int world, int 
       for (int j = 0; j < e_local; ++j) {
         const int e = d * e_local + j;
         base[e] = off;
-        if (d == my_rank) recv_offsets[j] = off < cap_rows ? off : cap_rows;
+        if (d == my_rank) {
+          recv_offsets[j] = off < cap_rows ? off : cap_rows;
+          if (valid) valid[j] = min(total[e], max(cap_rows - off, 0));     // real rows of local expert j (its group is padded to 128)
+        }
         off += (total[e] + 127) / 128 * 128;
       }
       // Too small a buffer is reported, never written past: senders drop rows beyond the capacity and every offset that later
@@ -647,10 +650,11 @@ extern "C" int lyra_ep_counts_push(const int* my_counts, const long long* counts
   return 0;
 }
 
+// valid (optional): [e_local] real row counts of this rank's experts
 extern "C" int lyra_ep_layout(const int* counts, int world, int my_rank, int n_experts, int e_local, int cap_rows, int* send_base,
-                              int* recv_offsets, int* tile_group, int* recv_total, int* status, void* stream) {
+                              int* recv_offsets, int* tile_group, int* recv_total, int* valid, int* status, void* stream) {
   ep_layout_kernel<<<1, 256, 2 * n_experts * sizeof(int), ST(stream)>>>(counts, world, my_rank, n_experts, e_local, cap_rows, send_base, recv_offsets,
-                                                                         tile_group, recv_total, status);
+                                                                         tile_group, recv_total, valid, status);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

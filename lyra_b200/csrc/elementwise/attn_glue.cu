@@ -5,6 +5,7 @@
 // Tensors are token-major [B, T, N, D] bf16, D in {64, 128}. Parameter gradients (norm scale, alpha) are written as
 // per-block partial sums that the caller adds up.
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -289,4 +290,58 @@ extern "C" int lyra_gate_xsa_bwd(const void* t, const void* logits, const void* 
   else return -60;
   if (cudaGetLastError() != cudaSuccess) return -3;
   return grid;
+}
+
+// ------------------------------------------------------------------------------------------------ KV cache append (one new position)
+// k, v: the new keys and values of one position, [B, Nkv, D] addressed by (batch, head) element strides; caches [B, Nkv, cap, D],
+// bf16 or e4m3 with one fp32 scale per (batch, head, position) (the (1, D) block of the cache quantisation, lyra/model.py:221-226;
+// same formula as the row quantiser: scale = amax / 448 in IEEE division, values multiplied by the rounded reciprocal). The
+// position is read on the device, so the launch is the same for every token of a CUDA-graph decode loop. One warp per
+// (batch, head, k | v).
+namespace lyra {
+template <bool F8>
+__global__ void kv_append_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long ksb, long long ksh,
+                                 long long vsb, long long vsh, void* __restrict__ kc, void* __restrict__ vc, float* __restrict__ ks, float* __restrict__ vs, int B, int Nkv,
+                                 int cap, int D, const int* __restrict__ pos_dev) {
+  const int w = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (w >= 2 * B * Nkv) return;
+  const int which = w & 1, bh = w >> 1, b = bh / Nkv, h = bh % Nkv;
+  const int pos = *pos_dev;
+  if (pos < 0 || pos >= cap) return;
+  const __nv_bfloat16* src = which ? v + b * vsb + h * vsh : k + b * ksb + h * ksh;
+  const long long row = (static_cast<long long>(bh) * cap + pos);
+  if (!F8) {
+    __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(which ? vc : kc) + row * D;
+    for (int c = lane; c < D; c += 32) dst[c] = src[c];
+  } else {
+    float amax = 0.f;
+    for (int c = lane; c < D; c += 32) amax = fmaxf(amax, fabsf(__bfloat162float(src[c])));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float sc = amax > 0.f ? __fdiv_rn(amax, 448.f) : 1.f;
+    const float inv = __frcp_rn(sc);
+    if (lane == 0) (which ? vs : ks)[row] = sc;
+    uint8_t* dst = reinterpret_cast<uint8_t*>(which ? vc : kc) + row * D;
+    for (int c = lane; c < D; c += 32) {
+      const float x = fminf(fmaxf(__fmul_rn(__bfloat162float(src[c]), inv), -448.f), 448.f);
+      dst[c] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3));
+    }
+  }
+}
+}  // namespace lyra
+
+extern "C" int lyra_kv_append(const void* k, const void* v, long long ksb, long long ksh, long long vsb, long long vsh, void* kc, void* vc, float* ks, float* vs, int B, int Nkv, int cap,
+                              int D, const int* pos_dev, int f8, void* stream) {
+  if (B <= 0 || Nkv <= 0) return 0;
+  const int warps = 2 * B * Nkv, wpb = 8;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (f8)
+    lyra::kv_append_kernel<true><<<(warps + wpb - 1) / wpb, wpb * 32, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(k), reinterpret_cast<const __nv_bfloat16*>(v),
+                                                                               ksb, ksh, vsb, vsh, kc, vc, ks, vs, B, Nkv, cap, D, pos_dev);
+  else
+    lyra::kv_append_kernel<false><<<(warps + wpb - 1) / wpb, wpb * 32, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(k), reinterpret_cast<const __nv_bfloat16*>(v),
+                                                                                ksb, ksh, vsb, vsh, kc, vc, ks, vs, B, Nkv, cap, D, pos_dev);
+  LYRA_CHECK_LAUNCH();
+  return 0;
 }

@@ -284,15 +284,18 @@ __global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ pre, const _
 }
 
 // ------------------------------------------------------------------------------------------------ QK-norm + RoPE (forward)
-// x, y [rows = B*T*N, D]; one warp per row; cos/sin [T, D/2]. Optional RMS norm over D with `scale`.
+// x, y [rows = B*T*N, D]; one warp per row; cos/sin [T, D/2]. Optional RMS norm over D with `scale`. The N heads of a token are
+// contiguous in x and consecutive tokens are `x_token_stride` elements apart (N * D for a tensor of its own, more for a slice
+// of a fused q | k | v projection); y is contiguous.
 __global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ scale, const float* __restrict__ cosv,
-                                       const float* __restrict__ sinv, __nv_bfloat16* __restrict__ y, long long rows, int T, int N, int D, float eps) {
+                                       const float* __restrict__ sinv, __nv_bfloat16* __restrict__ y, long long rows, int T, int N, int D, float eps,
+                                       long long x_token_stride) {
   const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   if (row >= rows) return;
   const int t = int((row / N) % T);
   const int half = D / 2;
-  const __nv_bfloat16* xr = x + row * D;
+  const __nv_bfloat16* xr = x + (row / N) * x_token_stride + (row % N) * D;
   float a[2], b[2];  // elements lane, lane+32 of each half (D <= 128)
   float ss = 0.f;
 #pragma unroll
@@ -497,11 +500,11 @@ extern "C" int lyra_swiglu_bwd_rows(const void* pre, const void* dact, void* dpr
 }
 
 extern "C" int lyra_qknorm_rope_fwd(const void* x, const float* scale, const float* cosv, const float* sinv, void* y, int B, int T, int N, int D,
-                                    float eps, void* stream) {
+                                    float eps, long long x_token_stride, void* stream) {
   const long long rows = (long long)B * T * N;
   if (rows <= 0) return 0;
-  if (D > 128 || D % 2) return -41;
-  qknorm_rope_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S_(stream)>>>(CBFP(x), scale, cosv, sinv, BFP(y), rows, T, N, D, eps);
+  if (D > 128 || D % 2 || x_token_stride < (long long)N * D) return -41;
+  qknorm_rope_fwd_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, S_(stream)>>>(CBFP(x), scale, cosv, sinv, BFP(y), rows, T, N, D, eps, x_token_stride);
   LYRA_CHECK_LAUNCH();
   return 0;
 }

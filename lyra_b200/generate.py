@@ -126,6 +126,11 @@ class BatchedGenerator:
         self.cache = init_cache(mcfg, capacity, device, batch, getattr(rt, "n_kv_local", None))   # tensor parallel: this rank's kv heads only
         self.batch, self.capacity = batch, capacity
         self.use_cuda_graph = use_cuda_graph and self.device.type == "cuda"
+        # The expert exchange alternates between two count buffers from call to call; a graph fixes each call's buffer at capture.
+        # With an odd number of exchanges per token the last call of one replay and the first call of the next would share a
+        # buffer, which the protocol does not allow: such models decode without a graph under expert parallelism.
+        if rt is not None and getattr(rt, "ep_size", 1) > 1 and sum(kind == "moe" for kind in mcfg.mlp_map) % 2 == 1:
+            self.use_cuda_graph = False
         self._graph = None
         self._static_tok = None
         self._static_out = None

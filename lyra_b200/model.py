@@ -90,10 +90,40 @@ class LayerCache:
     v: Any
 
 
+def _kv_append_kernel(cache: LayerCache, k: torch.Tensor, v: torch.Tensor, pos_dev: torch.Tensor) -> bool:
+    """One launch that writes the new position of both caches (and their scales) at the device-resident position; False when
+    the tensors are not what the kernel takes (then the PyTorch path below runs)."""
+    from lyra_b200.ops import native
+
+    quantised = isinstance(cache.k, QArray)
+    kc, vc = (cache.k.qval, cache.v.qval) if quantised else (cache.k, cache.v)
+    B, Nkv, T, D = k.shape
+    if not (k.is_cuda and T == 1 and k.dtype == torch.bfloat16 and v.dtype == torch.bfloat16 and native.kernels_available()
+            and hasattr(native.kernels(), "lyra_kv_append") and kc.is_contiguous() and vc.is_contiguous() and kc.shape[:2] == (B, Nkv) and kc.shape[3] == D
+            and k.stride(3) == 1 and v.stride(3) == 1 and v.shape == k.shape and pos_dev.dtype == torch.int32):
+        return False
+    if quantised:
+        if not (kc.dtype == torch.float8_e4m3fn and tuple(cache.k.block) == (1, D) and cache.k.scale.dtype == torch.float32
+                and cache.k.scale.is_contiguous() and cache.v.scale.is_contiguous()):
+            return False
+        ks, vs = cache.k.scale, cache.v.scale
+    else:
+        if kc.dtype != torch.bfloat16:
+            return False
+        ks = vs = None
+    native.check(native.kernels().lyra_kv_append(native.ptr(k), native.ptr(v), native.c_ll(k.stride(0)), native.c_ll(k.stride(1)), native.c_ll(v.stride(0)), native.c_ll(v.stride(1)), native.ptr(kc), native.ptr(vc),
+                                                 native.ptr(ks), native.ptr(vs), native.c_int(B), native.c_int(Nkv), native.c_int(kc.shape[2]), native.c_int(D),
+                                                 native.ptr(pos_dev), native.c_int(int(quantised)), native.stream_ptr()), "lyra_kv_append")
+    native.count_launch()
+    return True
+
+
 def cache_update(cache: LayerCache, k: torch.Tensor, v: torch.Tensor, start_pos: int, pos_dev: torch.Tensor | None = None) -> LayerCache:
     """Writes ``k, v [B, Nkv, T, D]`` at ``start_pos`` (in place). fp8 caches quantise per (position, head).
     With ``pos_dev`` (int device scalar, T == 1) the position is read on the device, so the call can be replayed."""
     if pos_dev is not None:
+        if _kv_append_kernel(cache, k, v, pos_dev):
+            return cache
         at = pos_dev.reshape(1).long()
         if isinstance(cache.k, QArray):
             for dst, new in ((cache.k, k), (cache.v, v)):
@@ -202,9 +232,19 @@ def attention_apply(x, w: AttentionWeights, idx: int, pos: int, freq_cis, cache:
         if rt is not None and rt.tp_size > 1:
             h = rt.tp_copy(h)                                # q / k / v and the gate are column-sharded: their input gradients are partial
         with scope("qkv_projection"):
-            q = ops.linear(h, _dq(W(w.q), h.dtype), W(w.q_bias), impl).reshape(B, T, -1, c.head_dim)
-            k = ops.linear(h, _dq(W(w.k), h.dtype), W(w.k_bias), impl).reshape(B, T, -1, c.head_dim)
-            v = ops.linear(h, _dq(W(w.v), h.dtype), W(w.v_bias), impl).reshape(B, T, -1, c.head_dim)
+            wq, wk, wv = W(w.q), W(w.k), W(w.v)
+            if (c.mode == Mode.DECODE and T == 1 and not probe.enabled and not torch.is_grad_enabled() and (rt is None or rt.tp_size == 1)
+                    and ops.use_kernels(h, impl) and all(isinstance(t, torch.Tensor) and t.ndim == 2 for t in (wq, wk, wv))):
+                # a decode step: one product with the fused [C, q | k | v] matrix (two launches instead of six)
+                fused, fused_bias = ops._cuda().fused_columns((wq, wk, wv), (W(w.q_bias), W(w.k_bias), W(w.v_bias)))
+                qkv = ops.linear(h, fused, fused_bias, impl)
+                q, k, v = (t.reshape(B, T, -1, c.head_dim) for t in qkv.split([wq.shape[1], wk.shape[1], wv.shape[1]], dim=-1))
+                if w.sdpa_gate is not None or c.use_learned_xsa:
+                    v = v.contiguous()                       # the gate / XSA kernel reads the values as a tensor of their own
+            else:
+                q = ops.linear(h, _dq(wq, h.dtype), W(w.q_bias), impl).reshape(B, T, -1, c.head_dim)
+                k = ops.linear(h, _dq(wk, h.dtype), W(w.k_bias), impl).reshape(B, T, -1, c.head_dim)
+                v = ops.linear(h, _dq(wv, h.dtype), W(w.v_bias), impl).reshape(B, T, -1, c.head_dim)
         if probe.enabled and w.qnorm_scale is not None:
             probe.tensor("q_pre_norm", q)
             probe.tensor("k_pre_norm", k)

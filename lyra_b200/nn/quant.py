@@ -104,11 +104,14 @@ def _quantize_kernel(x: torch.Tensor, dtype, block: tuple[int, ...], scale_dtype
     """CUDA path of ``quantize`` for e4m3 with a 2-D block over the last two axes (weights; KV rows when the block is (1, D))."""
     if dtype != torch.float8_e4m3fn or scale_dtype != torch.float32 or len(block) != 2 or x.ndim < 2:
         return None
-    if x.dtype not in (torch.float32, torch.bfloat16) or not x.is_contiguous() or x.numel() == 0:
+    if x.dtype not in (torch.float32, torch.bfloat16) or x.numel() == 0:
         return None
     lib = _kernel_lib(x)
     if lib is None:
         return None
+    # a strided view (e.g. the value slice of a fused q | k | v projection) is copied rather than sent down the PyTorch path: that
+    # path divides by the scale where the kernels multiply by its rounded reciprocal, and the two round a few values differently
+    x = x.contiguous()
     import ctypes
 
     from lyra_b200.ops import native

@@ -135,9 +135,17 @@ class _QKNormRopeKernel(torch.autograd.Function):
         return dx, dscale, None, None, None
 
 
+def _token_strided(x) -> bool:
+    """``[B, T, N, D]`` whose heads are contiguous inside a token and whose tokens are evenly spaced (a slice of a fused projection)."""
+    B, T, N, D = x.shape
+    return x.stride(3) == 1 and x.stride(2) == D and x.stride(1) >= N * D and (B == 1 or x.stride(0) == T * x.stride(1))
+
+
 def qk_norm_rope(q, k, qscale, kscale, cos, sin, eps):
-    ok = (q.dtype == BF16 and k.dtype == BF16 and _has("lyra_qknorm_rope_bwd") and q.is_contiguous() and k.is_contiguous()
-          and q.shape[-1] in (64, 128) and q.dim() == 4)
+    ok = (q.dtype == BF16 and k.dtype == BF16 and _has("lyra_qknorm_rope_bwd") and q.shape[-1] in (64, 128) and q.dim() == 4)
+    if ok and not (q.is_contiguous() and k.is_contiguous()):
+        if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad) or not (_token_strided(q) and _token_strided(k)):
+            q, k = q.contiguous(), k.contiguous()          # the backward kernel takes contiguous inputs only
     if ok:
         return _QKNormRopeKernel.apply(q, qscale, cos, sin, eps), _QKNormRopeKernel.apply(k, kscale, cos, sin, eps)
     return _QKNormRope.apply(q, qscale, cos, sin, eps), _QKNormRope.apply(k, kscale, cos, sin, eps)
@@ -145,10 +153,10 @@ def qk_norm_rope(q, k, qscale, kscale, cos, sin, eps):
 
 def _qknorm_rope_kernel(x, scale, c2, s2, eps):
     B, T, N, D = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty(B, T, N, D, dtype=x.dtype, device=x.device)
     sc = scale.detach().float().contiguous() if scale is not None else None
     native.check(_lib().lyra_qknorm_rope_fwd(ptr(x), ptr(sc), ptr(c2), ptr(s2), ptr(y), c_int(B), c_int(T), c_int(N), c_int(D), c_float(eps),
-                                             native.stream_ptr()), "qknorm_rope_fwd")
+                                             c_ll(x.stride(1)), native.stream_ptr()), "qknorm_rope_fwd")
     native.count_launch()
     return y
 

@@ -77,10 +77,10 @@ def _ep_moe_decode(rt, xn, scores, indices, w, c: ModelConfig):
     db = w.mlp_down_bias.detach().float().reshape(El, C) if w.mlp_down_bias is not None else None
     ex = _Exchange(rt, indices, C)
     bufs = ex.buf.for_layer(-1)
-    x_recv = ex.dispatch(xn.to(BF16), K, bufs["recv"], bufs["meta"])
     small = F_ * K <= EP_DECODE_MAX_ROWS and dec.decode_gemm_supported(C, n_up, wu) and dec.decode_gemm_supported(H, C, wd)
+    x_recv = ex.dispatch(xn.to(BF16), K, bufs["recv"], bufs["meta"], pad=not small)   # the small-M products read real rows only
     if small:
-        valid = ex.counts_mat.view(ex.W, ex.E)[:, ex.rank * El:(ex.rank + 1) * El].sum(0).to(torch.int32)
+        valid = ex.valid                                         # real rows per local expert, from the layout kernel
         most = ex.W * F_ * K                                     # an expert can receive at most every assignment of every rank
         usual = -(-2 * most // ex.E)                             # twice the balanced load
         act = dec.decode_gemm(x_recv, wu, offsets=ex.offsets, counts=valid, bias=ub, swiglu=True, swiglu_beta=c.swiglu_beta,
@@ -94,7 +94,10 @@ def _ep_moe_decode(rt, xn, scores, indices, w, c: ModelConfig):
                              out=torch.empty(cap, H, dtype=BF16, device=xn.device))
         rows = G.grouped_gemm(act, wd_t, ex.tile_group, bias=db, out=torch.empty(cap, C, dtype=BF16, device=xn.device))
     ret = ex.collect(rows, bufs["meta"], bufs["ret"])
-    return ew.combine_rows(ret, torch.arange(F_ * K, device=xn.device), scores, F_, K)
+    ident = rt._ep_state.setdefault("ident", {})
+    if F_ * K not in ident:
+        ident[F_ * K] = torch.arange(F_ * K, device=xn.device)
+    return ew.combine_rows(ret, ident[F_ * K], scores, F_, K)
 
 
 # ============================================================================================ baseline: collectives
@@ -285,8 +288,11 @@ class _Exchange:
         plan = getattr(rt, "routing_plan", None)                 # counts and permutation already made by the routing kernels of this layer call
         rt.routing_plan = None
         if plan is not None and plan.order.numel() == flat.numel() and plan.counts.numel() <= self.E:
-            counts = torch.zeros(self.E, dtype=torch.int32, device=dev)
-            counts[: plan.counts.numel()] = plan.counts
+            if plan.counts.numel() == self.E:                    # no shared experts behind the routed ones: the plan's counts as they are
+                counts = plan.counts
+            else:
+                counts = torch.zeros(self.E, dtype=torch.int32, device=dev)
+                counts[: plan.counts.numel()] = plan.counts
             self.order, self.rank_in_expert = plan.order, plan.rank_in_expert
         else:
             counts = ref.count_ids(flat, self.E).to(torch.int32)
@@ -313,14 +319,19 @@ class _Exchange:
         with span("ep_wait"):
             native.check(self.lib.lyra_wait_ctr(ctypes.c_void_p(self.flags.buffer.data_ptr() + FLAG_COUNTS), self.W, ctypes.c_void_p(self.ctr.data_ptr()),
                                                 native.ptr(native.status_word()), stream), "wait")
-        self.counts_mat = self.counts_slab.view(0, self.W * self.E, torch.int32).clone()   # private copy: the slab is reused by later calls
+        # A training exchange keeps a private copy for its backward pass (the slab is rewritten by the call after next). An
+        # inference call is over before that: a peer's push of the call after next follows this rank's push of the next call,
+        # which this rank's stream runs after everything of this call.
+        self.counts_mat = self.counts_slab.view(0, self.W * self.E, torch.int32)
+        if torch.is_grad_enabled():
+            self.counts_mat = self.counts_mat.clone()
         nt = self.buf.n_tiles
-        ints = torch.empty(self.E + (self.El + 1) + nt + 1 + (2 * (self.E + 1) + 2 * nt if tiles else 0), dtype=torch.int32, device=dev)
-        parts = [self.E, self.El + 1, nt, 1] + ([self.E + 1, self.E + 1, nt, nt] if tiles else [])
+        ints = torch.empty(self.E + (self.El + 1) + nt + 1 + self.El + (2 * (self.E + 1) + 2 * nt if tiles else 0), dtype=torch.int32, device=dev)
+        parts = [self.E, self.El + 1, nt, 1, self.El] + ([self.E + 1, self.E + 1, nt, nt] if tiles else [])
         views = torch.split(ints, parts)
-        self.send_base, self.offsets, self.tile_group, self.total = views[:4]
+        self.send_base, self.offsets, self.tile_group, self.total, self.valid = views[:5]
         if tiles:
-            self.starts, self.send_starts, self.tile_valid, self.tile_perm = views[4:]
+            self.starts, self.send_starts, self.tile_valid, self.tile_perm = views[5:]
             native.check(self.lib.lyra_ep_layout_tiles(native.ptr(self.counts_mat), self.W, self.rank, self.E, self.El, self.buf.cap,
                                                        native.ptr(self.send_base), native.ptr(self.offsets), native.ptr(self.tile_group),
                                                        native.ptr(self.total), native.ptr(self.starts), native.ptr(self.send_starts),
@@ -328,7 +339,7 @@ class _Exchange:
                                                        stream), "ep_layout_tiles")
         else:
             native.check(self.lib.lyra_ep_layout(native.ptr(self.counts_mat), self.W, self.rank, self.E, self.El, self.buf.cap, native.ptr(self.send_base),
-                                                 native.ptr(self.offsets), native.ptr(self.tile_group), native.ptr(self.total),
+                                                 native.ptr(self.offsets), native.ptr(self.tile_group), native.ptr(self.total), native.ptr(self.valid),
                                                  native.ptr(native.status_word()), stream), "ep_layout")
         native.count_launch(3)
 
@@ -354,15 +365,17 @@ class _Exchange:
         self.wait(flag_offset)
 
     # ---------------------------------------------------------------------------------- barrier-ordered protocol
-    def dispatch(self, src: torch.Tensor, src_div: int, recv_slab, meta_slab) -> torch.Tensor:
+    def dispatch(self, src: torch.Tensor, src_div: int, recv_slab, meta_slab, pad: bool = True) -> torch.Tensor:
+        """``pad=False``: the padding rows of the groups keep whatever they held (for consumers that read real rows only)."""
         nat = self.nat
         nat.check(self.lib.lyra_ep_dispatch(nat.ptr(src), nat.ptr(self.expert_of), nat.ptr(self.rank_in_expert), nat.ptr(self.send_base),
                                             _arr(recv_slab.peer_ptrs), _arr(meta_slab.peer_ptrs) if meta_slab is not None else None, self.W, self.rank,
                                             self.El, self.buf.cap, self.F * self.K, src_div, self.C, nat.stream_ptr()), "ep_dispatch")
         self._phase(FLAG_DISPATCH)
-        recv = self._zero_pad(recv_slab)
         nat.count_launch()
-        return recv
+        if not pad:
+            return recv_slab.view(0, self.buf.cap * self.C, BF16).view(self.buf.cap, self.C)
+        return self._zero_pad(recv_slab)
 
     def _zero_pad(self, recv_slab) -> torch.Tensor:
         nat = self.nat
