@@ -375,13 +375,15 @@ def route_tokens(t, w: MoEWeights, config: ModelConfig, *, probe: Probe = NO_PRO
     W = (lambda p: rt.materialize(p) if rt is not None else p)
     k = c.n_active_routed_experts
     with scope("router"):
-        logits = t.float() @ W(w.router).float()
-        if (ROUTING_TAPE is None and not probe.enabled and ops.use_kernels(t, c.implementation) and (rt is None or rt.tp_size == 1)):
+        kernels = ops.use_kernels(t, c.implementation)
+        f32 = ops._cuda().fp32_param if kernels else (lambda p: p.float())       # cached conversion of a bf16 checkpoint's router
+        logits = t.float() @ f32(W(w.router))
+        if (ROUTING_TAPE is None and not probe.enabled and kernels and (rt is None or rt.tp_size == 1)):
             from lyra_b200.ops import routing
 
             if routing.supported(c.n_routed_experts, k):
                 # one kernel chain: top-k, scores, both auxiliary terms, counts and the expert-sorted permutation
-                scores, idx, aux, plan = routing.route(logits, W(w.router_bias) if w.router_bias is not None else None, k,
+                scores, idx, aux, plan = routing.route(logits, f32(W(w.router_bias)) if w.router_bias is not None else None, k,
                                                        c.load_balance_weight, c.router_z_loss_weight)
                 meter = getattr(rt, "load_meter", None)
                 if meter is not None and (meter.always or torch.is_grad_enabled()):

@@ -75,6 +75,28 @@ def invalidate_shadows() -> None:
         _SHADOW[key] = (-1, shadow, ref)
 
 
+_F32: dict[int, tuple] = {}
+
+
+def fp32_param(p: torch.Tensor | None) -> torch.Tensor | None:
+    """fp32 copy of a parameter that is stored in another dtype (biases and the router of a bf16 checkpoint), cached per parameter
+    object until it changes: an inference step otherwise converts the same few tensors again in every layer call. Parameters that
+    take part in a gradient computation are converted in the graph as before."""
+    if p is None or p.dtype == torch.float32:
+        return p
+    if torch.is_grad_enabled() and p.requires_grad:
+        return p.float()
+    hit = _F32.get(id(p))
+    if hit is not None and hit[2]() is p and hit[0] == p._version:
+        return hit[1]
+    copy = p.detach().float()
+    if len(_F32) > 4096:
+        for k in [k for k, v in _F32.items() if v[2]() is None]:
+            del _F32[k]
+    _F32[id(p)] = (p._version, copy, weakref.ref(p))
+    return copy
+
+
 _FUSED: dict[tuple, tuple] = {}
 
 
@@ -184,7 +206,7 @@ def linear(x, w, bias=None, *, residual=None, alpha: float = 1.0, out_dtype=None
 
         x2 = x.reshape(rows, x.shape[-1]).to(BF16).contiguous()
         res2 = residual.reshape(rows, N).to(BF16).contiguous() if residual is not None else None
-        y = dec.decode_gemm(x2, bf16_weight(w), bias=bias.reshape(1, N) if bias is not None else None, residual=res2,
+        y = dec.decode_gemm(x2, bf16_weight(w), bias=fp32_param(bias).reshape(1, N) if bias is not None else None, residual=res2,
                             alpha=alpha).reshape(*x.shape[:-1], N)
     elif N % 8 or w.shape[0] % 8:
         y = ref_linear(x, w, bias, residual, alpha)

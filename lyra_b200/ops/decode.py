@@ -237,8 +237,8 @@ def decode_moe(xn, scores, indices, w_up, up_bias, w_down, down_bias, beta, limi
             dest = torch.empty_like(order)
             dest[order] = torch.arange(order.numel(), device=order.device)
             x_sorted = xn.to(BF16)[order // K].contiguous()
-        ub = up_bias.reshape(E, N_up) if up_bias is not None else None
-        db = down_bias.reshape(E, C) if down_bias is not None else None
+        ub = cuda_ops.fp32_param(up_bias).reshape(E, N_up) if up_bias is not None else None
+        db = cuda_ops.fp32_param(down_bias).reshape(E, C) if down_bias is not None else None
         usual = -(-2 * F_ * K // E)                            # twice the balanced rows per expert
         act = decode_gemm(x_sorted, wu, offsets=offsets, bias=ub, swiglu=True, swiglu_beta=beta, swiglu_limit=limit, active_groups=min(E, F_ * K),
                           typical_group_rows=usual)

@@ -73,8 +73,8 @@ def _ep_moe_decode(rt, xn, scores, indices, w, c: ModelConfig):
     wd = down if isinstance(down, QArray) else cuda_ops.bf16_weight(down)
     n_up = (wu.qval if isinstance(wu, QArray) else wu).shape[-1]
     H = n_up // 2
-    ub = w.mlp_up_bias.detach().float().reshape(El, n_up) if w.mlp_up_bias is not None else None
-    db = w.mlp_down_bias.detach().float().reshape(El, C) if w.mlp_down_bias is not None else None
+    ub = cuda_ops.fp32_param(w.mlp_up_bias).reshape(El, n_up) if w.mlp_up_bias is not None else None
+    db = cuda_ops.fp32_param(w.mlp_down_bias).reshape(El, C) if w.mlp_down_bias is not None else None
     ex = _Exchange(rt, indices, C)
     bufs = ex.buf.for_layer(-1)
     small = F_ * K <= EP_DECODE_MAX_ROWS and dec.decode_gemm_supported(C, n_up, wu) and dec.decode_gemm_supported(H, C, wd)
