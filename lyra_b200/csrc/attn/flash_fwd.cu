@@ -238,75 +238,56 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constant__
             }
           }
         };
-        // pass 1: the row maximum (the scores are read again below rather than kept: 128 live values per thread do not fit)
+        // One pass in the common case: the probabilities are formed against the current reference maximum while the tile's own
+        // maximum is tracked, and stay in registers (packed) until it is known that no row of the warp has to move its
+        // reference (lazy rescale: only when the new maximum exceeds the reference by more than 2^8). Otherwise the warp reads
+        // the scores again - they are still in TMEM - and redoes the tile with the new references; rows that keep theirs get the
+        // same values again.
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-        {
-          uint32_t ra[32], rb[32];
-          tmem_ld32(s_addr, ra);
-          tmem_ld32(s_addr + 32, rb);
-          tmem_ld_wait();
-          mask(ra, 0);
-          mask(rb, 1);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            mx4[0] = fmaxf(mx4[0], fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
-            mx4[1] = fmaxf(mx4[1], fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
-          }
-          tmem_ld32(s_addr + 64, ra);
-          tmem_ld32(s_addr + 96, rb);
-          tmem_ld_wait();
-          mask(ra, 2);
-          mask(rb, 3);
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            mx4[2] = fmaxf(mx4[2], fmaxf(__uint_as_float(ra[i]), __uint_as_float(ra[i + 1])));
-            mx4[3] = fmaxf(mx4[3], fmaxf(__uint_as_float(rb[i]), __uint_as_float(rb[i + 1])));
-          }
-        }
-        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;    // the scale is positive
-        // lazy rescale: keep the old reference max unless the new one exceeds it by more than 2^8
-        float factor = 1.0f;
-        if (mx > m + 8.0f) {
-          factor = exp2f(m - mx);
-          m = mx;
-        }
-        l *= factor;
-        if (j >= 2 && __any_sync(0xffffffffu, factor != 1.0f)) {   // O_g holds tiles j-2, j-4, ...: all retired (see the issuer)
-#pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t o[32];
-            tmem_ld32(o_addr + c * 32, o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
-            tmem_st32(o_addr + c * 32, o);
-          }
-        }
-        // pass 2: probabilities, as bf16 pairs back into columns 0..63 of the same buffer (column c holds keys 2c and 2c+1;
-        // a column is overwritten only after both scores it replaces were read). The next 64 scores are in flight while 64 are
-        // exponentiated.
         float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t ra[32], rb[32], pk[32];
-          tmem_ld32(s_addr + h * 64, ra);
-          tmem_ld32(s_addr + h * 64 + 32, rb);
+        uint32_t pk[2][32];
+        auto quarter_pass = [&](int c, bool track) {
+          uint32_t r[32];
+          tmem_ld32(s_addr + c * 32, r);
           tmem_ld_wait();
-          mask(ra, 2 * h);
-          mask(rb, 2 * h + 1);
+          mask(r, c);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float p0 = exp2f(fmaf(__uint_as_float(ra[i]), sc, -m));
-            const float p1 = exp2f(fmaf(__uint_as_float(ra[i + 1]), sc, -m));
-            const float p2 = exp2f(fmaf(__uint_as_float(rb[i]), sc, -m));
-            const float p3 = exp2f(fmaf(__uint_as_float(rb[i + 1]), sc, -m));
-            sum4[2 * h] += p0 + p1;
-            sum4[2 * h + 1] += p2 + p3;
-            pk[i >> 1] = pack_bf16(p0, p1);
-            pk[16 + (i >> 1)] = pack_bf16(p2, p3);
+            if (track) mx4[c] = fmaxf(mx4[c], fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])));
+            const float p0 = exp2f(fmaf(__uint_as_float(r[i]), sc, -m));
+            const float p1 = exp2f(fmaf(__uint_as_float(r[i + 1]), sc, -m));
+            sum4[c] += p0 + p1;
+            pk[c >> 1][(c & 1) * 16 + (i >> 1)] = pack_bf16(p0, p1);
           }
-          tmem_st32(s_addr + h * 32, pk);
+        };
+#pragma unroll
+        for (int c = 0; c < 4; ++c) quarter_pass(c, true);
+        const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;    // the scale is positive
+        if (__any_sync(0xffffffffu, mx > m + 8.0f)) {
+          float factor = 1.0f;
+          if (mx > m + 8.0f) {
+            factor = exp2f(m - mx);
+            m = mx;
+          }
+          l *= factor;
+          if (j >= 2) {                                       // O_g holds tiles j-2, j-4, ...: all retired (see the issuer)
+#pragma unroll 1
+            for (int c = 0; c < D / 32; ++c) {
+              uint32_t o[32];
+              tmem_ld32(o_addr + c * 32, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+              tmem_st32(o_addr + c * 32, o);
+            }
+          }
+          sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) quarter_pass(c, false);
         }
+        // bf16 pairs back into columns 0..63 of the same buffer (column c holds keys 2c and 2c+1)
+        tmem_st32(s_addr, pk[0]);
+        tmem_st32(s_addr + 32, pk[1]);
         tmem_st_wait();
         l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         tc_fence_before();
