@@ -69,6 +69,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   constexpr int HALF = 128 * 128;          // one 64-column block of a 128-row tile
   constexpr int KHALF = 64 * 128;          // one 64-column block of a 64-row tile
   constexpr uint32_t TMEM_COLS = 512, S_COL = 0, DP_COL = 128, DQ_COL = 256;   // S of group 0 / 1 at 0 / 64, dP at 128 / 192
+  constexpr uint32_t QA_COL = 384, DOA_COL = 384 + D / 2;                      // Q and dO as packed bf16 TMEM operands (D / 2 columns each)
   constexpr uint32_t IDESC_S = make_idesc(BQ, BKV, 1, 1, 0, 0);
   constexpr uint32_t IDESC_DQ = make_idesc(BQ, D, 1, 1, 0, 1);                 // dS (TMEM) x K (MN-major)
 
@@ -77,7 +78,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   uint8_t* sQ = smem;
   uint8_t* sDO = sQ + TILE;
   uint8_t* sKV = sDO + TILE;          // DQ_STAGES x (K, V)
-  __shared__ uint64_t q_full, kv_full[DQ_STAGES], kv_empty[DQ_STAGES], sdp_full[2], ds_full[2], dq_full;
+  __shared__ uint64_t q_full, a_full, kv_full[DQ_STAGES], kv_empty[DQ_STAGES], sdp_full[2], ds_full[2], dq_full;
   __shared__ uint32_t tmem_holder;
   __shared__ int abort_flag;
 
@@ -103,6 +104,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
       mbar_init(smem_u32(&ds_full[g]), 128);
     }
     mbar_init(smem_u32(&dq_full), 1);
+    mbar_init(smem_u32(&a_full), 256);
     abort_flag = 0;
     fence_mbar_init();
   }
@@ -116,6 +118,10 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   const uint32_t tmem = tmem_holder;
   volatile int* abortp = &abort_flag;
 
+  // Q and dO are the fixed operands of every S = Q K^T and dP = dO V^T of this CTA. They are copied once from their shared-memory
+  // tiles into TMEM (group 0 copies Q, group 1 dO) and the products take them from there: an SS product of a 128-row tile with a
+  // 64-column B needs 6 KB of shared-memory operands per instruction (48 clk at 128 B/clk against 32 clk of math); with A in
+  // TMEM it needs 2 KB.
   // Key tile j (64 keys) belongs to elementwise group j & 1; each group has its own S / dP buffers and turns dP in place into the
   // bf16 dS operand of dQ += dS K, so the groups never wait for each other and the tensor core always has the other group's work.
   if (warp == 0) {
@@ -144,7 +150,6 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
   } else if (warp == 1) {
     if (lane == 0 && n_tiles > 0) {
       // MMAs of one thread retire in issue order: dP_g(j + 2) is issued after dQ += dS_g(j) K_j, so it cannot overwrite dS_g(j) early
-      const uint64_t dq0 = make_smem_desc(smem_u32(sQ), 16, 1024), ddo0 = make_smem_desc(smem_u32(sDO), 16, 1024);
       const uint64_t dk0 = make_smem_desc(smem_u32(sKV), 16, 1024);          // K of stage 0 as the K-major operand of S
       const uint64_t dkmn0 = make_smem_desc(smem_u32(sKV), KHALF, 1024);     // the same tile as the MN-major operand of dQ += dS K
       auto issue_s = [&](int j) -> bool {
@@ -153,15 +158,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
         tc_fence_after();
         const uint64_t dk = desc_advance(dk0, (2 * s) * KTILE), dv = desc_advance(dk0, (2 * s + 1) * KTILE);
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k)
-          tc_mma_ss(tmem + S_COL + g * BKV, desc_advance(dq0, (k / 4) * HALF + (k % 4) * 32), desc_advance(dk, (k / 4) * KHALF + (k % 4) * 32), IDESC_S, k > 0);
+        for (int k = 0; k < D / 16; ++k)       // 16 values of d = 8 TMEM columns of the resident operand
+          tc_mma_ts(tmem + S_COL + g * BKV, tmem + QA_COL + k * 8, desc_advance(dk, (k / 4) * KHALF + (k % 4) * 32), IDESC_S, k > 0);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          tc_mma_ss(tmem + DP_COL + g * BKV, desc_advance(ddo0, (k / 4) * HALF + (k % 4) * 32), desc_advance(dv, (k / 4) * KHALF + (k % 4) * 32), IDESC_S, k > 0);
+          tc_mma_ts(tmem + DP_COL + g * BKV, tmem + DOA_COL + k * 8, desc_advance(dv, (k / 4) * KHALF + (k % 4) * 32), IDESC_S, k > 0);
         tc_commit(smem_u32(&sdp_full[g]));
         return true;
       };
-      bool ok = mbar_wait(smem_u32(&q_full), 0, abortp);
+      bool ok = mbar_wait(smem_u32(&a_full), 0, abortp);
       if (ok) ok = issue_s(0);
       if (ok && n_tiles > 1) ok = issue_s(1);
       for (int j = 0; j < n_tiles && ok; ++j) {
@@ -195,7 +200,28 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tq, const __grid_constan
     const int hi = min(qpos, p.S - 1);
     const int lo = p.window > 0 ? qpos - p.window + 1 : 0;
     bool failed = false;
-    for (int j = g; j < n_tiles; j += 2) {
+    if (n_tiles > 0) {
+      // this thread's row of Q (group 0) or dO (group 1): 128-byte-swizzled shared memory -> packed bf16 pairs in TMEM
+      if (!mbar_wait(smem_u32(&q_full), 0, abortp)) failed = true;
+      if (!failed) {
+        const uint8_t* tile = g == 0 ? sQ : sDO;
+        const uint32_t a_addr = tmem + lane_addr + (g == 0 ? QA_COL : DOA_COL);
+#pragma unroll
+        for (int h = 0; h < D / 64; ++h) {
+          uint32_t v[32];
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            const uint4 x = *reinterpret_cast<const uint4*>(tile + h * HALF + swz128(row, ch));
+            v[ch * 4 + 0] = x.x; v[ch * 4 + 1] = x.y; v[ch * 4 + 2] = x.z; v[ch * 4 + 3] = x.w;
+          }
+          tmem_st32(a_addr + h * 32, v);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      mbar_arrive(smem_u32(&a_full));
+    }
+    for (int j = g; j < n_tiles && !failed; j += 2) {
       const int k0 = (jt_begin + j) * BKV;
       if (!mbar_wait(smem_u32(&sdp_full[g]), (j >> 1) & 1, abortp)) { failed = true; break; }
       tc_fence_after();
