@@ -280,3 +280,60 @@ def test_gs_locations_are_mirrored_through_the_sync_tool(tmp_path, monkeypatch):
     assert (bucket / "runs" / "a" / "step_00000004" / "_CHECKPOINT_METADATA").is_file()   # pushed back
     assert C.sync_remote(tmp_path / "elsewhere") is False
     assert C.checkpoint_path("~/x") == C.checkpoint_path(str(C.Path.home() / "x"))
+
+
+def test_a_single_step_run_uses_the_peak_learning_rates():
+    from dataclasses import replace as _replace
+
+    from lyra_b200.training.presets import TRAINING_PRESETS
+
+    tcfg = _replace(TRAINING_PRESETS["train-dev"], steps=1)
+    adam_lr, muon_lr, scale = wsd_lr(0, tcfg)
+    assert abs(float(scale) - 1.0) < 1e-6
+    assert abs(float(adam_lr) - tcfg.adam_max_lr) < 1e-9 and abs(float(muon_lr) - tcfg.muon_max_lr) < 1e-9
+
+
+def test_validation_replays_the_same_batches_and_the_last_one_follows_the_final_checkpoint(tmp_path, monkeypatch):
+    """Evaluation runs before the first step, on its cadence and after the last step's checkpoint; every evaluation reads the
+    same first batches of the evaluation file in order, whatever the training loader's shuffling does."""
+    import json
+
+    from lyra_b200.training import train as train_module
+
+    c = small_config(seq_len=4, n_layers=1, mlp_map=("dense",), vocab_size=32, padded_vocab_size=32)
+    eval_tokens = np.arange(31, -2, -1, dtype=np.int32) % c.vocab_size
+    np.save(tmp_path / "train.npy", np.arange(17, dtype=np.int32))
+    np.save(tmp_path / "eval.npy", eval_tokens)
+    tcfg = TrainingConfig(steps=3, batch_size=1, accumulation_steps=1, data_path=tmp_path / "train.npy",
+                          data_loader=DataLoaderConfig(worker_count=0, shuffle=True), eval_data_path=tmp_path / "eval.npy", eval_every=2,
+                          eval_batches=2, checkpoint_every=100, checkpoint_path=tmp_path / "run")
+    final = tcfg.checkpoint_path / "step_00000003"
+    seen_runs, final_ready = [], []
+    real = train_module.run_validation
+
+    def watching(stepper, batches, *, eval_batches, microbatches):
+        final_ready.append(final.is_dir())
+        seen = []
+
+        def tap():
+            for x, y in batches:
+                seen.append((np.asarray(x).ravel().copy(), np.asarray(y).ravel().copy()))
+                yield x, y
+
+        out = real(stepper, tap(), eval_batches=eval_batches, microbatches=microbatches)
+        seen_runs.append(seen)
+        return out
+
+    monkeypatch.setattr(train_module, "run_validation", watching)
+    monkeypatch.setattr(train_module, "plot_run", lambda _: None)
+    state = train_module.train(ModelWeights.init(0, c), c, tcfg)
+    assert int(state.optimizer.adam_count) == tcfg.steps
+    assert final_ready == [False, False, True]
+    for seen in seen_runs:
+        assert len(seen) == tcfg.eval_batches
+        for i, (xs, ys) in enumerate(seen):
+            start = i * c.seq_len
+            np.testing.assert_array_equal(xs, eval_tokens[start:start + c.seq_len])
+            np.testing.assert_array_equal(ys, eval_tokens[start + 1:start + c.seq_len + 1])
+    rows = [json.loads(line) for line in (tcfg.checkpoint_path / "metrics.jsonl").read_text().splitlines()]
+    assert [r["step"] for r in rows if r["kind"] == "eval"] == [0, 2, 3]
