@@ -7,9 +7,10 @@ Each rank runs, per MoE layer call, the stream-ordered sequence of parallel/ep.p
     return rows to peers     -> signal flag192  -> wait flag192 -> combine reads the return buffer
 
 Ranks advance in a random interleaving (any rank that is not blocked may take its next step). The model checks what the
-design relies on when ONE set of buffers serves every layer (inference) and the counts slab is not double-buffered:
-no deadlock, and no rank ever overwrites a peer's counts / receive / return buffer while that peer has not yet consumed the
-previous exchange's contents."""
+design relies on when ONE set of buffers serves every layer (inference): no deadlock, and no rank ever overwrites a peer's
+counts / receive / return buffer while that peer has not yet consumed the previous exchange's contents. The counts live in
+two slabs used by call parity, and an inference call reads its slab in place until its return kernel (no private copy), so
+the slab of call n must survive until call n's last step while call n + 1 already uses the other one."""
 
 import random
 
@@ -17,6 +18,7 @@ import pytest
 
 STEPS = ["push_counts", "wait64", "read_counts", "dispatch", "signal128", "wait128", "gemm_reads_recv",
          "return", "signal192", "wait192", "combine_reads_ret"]
+COUNT_SLABS = 2
 
 
 class Rank:
@@ -26,7 +28,7 @@ class Rank:
         self.flags = {o: [0] * world for o in (64, 128, 192)}   # written by peers
         self.pc, self.call = 0, 0
         # generation (call index) of the data currently held in each buffer, per writer
-        self.counts_gen = [-1] * world
+        self.counts_gen = [[-1] * world for _ in range(COUNT_SLABS)]   # per slab (call parity), per writer
         self.recv_gen = [-1] * world
         self.ret_gen = [-1] * world
         self.consumed = {"counts": -1, "recv": -1, "ret": -1}   # last call whose contents this rank has finished reading
@@ -50,12 +52,12 @@ def run(world, calls, seed):
         elif step == "push_counts":
             rk.ctr[64] += 1
             for p in ranks:
-                assert p.consumed["counts"] >= n - 1, f"rank {rk.r} overwrites counts of rank {p.r} before call {n - 1} was read"
-                p.counts_gen[rk.r] = n
+                # the slab being written last held call n - COUNT_SLABS, whose owner reads it until its return kernel
+                assert p.consumed["counts"] >= n - COUNT_SLABS, f"rank {rk.r} overwrites counts of rank {p.r} still read by call {n - COUNT_SLABS}"
+                p.counts_gen[n % COUNT_SLABS][rk.r] = n
                 p.flags[64][rk.r] = rk.ctr[64]
         elif step == "read_counts":
-            assert rk.counts_gen == [n] * world
-            rk.consumed["counts"] = n
+            assert rk.counts_gen[n % COUNT_SLABS] == [n] * world
         elif step == "dispatch":
             for p in ranks:
                 assert p.consumed["recv"] >= n - 1, f"rank {rk.r} overwrites receive buffer of rank {p.r} still in use by call {n - 1}"
@@ -69,6 +71,8 @@ def run(world, calls, seed):
             assert rk.recv_gen == [n] * world
             rk.consumed["recv"] = n
         elif step == "return":
+            assert rk.counts_gen[n % COUNT_SLABS] == [n] * world     # the return kernel reads the counts in place: still this call's
+            rk.consumed["counts"] = n
             for p in ranks:
                 assert p.consumed["ret"] >= n - 1, f"rank {rk.r} overwrites return buffer of rank {p.r} still in use by call {n - 1}"
                 p.ret_gen[rk.r] = n
@@ -101,6 +105,18 @@ def test_model_detects_a_missing_barrier():
                 run(4, calls=6, seed=seed)
     finally:
         STEPS = saved
+
+
+def test_in_place_counts_reads_are_ordered_by_the_return_phase_even_with_one_slab():
+    """The margin of the inference path: a call reads its counts slab in place until its return kernel, and every peer's next
+    push waits (through the return phase) for that kernel, so even a single slab would never be overwritten while read."""
+    global COUNT_SLABS
+    try:
+        COUNT_SLABS = 1
+        for seed in range(60):
+            run(4, calls=6, seed=seed)
+    finally:
+        COUNT_SLABS = 2
 
 
 # ======================================================================================================================
