@@ -234,7 +234,8 @@ def attention_apply(x, w: AttentionWeights, idx: int, pos: int, freq_cis, cache:
         with scope("qkv_projection"):
             wq, wk, wv = W(w.q), W(w.k), W(w.v)
             if (c.mode == Mode.DECODE and T == 1 and not probe.enabled and not torch.is_grad_enabled() and (rt is None or rt.tp_size == 1)
-                    and ops.use_kernels(h, impl) and all(isinstance(t, torch.Tensor) and t.ndim == 2 for t in (wq, wk, wv))):
+                    and ops.use_kernels(h, impl) and all(isinstance(t, torch.Tensor) and t.ndim == 2 for t in (wq, wk, wv))
+                    and not ops._cuda().pull_pending(wq, wk, wv)):
                 # a decode step: one product with the fused [C, q | k | v] matrix (two launches instead of six)
                 fused, fused_bias = ops._cuda().fused_columns((wq, wk, wv), (W(w.q_bias), W(w.k_bias), W(w.v_bias)))
                 qkv = ops.linear(h, fused, fused_bias, impl)

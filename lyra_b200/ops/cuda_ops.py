@@ -69,8 +69,19 @@ def shadow_of(w: torch.Tensor) -> torch.Tensor | None:
     return hit[1] if hit is not None and hit[2]() is w else None
 
 
+_WEIGHTS_EPOCH = 0
+
+
+def weights_changed() -> None:
+    """Tells the derived-weight caches below (fused projections, fp32 copies) that parameters were rewritten behind PyTorch's
+    version counters: the optimizer kernels update masters and bf16 copies through raw pointers."""
+    global _WEIGHTS_EPOCH
+    _WEIGHTS_EPOCH += 1
+
+
 def invalidate_shadows() -> None:
     """Marks every cached bf16 copy stale (call after the masters changed through an alias, e.g. the optimizer)."""
+    weights_changed()
     for key, (_, shadow, ref) in list(_SHADOW.items()):
         _SHADOW[key] = (-1, shadow, ref)
 
@@ -87,17 +98,23 @@ def fp32_param(p: torch.Tensor | None) -> torch.Tensor | None:
     if torch.is_grad_enabled() and p.requires_grad:
         return p.float()
     hit = _F32.get(id(p))
-    if hit is not None and hit[2]() is p and hit[0] == p._version:
+    if hit is not None and hit[2]() is p and hit[0] == (p._version, _WEIGHTS_EPOCH):
         return hit[1]
     copy = p.detach().float()
     if len(_F32) > 4096:
         for k in [k for k, v in _F32.items() if v[2]() is None]:
             del _F32[k]
-    _F32[id(p)] = (p._version, copy, weakref.ref(p))
+    _F32[id(p)] = ((p._version, _WEIGHTS_EPOCH), copy, weakref.ref(p))
     return copy
 
 
 _FUSED: dict[tuple, tuple] = {}
+
+
+def pull_pending(*ws) -> bool:
+    """True when the sharding runtime still has to pull one of these weights from its owner (the pull rides inside the first
+    forward GEMM that is given the weight itself; a derived copy made before that would hold last step's values)."""
+    return AG_HOOK is not None and any(w is not None and AG_HOOK(w) is not None for w in ws)
 
 
 def fused_columns(ws, biases):
@@ -105,7 +122,7 @@ def fused_columns(ws, biases):
     until one of them changes: a decode step multiplies the same few rows with q, k and v, and one product of the fused
     matrix is two launches instead of six. Inference only (the copies do not follow the masters' gradients)."""
     key = tuple(id(w) for w in ws)
-    versions = tuple(w._version for w in ws) + tuple(-1 if b is None else b._version for b in biases)
+    versions = tuple(w._version for w in ws) + tuple(-1 if b is None else b._version for b in biases) + (_WEIGHTS_EPOCH,)
     hit = _FUSED.get(key)
     if hit is not None and hit[0] == versions and all(r() is w for r, w in zip(hit[3], ws)):
         return hit[1], hit[2]

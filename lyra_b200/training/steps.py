@@ -121,6 +121,7 @@ class Stepper:
 
                 shadows = {p: sh for p, t in trainable.items() if (sh := cuda_ops.shadow_of(t)) is not None}
                 metrics = optimizer_step_cuda(trainable, grads, self.state.optimizer, step, self.tcfg, shadows, rt=self.rt)
+                cuda_ops.weights_changed()               # masters and bf16 copies were rewritten through raw pointers
             else:
                 metrics = optimizer_step({p: t.detach() for p, t in trainable.items()}, grads, self.state.optimizer, step, self.tcfg, rt=self.rt)
                 if self.device.type == "cuda":

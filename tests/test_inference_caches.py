@@ -73,3 +73,22 @@ def test_heartbeat_done_lets_slower_ranks_finish(tmp_path):
         raise AssertionError("a rank that left must be reported")
     except PeerLost as e:
         assert e.rank == 0
+
+
+def test_caches_notice_updates_made_behind_the_version_counters():
+    """The optimizer kernels rewrite parameters through raw pointers (no version bump): ``weights_changed`` retires what was
+    derived from the old values."""
+    from lyra_b200.ops import cuda_ops
+
+    q, k, v = (torch.randn(4, n).bfloat16() for n in (8, 4, 4))
+    b = torch.randn(8).bfloat16()
+    with torch.no_grad():
+        w0, _ = cuda_ops.fused_columns((q, k, v), (None, None, None))
+        f0 = cuda_ops.fp32_param(b)
+        q.data.view(torch.int16).add_(1)          # a write that PyTorch does not see as one, like a kernel's
+        b.data.view(torch.int16).add_(1)
+        cuda_ops.weights_changed()
+        w1, _ = cuda_ops.fused_columns((q, k, v), (None, None, None))
+        f1 = cuda_ops.fp32_param(b)
+    assert w1 is not w0 and torch.equal(w1, torch.cat([q, k, v], 1))
+    assert f1 is not f0 and torch.equal(f1, b.float())
