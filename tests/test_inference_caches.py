@@ -92,3 +92,12 @@ def test_caches_notice_updates_made_behind_the_version_counters():
         f1 = cuda_ops.fp32_param(b)
     assert w1 is not w0 and torch.equal(w1, torch.cat([q, k, v], 1))
     assert f1 is not f0 and torch.equal(f1, b.float())
+
+
+def test_pending_pulls_keep_derived_copies_from_being_made(monkeypatch):
+    from lyra_b200.ops import cuda_ops
+
+    a, b = torch.ones(2), torch.ones(3)
+    assert not cuda_ops.pull_pending(a, b, None)                       # no sharding runtime: nothing is ever pending
+    monkeypatch.setattr(cuda_ops, "AG_HOOK", lambda w: {"src": 0} if w is b else None)
+    assert not cuda_ops.pull_pending(a) and cuda_ops.pull_pending(a, b)
