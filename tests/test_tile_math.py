@@ -2,6 +2,7 @@
 upper-triangle tile enumeration of symmetric products, the mirror condition of their epilogue, the grouped raster, and the
 piece order of the all-gather fused GEMM."""
 
+import numpy as np
 import pytest
 
 BM, BN = 128, 256
@@ -184,3 +185,99 @@ def test_exchange_layout_senders_and_receivers_agree(world, e_local, seed):
             rows = sorted(r for r, (s, jj) in landed[d].items() if jj == j)
             assert [landed[d][r][0] for r in rows] == sorted(landed[d][r][0] for r in rows)
             assert rows == list(range(lay["offsets"][j], lay["offsets"][j] + len(rows)))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Persistent flash-attention forward (csrc/attn/flash_fwd.cu): the work items of a launch and how the CTAs share them.
+def fwd_item(idx, n_qt, Nq, B, T, S, window, q_start):
+    """Restates ``item_at``: (q0, head, b, first key tile, key tiles) of item ``idx``; late query tiles come first."""
+    per_qt = Nq * B
+    q0 = (n_qt - 1 - idx // per_qt) * 128
+    rest = idx % per_qt
+    qlo = q_start + q0
+    qhi = min(q_start + min(q0 + 128, T) - 1, S - 1)
+    klo = max(0, qlo - window + 1) if window > 0 else 0
+    jt_begin = klo // 128
+    jt_end = jt_begin if qhi < 0 else qhi // 128 + 1
+    return q0, rest % Nq, rest // Nq, jt_begin, max(jt_end - jt_begin, 0)
+
+
+def fwd_schedule(grid, n_items):
+    """Items of every CTA in the order it takes them (serpentine over the rounds)."""
+    out = [[] for _ in range(grid)]
+    for cta in range(grid):
+        r = 0
+        while True:
+            idx = r * grid + (grid - 1 - cta if r & 1 else cta)
+            if idx >= n_items:
+                break
+            out[cta].append(idx)
+            r += 1
+    return out
+
+
+@pytest.mark.parametrize("T,S,window,q_start,Nq,B,grid", [(4096, 4096, 0, 0, 32, 2, 148), (4096, 4096, 128, 0, 16, 4, 148), (1000, 1000, 0, 0, 4, 2, 148),
+                                                       (128, 512, 128, 384, 4, 1, 4), (300, 300, 0, 0, 3, 1, 7), (4096, 4096, 0, 0, 32, 2, 1)])
+def test_forward_items_are_visited_once_and_the_serpentine_balances_them(T, S, window, q_start, Nq, B, grid):
+    n_qt = (T + 127) // 128
+    n_items = n_qt * Nq * B
+    grid = min(grid, n_items)
+    sched = fwd_schedule(grid, n_items)
+    seen = sorted(i for items in sched for i in items)
+    assert seen == list(range(n_items))                                  # every item exactly once
+    cover = set()
+    for idx in range(n_items):
+        q0, head, b, jt_begin, n_tiles = fwd_item(idx, n_qt, Nq, B, T, S, window, q_start)
+        cover.add((q0, head, b))
+        # the tiles are exactly those that intersect the band of the tile's queries
+        qs = range(q_start + q0, q_start + min(q0 + 128, T))
+        want = {k // 128 for q in qs for k in range(max(0, q - window + 1) if window else 0, min(q, S - 1) + 1)}
+        assert set(range(jt_begin, jt_begin + n_tiles)) == want
+    assert len(cover) == n_items
+    work = [sum(fwd_item(i, n_qt, Nq, B, T, S, window, q_start)[4] for i in items) for items in sched]
+    if grid == 148 and window == 0 and T == 4096:                         # the benchmark shape: CTAs finish within a few tiles of each other
+        assert max(work) - min(work) <= 0.06 * max(work), (min(work), max(work))
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# e4m3 decode GEMM (csrc/gemm/decode_gemm.cu): the (group, block of token rows) units every CTA lists for itself.
+def f8_units(offsets, counts, G, ntok, max_units=1024):
+    """Restates the warp scan: lane l owns ``per`` consecutive groups; units are numbered by an exclusive scan over the lanes."""
+    per = (G + 31) // 32
+    mine = []
+    for lane in range(32):
+        n = 0
+        for g in range(lane * per, min(G, (lane + 1) * per)):
+            beg = offsets[g]
+            end = beg + counts[g] if counts is not None else offsets[g + 1]
+            n += (max(end - beg, 0) + ntok - 1) // ntok
+        mine.append(n)
+    units = {}
+    for lane in range(32):
+        at = sum(mine[:lane])
+        for g in range(lane * per, min(G, (lane + 1) * per)):
+            beg = offsets[g]
+            end = beg + counts[g] if counts is not None else offsets[g + 1]
+            r0 = beg
+            while r0 < end and at < max_units:
+                units[at] = (g, r0, min(ntok, end - r0))
+                r0 += ntok
+                at += 1
+    return [units[i] for i in range(min(sum(mine), max_units))]
+
+
+@pytest.mark.parametrize("G,ntok,seed", [(128, 16, 0), (32, 16, 1), (33, 32, 2), (1, 64, 3), (200, 16, 4), (64, 64, 5)])
+def test_decode_gemm_units_cover_every_row_once_and_passes_are_balanced(G, ntok, seed):
+    rng = np.random.default_rng(seed)
+    real = np.where(rng.random(G) < 0.25, rng.integers(1, 3 * ntok, G), 0)            # most groups empty, some longer than a block
+    padded = (real + 127) // 128 * 128 if seed % 2 else real                            # receive buffers pad every group to 128 rows
+    offsets = np.concatenate([[0], np.cumsum(padded)]).astype(int)
+    units = f8_units(offsets, real if seed % 2 else None, G, ntok)
+    rows = [r for g, r0, cnt in units for r in range(r0, r0 + cnt)]
+    want = [r for g in range(G) for r in range(offsets[g], offsets[g] + real[g])]
+    assert rows == want                                                                # every real row once, in order; no empty unit
+    assert all(1 <= cnt <= ntok for _, _, cnt in units)
+    n_panels, splits, grid = 45, 1, 296
+    n_passes = n_panels * len(units) * splits
+    per_cta = [len(range(c, n_passes, grid)) for c in range(min(grid, max(n_passes, 1)))]
+    assert max(per_cta) - min(per_cta) <= 1                                            # equal-cost passes dealt round-robin
