@@ -207,3 +207,116 @@ def test_the_model_sees_a_missing_output_wait():
         for seed in range(300):
             rng = random.Random(seed)
             Broken([rng.choice([1, 2, 3]) for _ in range(5)], rng).run()
+
+
+# ======================================================================================================================
+# dK/dV kernel (csrc/attn/flash_bwd.cu): four-stage (Q, dO) ring, two elementwise groups on alternate iterations, each with its
+# own S^T / dP^T buffers that it turns in place into the operands of the accumulating products; statistics double-buffered.
+class DkvKernel:
+    STAGES = 4
+
+    def __init__(self, n_iter, rng, stages=4):
+        self.n, self.rng, self.STAGES = n_iter, rng, stages
+        one = lambda: Bar(1)
+        self.kv_full, self.acc_full = one(), one()
+        self.qd_full, self.qd_empty = [one() for _ in range(stages)], [one() for _ in range(stages)]
+        self.st_full, self.pt_full = [one(), one()], [one(), one()]
+        self.stage = [None] * stages            # iteration whose (Q, dO) the stage holds
+        self.stage_reads = [0] * stages         # issued products that still have to read the stage
+        self.st = [None, None]                  # per group: ("S", it) or ("P", it)
+        self.p_consumed = [True, True]
+        self.acc = set()
+        self.pipe = []
+
+    def tma(self):
+        self.kv_full.arrive()
+        for it in range(self.n):
+            s, ph = it % self.STAGES, (it // self.STAGES) & 1
+            yield lambda s=s, ph=ph: self.qd_empty[s].done(ph ^ 1)
+            assert self.stage_reads[s] == 0, "(Q, dO) stage overwritten while a product still has to read it"
+            self.stage[s] = it
+            self.qd_full[s].arrive()
+
+    def mma(self):
+        def issue_st(it):
+            s, g = it % self.STAGES, it & 1
+            yield lambda: self.qd_full[s].done((it // self.STAGES) & 1)
+            self.stage_reads[s] += 1
+
+            def run():
+                assert self.stage[s] == it, (self.stage[s], it)
+                assert self.st[g] is None or self.p_consumed[g], "S^T written over operands that were not multiplied yet"
+                self.st[g] = ("S", it)
+                self.stage_reads[s] -= 1
+            self.pipe.append(run)
+            self.pipe.append(self.st_full[g].arrive)
+
+        if self.n == 0:
+            return
+        yield lambda: self.kv_full.done(0)
+        yield from issue_st(0)
+        if self.n > 1:
+            yield from issue_st(1)
+        for it in range(self.n):
+            s, g = it % self.STAGES, it & 1
+            yield lambda g=g, it=it: self.pt_full[g].done((it >> 1) & 1)
+            self.stage_reads[s] += 1
+
+            def run(it=it, s=s, g=g):
+                assert self.st[g] == ("P", it) and self.stage[s] == it, (self.st[g], self.stage[s], it)
+                self.acc.add(it)
+                self.p_consumed[g] = True
+                self.stage_reads[s] -= 1
+            self.pipe.append(run)
+            self.pipe.append(self.qd_empty[s].arrive)
+            if it + 2 < self.n:
+                yield from issue_st(it + 2)
+        self.pipe.append(self.acc_full.arrive)
+
+    def group(self, g):
+        for it in range(g, self.n, 2):
+            yield lambda it=it: self.st_full[g].done((it >> 1) & 1)
+            assert self.st[g] == ("S", it), (self.st[g], it)
+            yield None
+            self.st[g], self.p_consumed[g] = ("P", it), False
+            self.pt_full[g].arrive()
+        if self.n:
+            yield lambda: self.acc_full.done(0)
+            assert self.acc == set(range(self.n))
+
+    def run(self):
+        agents = {"tma": self.tma(), "mma": self.mma(), "g0": self.group(0), "g1": self.group(1)}
+        waiting, live, idle = {}, set(agents), 0
+        while live or self.pipe:
+            who = self.rng.choice(list(live) + (["pipe"] if self.pipe else []))
+            if who == "pipe":
+                self.pipe.pop(0)()
+                idle = 0
+                continue
+            cond = waiting.get(who)
+            if cond is not None and not cond():
+                idle += 1
+                assert idle < 20000, f"deadlock: {sorted(live)}"
+                continue
+            waiting.pop(who, None)
+            idle = 0
+            try:
+                nxt = next(agents[who])
+                if nxt is not None:
+                    waiting[who] = nxt
+            except StopIteration:
+                live.discard(who)
+
+
+@pytest.mark.parametrize("seed", range(40))
+def test_dkv_kernel_protocol_has_no_deadlock_and_no_early_reuse(seed):
+    rng = random.Random(seed)
+    DkvKernel(rng.choice([0, 1, 2, 3, 4, 5, 8, 9, 17, 32]), rng).run()
+
+
+def test_dkv_ring_needs_more_than_two_stages_to_run_ahead():
+    """With two stages the load of iteration it + 2 can only start when the products of iteration it have retired - it still
+    works (the ring protocol is the same), it just cannot run ahead; the model accepts any ring length of two or more."""
+    for stages in (2, 3, 4, 6):
+        for seed in range(10):
+            DkvKernel(9, random.Random(seed), stages=stages).run()
