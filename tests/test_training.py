@@ -295,45 +295,42 @@ def test_a_single_step_run_uses_the_peak_learning_rates():
 
 def test_validation_replays_the_same_batches_and_the_last_one_follows_the_final_checkpoint(tmp_path, monkeypatch):
     """Evaluation runs before the first step, on its cadence and after the last step's checkpoint; every evaluation reads the
-    same first batches of the evaluation file in order, whatever the training loader's shuffling does."""
-    import json
-
+    same leading batches of the evaluation file, in file order, whatever the (shuffled) training loader does."""
     from lyra_b200.training import train as train_module
 
-    c = small_config(seq_len=4, n_layers=1, mlp_map=("dense",), vocab_size=32, padded_vocab_size=32)
-    eval_tokens = np.arange(31, -2, -1, dtype=np.int32) % c.vocab_size
-    np.save(tmp_path / "train.npy", np.arange(17, dtype=np.int32))
-    np.save(tmp_path / "eval.npy", eval_tokens)
-    tcfg = TrainingConfig(steps=3, batch_size=1, accumulation_steps=1, data_path=tmp_path / "train.npy",
-                          data_loader=DataLoaderConfig(worker_count=0, shuffle=True), eval_data_path=tmp_path / "eval.npy", eval_every=2,
-                          eval_batches=2, checkpoint_every=100, checkpoint_path=tmp_path / "run")
-    final = tcfg.checkpoint_path / "step_00000003"
-    seen_runs, final_ready = [], []
-    real = train_module.run_validation
+    c = small_config(seq_len=8, n_layers=1, mlp_map=("dense",), vocab_size=64, padded_vocab_size=64)
+    T, n_eval = c.seq_len, 3
+    held_out = ((np.arange(6 * T + 1) * 7 + 3) % c.vocab_size).astype(np.int32)      # a recognisable pattern, no two windows alike
+    np.save(tmp_path / "held_out.npy", held_out)
+    tcfg = TrainingConfig(steps=5, batch_size=1, accumulation_steps=1, data_path=token_file(tmp_path / "tok.npy", n=40 * T, vocab=c.vocab_size),
+                          data_loader=DataLoaderConfig(worker_count=0, shuffle=True), eval_data_path=tmp_path / "held_out.npy", eval_every=3,
+                          eval_batches=n_eval, checkpoint_every=1000, checkpoint_path=tmp_path / "out")
+    last_checkpoint = tcfg.checkpoint_path / f"step_{tcfg.steps:08d}"
+    windows_per_eval, checkpoint_seen = [], []
+    original = train_module.run_validation
 
-    def watching(stepper, batches, *, eval_batches, microbatches):
-        final_ready.append(final.is_dir())
-        seen = []
+    def spy(stepper, batches, **kw):
+        checkpoint_seen.append(last_checkpoint.is_dir())
+        taken = []
 
-        def tap():
+        def recording():
             for x, y in batches:
-                seen.append((np.asarray(x).ravel().copy(), np.asarray(y).ravel().copy()))
+                taken.append((np.array(x).reshape(-1), np.array(y).reshape(-1)))
                 yield x, y
 
-        out = real(stepper, tap(), eval_batches=eval_batches, microbatches=microbatches)
-        seen_runs.append(seen)
-        return out
+        result = original(stepper, recording(), **kw)
+        windows_per_eval.append(taken)
+        return result
 
-    monkeypatch.setattr(train_module, "run_validation", watching)
-    monkeypatch.setattr(train_module, "plot_run", lambda _: None)
-    state = train_module.train(ModelWeights.init(0, c), c, tcfg)
-    assert int(state.optimizer.adam_count) == tcfg.steps
-    assert final_ready == [False, False, True]
-    for seen in seen_runs:
-        assert len(seen) == tcfg.eval_batches
-        for i, (xs, ys) in enumerate(seen):
-            start = i * c.seq_len
-            np.testing.assert_array_equal(xs, eval_tokens[start:start + c.seq_len])
-            np.testing.assert_array_equal(ys, eval_tokens[start + 1:start + c.seq_len + 1])
-    rows = [json.loads(line) for line in (tcfg.checkpoint_path / "metrics.jsonl").read_text().splitlines()]
-    assert [r["step"] for r in rows if r["kind"] == "eval"] == [0, 2, 3]
+    monkeypatch.setattr(train_module, "run_validation", spy)
+    monkeypatch.setattr(train_module, "plot_run", lambda run_dir: None)
+    train_module.train(ModelWeights.init(0, c), c, tcfg)
+
+    logged = [json.loads(line) for line in (tcfg.checkpoint_path / "metrics.jsonl").read_text().splitlines()]
+    assert [row["step"] for row in logged if row["kind"] == "eval"] == [0, 3, 5]
+    assert checkpoint_seen == [False, False, True]          # only the last evaluation comes after the final checkpoint
+    expected = [(held_out[i * T:(i + 1) * T], held_out[i * T + 1:(i + 1) * T + 1]) for i in range(n_eval)]
+    for taken in windows_per_eval:
+        assert len(taken) == n_eval
+        for (x, y), (want_x, want_y) in zip(taken, expected):
+            assert np.array_equal(x, want_x) and np.array_equal(y, want_y)
