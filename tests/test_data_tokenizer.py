@@ -100,3 +100,29 @@ def test_prepare_script_tokenizes_local_files_up_to_the_limit(tmp_path):
     stream = TokenBlocks(out, 1, 8).read(0, 700)
     first = tok.encode_ordinary("the quick brown fox jumps over the lazy dog " * 4)
     assert stream[:len(first)].tolist() == first and stream[len(first)] == tok.eos_token
+
+
+def test_dataset_script_selects_whole_shards_and_writes_synthetic_ones_the_loader_reads(tmp_path):
+    import importlib.util
+    import sys
+    from pathlib import Path
+
+    spec = importlib.util.spec_from_file_location("dataset_script", Path(__file__).resolve().parents[1] / "data" / "dataset.py")
+    ds = importlib.util.module_from_spec(spec)
+    sys.modules["dataset_script"] = ds                   # dataclasses look their module up while the class is built
+    spec.loader.exec_module(ds)
+
+    few = ds.ShardSelection.for_budget(2 * ds.SHARD_TOKENS + 1, with_val=True)        # budgets round up to whole shards
+    assert few.train == (0, 1, 2) and few.val == (ds.N_SHARDS - 1,)
+    everything = ds.ShardSelection.for_budget(None, with_val=False)
+    assert everything.train == tuple(range(ds.N_SHARDS - 1)) and everything.val == ()
+    with pytest.raises(SystemExit):
+        ds.ShardSelection.for_budget(ds.N_SHARDS * ds.SHARD_TOKENS, with_val=True)    # more than the training shards hold
+    assert ds.shard_files((7,)) == ["shard-00007.array_record", "shard-00007.array_record" + ds.LENGTHS_SUFFIX]
+
+    ds.write_synthetic(4000, tmp_path / "train", seed=3, vocab=97, doc_len=300)
+    blocks = TokenBlocks(tmp_path / "train", 2, 16)
+    assert len(blocks) == (4000 - 1) // 32
+    first = blocks[0]
+    assert first["input_ids"].shape == (2, 16) and int(first["input_ids"].max()) < 97
+    assert np.array_equal(first["input_ids"].reshape(-1)[1:], first["labels"].reshape(-1)[:-1])
