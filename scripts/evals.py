@@ -1,81 +1,76 @@
-"""Loglikelihood evaluation (MMLU, ARC-Challenge, ARC-Easy, HellaSwag) of a checkpoint."""
+"""Multiple-choice evaluation of a checkpoint by continuation log-likelihood: MMLU, ARC-Challenge, ARC-Easy, HellaSwag.
+
+Flags follow the reference's ``scripts/evals.py``. Launched under ``python -m torch.distributed.run --nproc-per-node N``
+the model is split tensor-parallel over the N processes and every process scores the same documents; the first one
+reports."""
 
 from __future__ import annotations
 
-import os
-import sys
 from dataclasses import dataclass, field
-from pathlib import Path
 from typing import Literal
 
 import tyro
 
-ROOT = Path(__file__).resolve().parents[1]
-sys.path.insert(0, str(ROOT))
+try:
+    from scripts._launch import default_weights, join_tensor_parallel, place
+except ImportError:                        # run as a file: scripts/ itself is the import root
+    from _launch import default_weights, join_tensor_parallel, place
+
+TaskName = Literal["mmlu", "arc-challenge", "arc-easy", "hellaswag"]
 
 
 @dataclass(frozen=True)
 class Args:
     variant: str = "lyra-small"
-    """Model variant."""
+    """Which model variant the checkpoint belongs to."""
     weights: str | None = None
-    """Checkpoint path; defaults to chkpt/<variant>."""
-    tasks: tuple[Literal["mmlu", "arc-challenge", "arc-easy", "hellaswag"], ...] = ("mmlu", "arc-challenge", "arc-easy", "hellaswag")
-    """Evaluation tasks."""
+    """Checkpoint (or run) directory; chkpt/<variant> when omitted."""
+    tasks: tuple[TaskName, ...] = ("mmlu", "arc-challenge", "arc-easy", "hellaswag")
+    """Tasks to run, in this order."""
     format: Literal["orbax", "gpt-oss"] = "orbax"
-    """Checkpoint format."""
+    """orbax: a checkpoint written by scripts/train.py; gpt-oss: an original/ GPT-OSS checkpoint (Harmony prompts)."""
     device: Literal["auto", "cpu", "gpu"] = "auto"
-    """Device."""
+    """auto takes a GPU when there is one."""
     batch_size: int = 8
-    """Sequences per forward pass."""
+    """Continuations scored per forward pass."""
     limit: int | None = None
-    """Maximum documents per task."""
+    """Score only the first N documents of each task."""
     fewshot: dict[str, int] = field(default_factory=dict)
-    """Few-shot examples per task; tasks not listed are zero-shot."""
+    """Number of in-context examples per task, e.g. --fewshot mmlu=5; unlisted tasks get none."""
     fewshot_seed: int = 1234
-    """Seed for choosing ARC and HellaSwag few-shot examples."""
+    """Seed of the draw of ARC and HellaSwag in-context examples."""
+
+
+def open_model(args: Args, where, config):
+    from lyra_b200.gpt_oss import load_gpt_oss_model
+    from lyra_b200.model import ModelWeights
+
+    source = args.weights or default_weights(args.variant)
+    if args.format == "gpt-oss":
+        return load_gpt_oss_model(source, config, device=where.device, shard_fn=where.shard_fn)
+    return ModelWeights.load(source, config, device=where.device, rt=where.runtime)
 
 
 def main(argv: list[str] | None = None) -> int:
     args = tyro.cli(Args, args=argv)
-    import torch
-
     from lyra_b200.evals import TASKS, Scorer, evaluate
-    from lyra_b200.gpt_oss import load_gpt_oss_model
-    from lyra_b200.model import ModelWeights
     from lyra_b200.variants import model_variant
 
-    use_gpu = args.device == "gpu" or (args.device == "auto" and torch.cuda.is_available())
-    world, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
-    if use_gpu:
-        torch.cuda.set_device(local)
-    device = f"cuda:{local}" if use_gpu else "cpu"
     config = model_variant(args.variant)
-    weights = args.weights or str(ROOT / "chkpt" / args.variant)
-    rt = None
-    if world > 1:   # under torch.distributed.run the model is split tensor-parallel; every rank scores the same documents
-        import torch.distributed as dist
-
-        from lyra_b200.parallel.tp import TensorParallel
-
-        dist.init_process_group("nccl" if use_gpu else "gloo")
-        rt = TensorParallel(config, dist.get_rank(), world)
-    say = print if rt is None or rt.rank == 0 else (lambda *a, **k: None)
-    if args.format == "gpt-oss":
-        model = load_gpt_oss_model(weights, config, device=device, shard_fn=rt.shard_info if rt is not None else None)
-    else:
-        model = ModelWeights.load(weights, config, device=device, rt=rt)
-    scorer = Scorer(model, config, batch_size=args.batch_size, harmony=args.format == "gpt-oss", device=device, rt=rt)
-    results = []
-    for task in args.tasks:
-        shots = args.fewshot.get(task, 0)
-        docs = TASKS[task](limit=args.limit, num_fewshot=shots, fewshot_seed=args.fewshot_seed)
-        say(f"Running {task} ({shots}-shot) on {len(docs)} documents...", flush=True)
-        results.append(evaluate(task, docs, scorer))
-        say(results[-1], flush=True)
-    say("\nResults")
-    for result in results:
-        say(result)
+    where = join_tensor_parallel(place(args.device), config)
+    scorer = Scorer(open_model(args, where, config), config, batch_size=args.batch_size, harmony=args.format == "gpt-oss",
+                    device=where.device, rt=where.runtime)
+    summary = []
+    for name in args.tasks:
+        shots = args.fewshot.get(name, 0)
+        documents = TASKS[name](limit=args.limit, num_fewshot=shots, fewshot_seed=args.fewshot_seed)
+        where.say(f"[{name}] {len(documents)} documents, {shots}-shot ...", flush=True)
+        outcome = evaluate(name, documents, scorer)
+        where.say(f"[{name}] {outcome}", flush=True)
+        summary.append(outcome)
+    where.say("\nSummary")
+    for outcome in summary:
+        where.say(f"  {outcome}")
     return 0
 
 
