@@ -18,6 +18,9 @@ from lyra_b200.tokenizer import LyraTokenizer
 
 @dataclass(frozen=True)
 class Doc:
+    """One multiple-choice question: the text shown to the model, the candidate continuations, the index of the right one, and
+    whether the task also reports length-normalised accuracy (field names as in lyra/evals/common.py)."""
+
     context: str
     choices: tuple[str, ...]
     gold: int
@@ -26,14 +29,18 @@ class Doc:
 
 @dataclass
 class EvalResult:
+    """Accuracy of one task; ``acc_norm`` only for tasks whose documents ask for it."""
+
     task: str
     num_docs: int
     acc: float
     acc_norm: float | None = None
 
     def __str__(self) -> str:
-        norm = "" if self.acc_norm is None else f" acc_norm={self.acc_norm:.4f}"
-        return f"{self.task}: acc={self.acc:.4f}{norm} (n={self.num_docs})"
+        parts = [f"acc={self.acc:.4f}"]
+        if self.acc_norm is not None:
+            parts.append(f"acc_norm={self.acc_norm:.4f}")
+        return f"{self.task}: {' '.join(parts)} (n={self.num_docs})"
 
 
 @torch.no_grad()
@@ -58,21 +65,30 @@ class Scorer:
     def __init__(self, model: ModelWeights, config: ModelConfig, *, batch_size: int = 8, harmony: bool = False, device="cpu", rt=None) -> None:
         self.model, self.config, self.batch_size, self.device, self.rt = model, config, batch_size, device, rt
         self.tokenizer = LyraTokenizer()
-        self.harmony = None
-        if harmony:
-            from openai_harmony import HarmonyEncodingName, load_harmony_encoding
+        self.harmony = self._harmony_encoding() if harmony else None
 
-            self.harmony = load_harmony_encoding(HarmonyEncodingName.HARMONY_GPT_OSS)
+    @staticmethod
+    def _harmony_encoding():
+        import openai_harmony as oh
+
+        return oh.load_harmony_encoding(oh.HarmonyEncodingName.HARMONY_GPT_OSS)
 
     def _encode(self, context: str, continuation: str) -> tuple[list[int], list[int]]:
-        if self.harmony is None:
-            return [self.tokenizer.eos_token, *self.tokenizer.encode_ordinary(context)], self.tokenizer.encode_ordinary(continuation)
-        from openai_harmony import Conversation, Message, Role
+        """Token ids of the context and of the continuation. Plain models see ``<eos> context``; GPT-OSS models see the context
+        as a user message and answer in the ``final`` channel of an assistant message (lyra/evals/common.py:52-63)."""
+        if self.harmony is not None:
+            return self._encode_chat(context, continuation)
+        tok = self.tokenizer
+        return [tok.eos_token] + list(tok.encode_ordinary(context)), list(tok.encode_ordinary(continuation))
 
-        conversation = Conversation.from_messages([Message.from_role_and_content(Role.USER, context)])
-        prompt = self.harmony.render_conversation_for_completion(conversation, Role.ASSISTANT)
-        prompt += self.harmony.encode("<|channel|>final<|message|>", allowed_special="all")
-        return prompt, self.harmony.encode(continuation)
+    def _encode_chat(self, context: str, continuation: str) -> tuple[list[int], list[int]]:
+        import openai_harmony as oh
+
+        enc = self.harmony
+        asked = oh.Conversation.from_messages([oh.Message.from_role_and_content(oh.Role.USER, context)])
+        opening = list(enc.render_conversation_for_completion(asked, oh.Role.ASSISTANT))
+        opening += enc.encode("<|channel|>final<|message|>", allowed_special="all")
+        return opening, list(enc.encode(continuation))
 
     def requests(self, docs: list[Doc]) -> list["Request"]:
         """One request per (document, choice). The continuation is the choice joined to the context by a single space (trailing
@@ -125,18 +141,29 @@ class Request:
 
 
 def evaluate(task: str, docs: list[Doc], scorer: Scorer) -> EvalResult:
+    """``acc``: share of documents whose highest-scoring choice is the gold one; ``acc_norm`` (when the task's documents ask for
+    it): the same after dividing every score by its choice's length in characters."""
     scores = scorer.score(docs)
-    correct = [int(np.argmax(s)) == doc.gold for doc, s in zip(docs, scores)]
-    acc_norm = None
-    if docs[0].normalize_choices:
-        normalized = [[s / len(choice) for s, choice in zip(ss, doc.choices)] for doc, ss in zip(docs, scores)]
-        acc_norm = float(np.mean([int(np.argmax(s)) == doc.gold for doc, s in zip(docs, normalized)]))
-    return EvalResult(task=task, num_docs=len(docs), acc=float(np.mean(correct)), acc_norm=acc_norm)
+    gold = np.array([doc.gold for doc in docs])
+
+    def accuracy(per_doc) -> float:
+        picked = np.array([int(np.argmax(row)) for row in per_doc])
+        return float((picked == gold).mean())
+
+    by_length = None
+    if docs and docs[0].normalize_choices:
+        by_length = accuracy([np.asarray(row) / np.array([len(choice) for choice in doc.choices]) for doc, row in zip(docs, scores)])
+    return EvalResult(task=task, num_docs=len(docs), acc=accuracy(scores), acc_norm=by_length)
 
 
 def few_shot_prefix(docs: list[Doc]) -> str:
-    return "".join(f"{doc.context} {doc.choices[doc.gold]}\n\n" for doc in docs)
+    """The in-context examples in front of a question: each example's context, a space, its right answer, a blank line."""
+    shown = [doc.context + " " + doc.choices[doc.gold] for doc in docs]
+    return "\n\n".join(shown) + "\n\n" if shown else ""
 
 
 def select_limit(data, limit: int | None):
-    return data if limit is None else data.select(range(min(limit, len(data))))
+    """The first ``limit`` rows of a Hugging Face dataset (all of them for None)."""
+    if limit is None or limit >= len(data):
+        return data
+    return data.select(range(limit))
