@@ -320,3 +320,39 @@ def test_dkv_ring_needs_more_than_two_stages_to_run_ahead():
     for stages in (2, 3, 4, 6):
         for seed in range(10):
             DkvKernel(9, random.Random(seed), stages=stages).run()
+
+
+# ======================================================================================================================
+# dQ kernel: Q and dO are copied once into TMEM by the two elementwise groups (barrier a_full, 2 arrivals here), then the same
+# alternation as above over 64-key tiles with a four-stage (K, V) ring; dS replaces dP in place.
+class DqKernel(DkvKernel):
+    def __init__(self, n_tiles, rng, stages=4):
+        super().__init__(n_tiles, rng, stages)
+        self.q_full, self.a_full = Bar(1), Bar(2)
+        self.resident = 0                           # groups whose operand copy has landed in TMEM
+
+    def tma(self):
+        if self.n:
+            self.q_full.arrive()
+        yield from (step for step in super().tma() if True)
+
+    def mma(self):
+        if self.n == 0:
+            return
+        yield lambda: self.a_full.done(0)
+        assert self.resident == 2, "a product was issued before both resident operands were in TMEM"
+        yield from super().mma()
+
+    def group(self, g):
+        if self.n:
+            yield lambda: self.q_full.done(0)
+            yield None                              # shared memory -> registers -> TMEM
+            self.resident += 1
+            self.a_full.arrive()
+        yield from super().group(g)
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_dq_kernel_protocol_has_no_deadlock_and_no_early_reuse(seed):
+    rng = random.Random(seed)
+    DqKernel(rng.choice([0, 1, 2, 3, 5, 8, 13, 64]), rng).run()
